@@ -1,0 +1,172 @@
+/*
+ * orin_attn_b200 -- C ABI of the B200 (sm_100a) attention path for Heng-W/orin_llm.
+ *
+ * This is the drop-in boundary: plain pointers and sizes, no C++ or framework types.  The
+ * reference reaches its attention through free functions in `namespace llm::cuda`
+ * (src/kernels.h); each entry point below names the reference function it stands in for.
+ * The C++ wrappers with the reference's exact signatures are in
+ * orin_llm_b200/host/kernels.h and are implemented on top of this header.
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer unless the comment says "host".
+ *   - The caller owns every buffer; nothing here allocates, frees or synchronises.
+ *   - `stream` is a cudaStream_t passed as void* (the reference does the same in
+ *     cuda::set_stream, src/kernels.h:10).  Every call is asynchronous on that stream and may
+ *     be recorded into a CUDA graph: launch shapes never depend on the token position, which
+ *     arrives through `d_pos` in device memory (src/kernels.h:59-62, 69-70, 80-81).
+ *   - Return value: OATTN_OK or an OATTN_ERR_* code.  Nothing aborts (the reference aborts
+ *     through CUDA_CHECK, src/common.h:14-22; a library must not).
+ *   - KV cache of one layer: fp16 bit patterns as uint16_t, laid out [n_kv][n_ctx][head_dim]
+ *     (src/kernels.cu:1675, src/model_gpu.cu:229-235, 259-260).
+ *   - Activations q / k / v / out: fp32, [batch][heads][head_dim] (src/kernels.cu:1404, 1563).
+ *   - head_dim must be 64 or 128 (same restriction as src/kernels.cu:1976-1980);
+ *     n_head must be a multiple of n_kv with n_head/n_kv <= 16.
+ */
+#ifndef ORIN_ATTN_B200_H
+#define ORIN_ATTN_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+    OATTN_OK = 0,
+    OATTN_ERR_ARG = 1,         /* null pointer, non-positive size, batch/n_past outside n_ctx */
+    OATTN_ERR_UNSUPPORTED = 2, /* head_dim, GQA ratio or n_rot outside what the kernels cover */
+    OATTN_ERR_WORKSPACE = 3,   /* workspace missing, misaligned or smaller than *_workspace_bytes() */
+    OATTN_ERR_CUDA = 4,        /* a CUDA runtime call or launch failed; see oattn_last_cuda_error() */
+    OATTN_ERR_DEVICE = 5       /* not an sm_100 device, or oattn_init() not called on this device */
+};
+
+/* RoPE pairing, numbered like HParams::rope_type (src/model.h:27-28). */
+enum { OATTN_ROPE_NORMAL = 0, OATTN_ROPE_NEOX = 1 };
+
+/* What the fused attention calls do before attending (src/model_gpu.cu:277-282, 379-384). */
+enum {
+    OATTN_FUSE_NONE = 0,      /* q already rotated, cache already holds this step's K/V          */
+    OATTN_FUSE_ROPE_Q = 1,    /* rotate q (not written back)                                     */
+    OATTN_FUSE_ROPE_K = 2,    /* rotate k_new before it is appended (needs OATTN_FUSE_KV_APPEND) */
+    OATTN_FUSE_KV_APPEND = 4, /* convert k_new, v_new to fp16 and store them in the cache         */
+    OATTN_FUSE_ALL = 7
+};
+
+/* RoPE parameters of the fused calls (src/model.h:24-30).  freq_factors: device, n_rot/2 floats
+ * or NULL (src/model_common.cpp:37-43). */
+typedef struct oattn_rope_params {
+    int rope_type;
+    int n_rot;
+    float theta;
+    const float* freq_factors;
+} oattn_rope_params;
+
+const char* oattn_strerror(int code);
+/* Text of the last CUDA error seen by this library on the calling thread's device (host string). */
+const char* oattn_last_cuda_error(void);
+
+/* Replaces cuda::init (src/kernels.cu:1730-1737), generalised from device 0 to `device`:
+ * makes it current, checks for compute capability 10.x, raises the shared-memory limits of the
+ * kernels once (the reference does that on every launch, src/kernels.cu:1968,1988). */
+int oattn_init(int device);
+/* Number of SMs of the initialised device (0 before oattn_init). */
+int oattn_sm_count(void);
+
+/* ---- unfused building blocks: same semantics as the reference wrappers -------------------- */
+
+/* Replaces cuda::rope_neox_batch / rope_normal_batch (src/kernels.cu:2059-2067) when d_pos is
+ * NULL: row r of x [rows][head_dim] is rotated in place at position n_past + r/heads.
+ * Replaces cuda::rope_neox_ind / rope_normal_ind (src/kernels.cu:2069-2075) when d_pos is not
+ * NULL: every row is rotated at position *d_pos (n_past, heads ignored).
+ * Frequencies and angles are evaluated as the reference's CPU backend does
+ * (src/model_cpu.cpp:179-203), not with the fast-math intrinsics of src/kernels.cu:1631-1634. */
+int oattn_rope(float* x, int rows, int head_dim, int rope_type, int n_rot, float theta, int n_past,
+               int heads, const int* d_pos, const float* freq_factors, void* stream);
+
+/* Replaces cuda::kv_store_batch (src/kernels.cu:2079-2083) when d_pos is NULL: k, v
+ * [batch][heads][head_dim] fp32 -> fp16 at cache rows pos_base + b.
+ * Replaces cuda::kv_store_ind (src/kernels.cu:2085-2088) when d_pos is not NULL: one token at
+ * row *d_pos (pos_base ignored, batch must be 1). */
+int oattn_kv_store(uint16_t* kc, uint16_t* vc, const float* k, const float* v, int heads, int head_dim,
+                   int n_ctx, int pos_base, int batch, const int* d_pos, void* stream);
+
+/* Replaces cuda::kv_shift (src/kernels.cu:2090-2093): for every layer and kv head drop rows
+ * [n_keep, n_keep+shift), slide the rest left, zero the last `shift` rows.  kc, vc point at
+ * layer 0; layers are n_kv*n_ctx*head_dim elements apart.  In place, no scratch.
+ * Requires 0 <= n_keep, 0 < shift, n_keep + shift <= n_ctx. */
+int oattn_kv_shift(uint16_t* kc, uint16_t* vc, int n_layer, int n_kv, int head_dim, int n_ctx, int n_keep,
+                   int shift, void* stream);
+
+/* ---- decode: one query token, split-KV flash decoding + log-sum-exp combine --------------- */
+
+/* Bytes of scratch the decode calls need for their per-split partial results (m, l, O).
+ * Follows the reference's scratch_size()/scratch_assign() pattern (src/kernels.cu:1753-1776):
+ * the caller allocates once and passes the block on every call.  256-byte aligned. */
+size_t oattn_decode_workspace_bytes(int n_head, int n_kv, int head_dim);
+
+/* Replaces the decode sequence rope_*_ind(q), rope_*_ind(k), kv_store_ind,
+ * flash_attention_decode_ind (src/model_gpu.cu:277-282; src/kernels.cu:1993-2000).
+ * Attends q [n_head][head_dim] over cache rows 0..*d_pos.  With fuse == OATTN_FUSE_NONE it is
+ * exactly flash_attention_decode_ind (k_new, v_new, rope may be NULL).  With fuse flags the new
+ * token's K/V row (k_new, v_new: [n_kv][head_dim] fp32) is rotated, converted and stored at row
+ * *d_pos inside the same launch.  Two launches: split kernel (grid fixed by n_kv and the SM
+ * count) and combine kernel. */
+int oattn_decode(const float* q, const float* k_new, const float* v_new, uint16_t* kc, uint16_t* vc,
+                 float* out, int n_head, int n_kv, int head_dim, int n_ctx, const int* d_pos, float scale,
+                 int fuse, const oattn_rope_params* rope, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Multi-GPU building block (no reference counterpart as a function; the arithmetic is the
+ * cross-warp merge of src/kernels.cu:1300-1342 lifted to KV slices).  Attends q over the LOCAL
+ * cache rows [0, *d_len) and writes one un-normalised partial per head:
+ * part [n_head][head_dim + 4] = { O[head_dim], m, l, 0, 0 } with m = max score (scaled),
+ * l = sum exp(score - m), O = sum exp(score - m) * v.  *d_len == 0 gives m = -inf, l = 0. */
+int oattn_decode_partial(const float* q, const uint16_t* kc, const uint16_t* vc, float* part, int n_head,
+                         int n_kv, int head_dim, int n_ctx, const int* d_len, float scale, void* workspace,
+                         size_t workspace_bytes, void* stream);
+
+/* Merges n_parts partials laid out [n_parts][n_head][head_dim + 4] (the all-gathered output of
+ * oattn_decode_partial on every rank) into out [n_head][head_dim]:
+ * M = max m_r, L = sum l_r e^(m_r - M), out = sum O_r e^(m_r - M) / L. */
+int oattn_combine(const float* parts, int n_parts, float* out, int n_head, int head_dim, void* stream);
+
+/* ---- prefill: a chunk of `batch` query tokens, causal ------------------------------------ */
+
+/* Scratch for the prefill call (fp16 staging of the rotated, scaled queries). 256-byte aligned. */
+size_t oattn_prefill_workspace_bytes(int n_head, int n_kv, int head_dim, int max_batch);
+
+/* Replaces the prefill sequence rope_*_batch(q), rope_*_batch(k), kv_store_batch,
+ * flash_attention (src/model_gpu.cu:379-384; src/kernels.cu:1974-1981).  Query token t of
+ * q [batch][n_head][head_dim] sits at position n_past + t and sees cache rows 0..n_past+t.
+ * With fuse == OATTN_FUSE_NONE it is exactly cuda::flash_attention. */
+int oattn_prefill(const float* q, const float* k_new, const float* v_new, uint16_t* kc, uint16_t* vc,
+                  float* out, int n_head, int n_kv, int head_dim, int n_ctx, int n_past, int batch,
+                  float scale, int fuse, const oattn_rope_params* rope, void* workspace, size_t workspace_bytes,
+                  void* stream);
+
+/* Which prefill kernel oattn_prefill launches: 0 = tcgen05/TMEM kernel (default),
+ * 1 = the warp-level mma.sync kernel kept as an in-library cross-check.  Process-wide. */
+int oattn_set_prefill_impl(int impl);
+
+/* Lower bound on the 64-row tiles one decode split handles (default 2): short contexts then
+ * use fewer, fuller splits.  Process-wide tuning knob; must not change between the capture and
+ * the replays of a CUDA graph. */
+int oattn_set_decode_min_tiles(int tiles);
+
+/* Opt-in kernel timing for benchmarks (off by default; the hot calls allocate nothing either way:
+ * the events are created here).  After oattn_profile_enable(n) every oattn_decode /
+ * oattn_decode_partial call brackets its split-KV kernel (not the combine kernel) with a pair of
+ * CUDA events on the call's stream, for the first n calls.  oattn_profile_collect waits for those
+ * events, writes the elapsed milliseconds of each recorded call to ms (host, `capacity` floats),
+ * stores the count in *n_written and rearms the counter.  oattn_profile_enable(0) destroys the
+ * events.  Not for use during stream capture. */
+int oattn_profile_enable(int max_records);
+int oattn_profile_collect(float* ms, int capacity, int* n_written);
+
+/* Number of kernels this library has launched since load (for launch accounting in benchmarks). */
+unsigned long long oattn_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ORIN_ATTN_B200_H */

@@ -1,0 +1,74 @@
+// Internal launch interface between the C ABI (capi.cu) and the kernel translation units.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "common.cuh"
+
+namespace oattn {
+
+constexpr int DECODE_TILE = 64;        // cache rows per pipeline stage of the decode kernel
+constexpr int DECODE_MAX_SPLITS = 512; // upper bound on KV splits per kv head (combine smem)
+constexpr int PART_PAD = 4;            // floats after O in a partial record: m, l, 0, 0
+
+struct DecodeArgs {
+    const float* q;        // [n_head][hd] fp32
+    const float* k_new;    // [n_kv][hd] fp32 or nullptr
+    const float* v_new;    // [n_kv][hd] fp32 or nullptr
+    uint16_t* kc;          // [n_kv][n_ctx][hd] fp16 bits
+    uint16_t* vc;
+    float* out;            // [n_head][hd] (final) or [n_head][hd+PART_PAD] (partial record)
+    float* ws_o;           // [n_head][n_splits][hd]
+    float* ws_ml;          // [n_head][n_splits][2]  (m in natural-log units of the scaled score, l)
+    const int* d_pos;      // device scalar
+    int pos_bias;          // valid rows = *d_pos + pos_bias  (1: d_pos is the new token's position; 0: d_pos is a length)
+    int n_head, n_kv, head_dim, n_ctx, n_splits, min_tiles;
+    float scale;
+    int fuse;
+    RopeArgs rope;
+    int emit_partial;      // combine writes the un-normalised record instead of the normalised output
+};
+
+// Number of KV splits per kv head the decode launch uses on a device with `sm_count` SMs.
+int decode_num_splits(int n_kv, int sm_count);
+cudaError_t decode_set_attributes();
+// ev_start / ev_stop (optional) are recorded around the split kernel only.
+cudaError_t launch_decode(const DecodeArgs& a, cudaStream_t stream, unsigned long long* launches,
+                          cudaEvent_t ev_start = nullptr, cudaEvent_t ev_stop = nullptr);
+// Merge n_parts records [n_parts][n_head][hd+PART_PAD] -> out [n_head][hd].
+cudaError_t launch_combine_records(const float* parts, int n_parts, float* out, int n_head, int head_dim,
+                                   cudaStream_t stream, unsigned long long* launches);
+
+struct PrefillArgs {
+    const float* q;        // [batch][n_head][hd] fp32
+    const float* k_new;    // [batch][n_kv][hd] fp32 or nullptr
+    const float* v_new;
+    uint16_t* kc;
+    uint16_t* vc;
+    float* out;            // [batch][n_head][hd] fp32
+    __half* q16;           // workspace: [batch][n_head][hd] fp16, rotated and pre-scaled by scale*log2(e)
+    int n_head, n_kv, head_dim, n_ctx, n_past, batch;
+    float scale;
+    int fuse;
+    RopeArgs rope;
+};
+
+// Prologue shared by both prefill kernels: RoPE(q) -> q16, RoPE(k_new) + fp16 append of k_new, v_new.
+cudaError_t launch_prefill_prologue(const PrefillArgs& a, cudaStream_t stream, unsigned long long* launches);
+cudaError_t prefill_mma_set_attributes();
+cudaError_t launch_prefill_mma(const PrefillArgs& a, cudaStream_t stream, unsigned long long* launches);
+cudaError_t prefill_tc_set_attributes();
+// Returns cudaErrorNotSupported when the tcgen05 kernel does not cover the shape.
+cudaError_t launch_prefill_tc(const PrefillArgs& a, int sm_count, cudaStream_t stream, unsigned long long* launches);
+
+cudaError_t launch_rope(float* x, int rows, int head_dim, const RopeArgs& r, int n_past, int heads,
+                        const int* d_pos, cudaStream_t stream, unsigned long long* launches);
+cudaError_t launch_kv_store(uint16_t* kc, uint16_t* vc, const float* k, const float* v, int heads, int head_dim,
+                            int n_ctx, int pos_base, int batch, const int* d_pos, cudaStream_t stream,
+                            unsigned long long* launches);
+cudaError_t launch_kv_shift(uint16_t* kc, uint16_t* vc, int n_layer, int n_kv, int head_dim, int n_ctx, int n_keep,
+                            int shift, cudaStream_t stream, unsigned long long* launches);
+
+} // namespace oattn

@@ -1,0 +1,285 @@
+// extern "C" layer: argument checking, workspace carving, launch.  See include/orin_attn_b200.h.
+#include <stdio.h>
+#include <string.h>
+
+#include "../../include/orin_attn_b200.h"
+#include "attn_internal.h"
+
+using namespace oattn;
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+struct DeviceState {
+    bool ready = false;
+    int sm_count = 0;
+};
+DeviceState g_dev[kMaxDevices];
+int g_cur = -1;                       // device of the last oattn_init
+int g_prefill_impl = 0;               // 0 = tcgen05, 1 = mma.sync
+int g_decode_min_tiles = 2;
+unsigned long long g_launches = 0;
+char g_cuda_err[256] = "";
+
+// opt-in timing of the split-KV kernel (oattn_profile_enable)
+cudaEvent_t* g_prof_ev = nullptr;   // 2 * g_prof_cap events: start, stop per record
+int g_prof_cap = 0, g_prof_n = 0;
+
+int cuda_fail(cudaError_t e, const char* where) {
+    snprintf(g_cuda_err, sizeof(g_cuda_err), "%s: %s", where, cudaGetErrorString(e));
+    return OATTN_ERR_CUDA;
+}
+
+inline size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+int check_shape(int n_head, int n_kv, int head_dim) {
+    if (n_head <= 0 || n_kv <= 0) return OATTN_ERR_ARG;
+    if (head_dim != 64 && head_dim != 128) return OATTN_ERR_UNSUPPORTED;
+    if (n_head % n_kv != 0 || n_head / n_kv > 16) return OATTN_ERR_UNSUPPORTED;
+    return OATTN_OK;
+}
+
+int check_rope(int fuse, const oattn_rope_params* rope, int head_dim, RopeArgs& r) {
+    r = RopeArgs{0, 0, 10000.0f, nullptr};
+    if (fuse & (OATTN_FUSE_ROPE_Q | OATTN_FUSE_ROPE_K)) {
+        if (!rope) return OATTN_ERR_ARG;
+        if (rope->rope_type != OATTN_ROPE_NORMAL && rope->rope_type != OATTN_ROPE_NEOX) return OATTN_ERR_ARG;
+        if (rope->n_rot <= 0 || rope->n_rot > head_dim || (rope->n_rot & 1)) return OATTN_ERR_UNSUPPORTED;
+        if (!(rope->theta > 0.0f)) return OATTN_ERR_ARG;
+        r.rope_type = rope->rope_type;
+        r.n_rot = rope->n_rot;
+        r.theta = rope->theta;
+        r.freq_factors = rope->freq_factors;
+    }
+    return OATTN_OK;
+}
+
+bool device_ready() { return g_cur >= 0 && g_dev[g_cur].ready; }
+
+struct DecodeWs {
+    size_t o_bytes, ml_bytes, total;
+    int n_splits;
+};
+DecodeWs decode_ws(int n_head, int n_kv, int head_dim, int sm_count) {
+    DecodeWs w;
+    w.n_splits = decode_num_splits(n_kv, sm_count);
+    w.o_bytes = align256((size_t)n_head * w.n_splits * head_dim * sizeof(float));
+    w.ml_bytes = align256((size_t)n_head * w.n_splits * 2 * sizeof(float));
+    w.total = w.o_bytes + w.ml_bytes;
+    return w;
+}
+
+} // namespace
+
+extern "C" {
+
+const char* oattn_strerror(int code) {
+    switch (code) {
+        case OATTN_OK: return "ok";
+        case OATTN_ERR_ARG: return "invalid argument";
+        case OATTN_ERR_UNSUPPORTED: return "shape not supported (head_dim 64/128, n_head/n_kv <= 16, even n_rot <= head_dim)";
+        case OATTN_ERR_WORKSPACE: return "workspace missing, misaligned or too small";
+        case OATTN_ERR_CUDA: return "CUDA error";
+        case OATTN_ERR_DEVICE: return "device not initialised or not compute capability 10.x";
+        default: return "unknown error";
+    }
+}
+
+const char* oattn_last_cuda_error(void) { return g_cuda_err; }
+
+int oattn_init(int device) {
+    if (device < 0 || device >= kMaxDevices) return OATTN_ERR_ARG;
+    cudaError_t e = cudaSetDevice(device);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaSetDevice");
+    int major = 0, sms = 0;
+    if ((e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device)) != cudaSuccess) return cuda_fail(e, "cudaDeviceGetAttribute");
+    if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device)) != cudaSuccess) return cuda_fail(e, "cudaDeviceGetAttribute");
+    if (major != 10) return OATTN_ERR_DEVICE;
+    if (!g_dev[device].ready) {
+        if ((e = decode_set_attributes()) != cudaSuccess) return cuda_fail(e, "decode attributes");
+        if ((e = prefill_mma_set_attributes()) != cudaSuccess) return cuda_fail(e, "prefill (mma) attributes");
+        if ((e = prefill_tc_set_attributes()) != cudaSuccess) return cuda_fail(e, "prefill (tcgen05) attributes");
+        g_dev[device].sm_count = sms;
+        g_dev[device].ready = true;
+    }
+    g_cur = device;
+    return OATTN_OK;
+}
+
+int oattn_sm_count(void) { return device_ready() ? g_dev[g_cur].sm_count : 0; }
+
+int oattn_rope(float* x, int rows, int head_dim, int rope_type, int n_rot, float theta, int n_past, int heads,
+               const int* d_pos, const float* freq_factors, void* stream) {
+    if (!device_ready()) return OATTN_ERR_DEVICE;
+    if (!x || rows < 0 || head_dim <= 0) return OATTN_ERR_ARG;
+    if (rope_type != OATTN_ROPE_NORMAL && rope_type != OATTN_ROPE_NEOX) return OATTN_ERR_ARG;
+    if (n_rot <= 0 || n_rot > head_dim || (n_rot & 1) || n_rot > 256) return OATTN_ERR_UNSUPPORTED;
+    if (!d_pos && heads <= 0) return OATTN_ERR_ARG;
+    RopeArgs r{rope_type, n_rot, theta, freq_factors};
+    cudaError_t e = launch_rope(x, rows, head_dim, r, n_past, heads, d_pos, (cudaStream_t)stream, &g_launches);
+    return e == cudaSuccess ? OATTN_OK : cuda_fail(e, "rope launch");
+}
+
+int oattn_kv_store(uint16_t* kc, uint16_t* vc, const float* k, const float* v, int heads, int head_dim, int n_ctx,
+                   int pos_base, int batch, const int* d_pos, void* stream) {
+    if (!device_ready()) return OATTN_ERR_DEVICE;
+    if (!kc || !vc || !k || !v || heads <= 0 || head_dim <= 0 || n_ctx <= 0 || batch <= 0) return OATTN_ERR_ARG;
+    if (d_pos && batch != 1) return OATTN_ERR_ARG;
+    if (!d_pos && (pos_base < 0 || pos_base + batch > n_ctx)) return OATTN_ERR_ARG;
+    cudaError_t e = launch_kv_store(kc, vc, k, v, heads, head_dim, n_ctx, pos_base, batch, d_pos, (cudaStream_t)stream, &g_launches);
+    return e == cudaSuccess ? OATTN_OK : cuda_fail(e, "kv_store launch");
+}
+
+int oattn_kv_shift(uint16_t* kc, uint16_t* vc, int n_layer, int n_kv, int head_dim, int n_ctx, int n_keep, int shift,
+                   void* stream) {
+    if (!device_ready()) return OATTN_ERR_DEVICE;
+    if (!kc || !vc || n_layer <= 0 || n_kv <= 0 || n_ctx <= 0) return OATTN_ERR_ARG;
+    if (head_dim <= 0 || (head_dim % 16) != 0) return OATTN_ERR_UNSUPPORTED;
+    if (n_keep < 0 || shift <= 0 || n_keep + shift > n_ctx) return OATTN_ERR_ARG;
+    cudaError_t e = launch_kv_shift(kc, vc, n_layer, n_kv, head_dim, n_ctx, n_keep, shift, (cudaStream_t)stream, &g_launches);
+    return e == cudaSuccess ? OATTN_OK : cuda_fail(e, "kv_shift launch");
+}
+
+size_t oattn_decode_workspace_bytes(int n_head, int n_kv, int head_dim) {
+    if (!device_ready() || check_shape(n_head, n_kv, head_dim) != OATTN_OK) return 0;
+    return decode_ws(n_head, n_kv, head_dim, g_dev[g_cur].sm_count).total;
+}
+
+static int decode_common(const float* q, const float* k_new, const float* v_new, uint16_t* kc, uint16_t* vc, float* out,
+                         int n_head, int n_kv, int head_dim, int n_ctx, const int* d_pos, int pos_bias, float scale,
+                         int fuse, const oattn_rope_params* rope, int emit_partial, void* workspace, size_t workspace_bytes,
+                         void* stream) {
+    if (!device_ready()) return OATTN_ERR_DEVICE;
+    int rc = check_shape(n_head, n_kv, head_dim);
+    if (rc != OATTN_OK) return rc;
+    if (!q || !kc || !vc || !out || !d_pos || n_ctx <= 0 || !(scale > 0.0f)) return OATTN_ERR_ARG;
+    if (fuse & ~OATTN_FUSE_ALL) return OATTN_ERR_ARG;
+    if ((fuse & OATTN_FUSE_ROPE_K) && !(fuse & OATTN_FUSE_KV_APPEND)) return OATTN_ERR_ARG;
+    if ((fuse & OATTN_FUSE_KV_APPEND) && (!k_new || !v_new)) return OATTN_ERR_ARG;
+    DecodeArgs a;
+    if ((rc = check_rope(fuse, rope, head_dim, a.rope)) != OATTN_OK) return rc;
+    const DecodeWs w = decode_ws(n_head, n_kv, head_dim, g_dev[g_cur].sm_count);
+    if (!workspace || ((uintptr_t)workspace & 255) || workspace_bytes < w.total) return OATTN_ERR_WORKSPACE;
+    a.q = q; a.k_new = k_new; a.v_new = v_new; a.kc = kc; a.vc = vc; a.out = out;
+    a.ws_o = reinterpret_cast<float*>(workspace);
+    a.ws_ml = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + w.o_bytes);
+    a.d_pos = d_pos; a.pos_bias = pos_bias;
+    a.n_head = n_head; a.n_kv = n_kv; a.head_dim = head_dim; a.n_ctx = n_ctx;
+    a.n_splits = w.n_splits; a.min_tiles = g_decode_min_tiles;
+    a.scale = scale; a.fuse = fuse; a.emit_partial = emit_partial;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    if (g_prof_ev && g_prof_n < g_prof_cap) {
+        ev0 = g_prof_ev[2 * g_prof_n];
+        ev1 = g_prof_ev[2 * g_prof_n + 1];
+        ++g_prof_n;
+    }
+    cudaError_t e = launch_decode(a, (cudaStream_t)stream, &g_launches, ev0, ev1);
+    return e == cudaSuccess ? OATTN_OK : cuda_fail(e, "decode launch");
+}
+
+int oattn_decode(const float* q, const float* k_new, const float* v_new, uint16_t* kc, uint16_t* vc, float* out,
+                 int n_head, int n_kv, int head_dim, int n_ctx, const int* d_pos, float scale, int fuse,
+                 const oattn_rope_params* rope, void* workspace, size_t workspace_bytes, void* stream) {
+    return decode_common(q, k_new, v_new, kc, vc, out, n_head, n_kv, head_dim, n_ctx, d_pos, 1, scale, fuse, rope, 0,
+                         workspace, workspace_bytes, stream);
+}
+
+int oattn_decode_partial(const float* q, const uint16_t* kc, const uint16_t* vc, float* part, int n_head, int n_kv,
+                         int head_dim, int n_ctx, const int* d_len, float scale, void* workspace, size_t workspace_bytes,
+                         void* stream) {
+    return decode_common(q, nullptr, nullptr, const_cast<uint16_t*>(kc), const_cast<uint16_t*>(vc), part, n_head, n_kv,
+                         head_dim, n_ctx, d_len, 0, scale, OATTN_FUSE_NONE, nullptr, 1, workspace, workspace_bytes, stream);
+}
+
+int oattn_combine(const float* parts, int n_parts, float* out, int n_head, int head_dim, void* stream) {
+    if (!device_ready()) return OATTN_ERR_DEVICE;
+    if (!parts || !out || n_head <= 0 || n_parts <= 0) return OATTN_ERR_ARG;
+    if (head_dim != 64 && head_dim != 128) return OATTN_ERR_UNSUPPORTED;
+    if (n_parts > DECODE_MAX_SPLITS) return OATTN_ERR_UNSUPPORTED;
+    if ((uintptr_t)parts & 15) return OATTN_ERR_ARG;
+    cudaError_t e = launch_combine_records(parts, n_parts, out, n_head, head_dim, (cudaStream_t)stream, &g_launches);
+    return e == cudaSuccess ? OATTN_OK : cuda_fail(e, "combine launch");
+}
+
+size_t oattn_prefill_workspace_bytes(int n_head, int n_kv, int head_dim, int max_batch) {
+    if (check_shape(n_head, n_kv, head_dim) != OATTN_OK || max_batch <= 0) return 0;
+    return align256((size_t)max_batch * n_head * head_dim * sizeof(__half));
+}
+
+int oattn_prefill(const float* q, const float* k_new, const float* v_new, uint16_t* kc, uint16_t* vc, float* out,
+                  int n_head, int n_kv, int head_dim, int n_ctx, int n_past, int batch, float scale, int fuse,
+                  const oattn_rope_params* rope, void* workspace, size_t workspace_bytes, void* stream) {
+    if (!device_ready()) return OATTN_ERR_DEVICE;
+    int rc = check_shape(n_head, n_kv, head_dim);
+    if (rc != OATTN_OK) return rc;
+    if (!q || !kc || !vc || !out || n_ctx <= 0 || !(scale > 0.0f)) return OATTN_ERR_ARG;
+    if (batch <= 0 || n_past < 0 || n_past + batch > n_ctx) return OATTN_ERR_ARG;
+    if (fuse & ~OATTN_FUSE_ALL) return OATTN_ERR_ARG;
+    if ((fuse & OATTN_FUSE_ROPE_K) && !(fuse & OATTN_FUSE_KV_APPEND)) return OATTN_ERR_ARG;
+    if ((fuse & OATTN_FUSE_KV_APPEND) && (!k_new || !v_new)) return OATTN_ERR_ARG;
+    PrefillArgs a;
+    if ((rc = check_rope(fuse, rope, head_dim, a.rope)) != OATTN_OK) return rc;
+    const size_t need = oattn_prefill_workspace_bytes(n_head, n_kv, head_dim, batch);
+    if (!workspace || ((uintptr_t)workspace & 255) || workspace_bytes < need) return OATTN_ERR_WORKSPACE;
+    a.q = q; a.k_new = k_new; a.v_new = v_new; a.kc = kc; a.vc = vc; a.out = out;
+    a.q16 = reinterpret_cast<__half*>(workspace);
+    a.n_head = n_head; a.n_kv = n_kv; a.head_dim = head_dim; a.n_ctx = n_ctx; a.n_past = n_past; a.batch = batch;
+    a.scale = scale; a.fuse = fuse;
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t e = launch_prefill_prologue(a, s, &g_launches);
+    if (e != cudaSuccess) return cuda_fail(e, "prefill prologue launch");
+    if (g_prefill_impl == 0) {
+        e = launch_prefill_tc(a, g_dev[g_cur].sm_count, s, &g_launches);
+        if (e == cudaSuccess) return OATTN_OK;
+        if (e != cudaErrorNotSupported) return cuda_fail(e, "prefill (tcgen05) launch");
+    }
+    e = launch_prefill_mma(a, s, &g_launches);
+    return e == cudaSuccess ? OATTN_OK : cuda_fail(e, "prefill (mma) launch");
+}
+
+int oattn_set_prefill_impl(int impl) {
+    if (impl != 0 && impl != 1) return OATTN_ERR_ARG;
+    g_prefill_impl = impl;
+    return OATTN_OK;
+}
+
+int oattn_set_decode_min_tiles(int tiles) {
+    if (tiles < 1 || tiles > 1024) return OATTN_ERR_ARG;
+    g_decode_min_tiles = tiles;
+    return OATTN_OK;
+}
+
+int oattn_profile_enable(int max_records) {
+    if (max_records < 0 || max_records > (1 << 16)) return OATTN_ERR_ARG;
+    if (g_prof_ev) {
+        for (int i = 0; i < 2 * g_prof_cap; ++i) cudaEventDestroy(g_prof_ev[i]);
+        delete[] g_prof_ev;
+        g_prof_ev = nullptr;
+    }
+    g_prof_cap = g_prof_n = 0;
+    if (max_records == 0) return OATTN_OK;
+    g_prof_ev = new cudaEvent_t[2 * max_records];
+    for (int i = 0; i < 2 * max_records; ++i) {
+        cudaError_t e = cudaEventCreate(&g_prof_ev[i]);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaEventCreate");
+    }
+    g_prof_cap = max_records;
+    return OATTN_OK;
+}
+
+int oattn_profile_collect(float* ms, int capacity, int* n_written) {
+    if (!ms || !n_written || capacity < 0) return OATTN_ERR_ARG;
+    int n = g_prof_n < capacity ? g_prof_n : capacity;
+    for (int i = 0; i < n; ++i) {
+        cudaError_t e = cudaEventSynchronize(g_prof_ev[2 * i + 1]);
+        if (e == cudaSuccess) e = cudaEventElapsedTime(&ms[i], g_prof_ev[2 * i], g_prof_ev[2 * i + 1]);
+        if (e != cudaSuccess) return cuda_fail(e, "profile collect");
+    }
+    *n_written = n;
+    g_prof_n = 0;
+    return OATTN_OK;
+}
+
+unsigned long long oattn_launch_count(void) { return g_launches; }
+
+} // extern "C"

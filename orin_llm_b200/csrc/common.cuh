@@ -1,0 +1,95 @@
+// Shared device helpers of the sm_100a attention kernels.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <math_constants.h>
+#include <stdint.h>
+
+namespace oattn {
+
+constexpr float LOG2E = 1.4426950408889634f;
+
+struct RopeArgs {
+    int rope_type;              // 0 = normal pairs (2i, 2i+1), 1 = neox pairs (i, i + n_rot/2)
+    int n_rot;
+    float theta;
+    const float* freq_factors;  // device, n_rot/2 floats or nullptr
+};
+
+// ---- RoPE arithmetic -----------------------------------------------------------------------
+// Frequency of pair i exactly as the reference's CPU backend evaluates it
+// (src/model_cpu.cpp:182-183, 195-196): exponent -2i/n_rot rounded to fp32, theta^e rounded to
+// fp32, then an fp32 divide by the optional factor.  The power goes through double so that the
+// fp32 result is correctly rounded, which is what the host libm delivers; fast-math __powf
+// (src/kernels.cu:1631) drifts by several ulp and the error is multiplied by the position.
+__device__ __forceinline__ float rope_freq(int pair, int n_rot, float theta, const float* freq_factors) {
+    const float e = (-2.0f * (float)pair) / (float)n_rot;
+    float freq = (float)pow((double)theta, (double)e);
+    if (freq_factors) freq = __fdiv_rn(freq, freq_factors[pair]);
+    return freq;
+}
+
+// cos/sin of pos*freq with the accurate (range-reduced) single-precision routines.
+__device__ __forceinline__ void rope_cs(int pos, float freq, float& c, float& s) {
+    const float ang = __fmul_rn((float)pos, freq);
+    sincosf(ang, &s, &c);
+}
+
+// The two element indices that pair `pair` touches inside a head row.
+__device__ __forceinline__ void rope_pair_index(int rope_type, int pair, int n_rot, int& i0, int& i1) {
+    if (rope_type == 1) { i0 = pair; i1 = pair + n_rot / 2; }
+    else                { i0 = 2 * pair; i1 = 2 * pair + 1; }
+}
+
+// ---- async copy / ldmatrix / mma -----------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+// 16-byte global->shared copy; src_bytes = 0 writes zeros instead (used for rows past the
+// valid length so that never-written cache rows cannot inject NaN into P*V).
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, int src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(src_bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+
+// D(16x8, fp32) += A(16x16, fp16, row) * B(16x8, fp16, col)
+__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                          uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// Byte offset of (row, 16-byte chunk) inside a tile whose rows are ROW_BYTES wide, with the
+// chunk index XOR-ed by the row so that the 8 rows one ldmatrix phase touches fall in 8
+// different bank groups.
+template <int ROW_BYTES>
+__device__ __forceinline__ uint32_t swz(int row, int chunk) {
+    return (uint32_t)(row * ROW_BYTES + ((chunk ^ (row & 7)) << 4));
+}
+
+} // namespace oattn

@@ -1,0 +1,528 @@
+// Single-token decode attention over the fp16 KV cache: split-KV flash decoding.
+//
+// Stands in for flash_attention_decode_mma_k (src/kernels.cu:1107-1345), which walks the whole
+// sequence with one CTA per kv head.  Here the sequence of every kv head is cut into
+// `n_splits` contiguous slices, one CTA each (grid = n_splits x n_kv, about two CTAs per SM), so
+// that every SM streams cache rows.  The grid never depends on the position: each CTA derives
+// its slice from *d_pos, and CTAs whose slice is empty return at once, which keeps the launch
+// replayable from a CUDA graph (src/model_gpu.cu:295-344).
+//
+// Data path of one CTA (4 warps): 64-row K and V tiles are brought to shared memory with 16-byte
+// cp.async copies, three stages deep; rows at or past the valid length are zero-filled by the
+// copy itself.  Warp w owns rows 16w..16w+15 of every tile: S = Q K^T with the (padded to 16)
+// query heads of the group as the M dimension of mma.m16n8k16, online softmax in fp32 with
+// quad shuffles for max and sum, O += P V with V fragments taken by ldmatrix.trans.  The four
+// warps' (m, l, O) are merged through shared memory, and the CTA writes one partial per head.
+// A second small kernel merges the partials of all slices (log-sum-exp combine).
+//
+// Optional fused prologue: RoPE of q, RoPE + fp16 conversion + cache store of the new token's
+// k/v row (rope_*_ind, kv_store_ind of src/model_gpu.cu:277-281).  The CTA whose slice contains
+// the new row stores it and patches it into its own shared-memory tile, so no CTA ever reads a
+// row another CTA is writing.
+#include "attn_internal.h"
+
+namespace oattn {
+
+namespace {
+
+constexpr int kThreads = 128;
+constexpr int kStages = 3;
+
+template <int HD>
+struct DecodeSmem {
+    static constexpr int ROWB = HD * 2;
+    static constexpr int CHUNKS = ROWB / 16;
+    static constexpr int TILE_BYTES = DECODE_TILE * ROWB;
+    static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
+    static constexpr int Q_OFF = kStages * STAGE_BYTES;
+    static constexpr int Q_BYTES = 16 * ROWB;
+    static constexpr int KNEW_OFF = Q_OFF + Q_BYTES;
+    static constexpr int VNEW_OFF = KNEW_OFF + ROWB;
+    static constexpr int CS_OFF = VNEW_OFF + ROWB;        // cos[HD/2], sin[HD/2] fp32
+    static constexpr int TOTAL = CS_OFF + HD * 4;
+    // merge buffers alias the stage area once the pipeline has drained
+    static constexpr int MERGE_O_BYTES = 4 * 16 * HD * 4;
+    static constexpr int MERGE_ML_OFF = MERGE_O_BYTES;
+    static_assert(MERGE_O_BYTES + 4 * 16 * 2 * 4 <= kStages * STAGE_BYTES, "merge area must fit in the stage area");
+};
+
+struct SplitPlan {
+    int n_tiles, tiles_per_split, active;
+};
+
+__host__ __device__ inline SplitPlan plan_splits(int npos, int n_splits, int min_tiles) {
+    SplitPlan s;
+    s.n_tiles = (npos + DECODE_TILE - 1) / DECODE_TILE;
+    int tps = (s.n_tiles + n_splits - 1) / n_splits;
+    if (tps < min_tiles) tps = min_tiles;
+    if (tps < 1) tps = 1;
+    s.tiles_per_split = tps;
+    s.active = (s.n_tiles + tps - 1) / tps;
+    return s;
+}
+
+__device__ __forceinline__ int clamp_len(int v, int n_ctx) { return v < 0 ? 0 : (v > n_ctx ? n_ctx : v); }
+
+// Rotates (optionally) one fp32 head row and writes it as fp16 through `store(elem, value)`.
+template <typename Store>
+__device__ __forceinline__ void rope_row_to_half(const float* src, int hd, bool rotate, const RopeArgs& r,
+                                                 const float* s_cos, const float* s_sin, int lane_id, int lanes,
+                                                 Store store) {
+    const int n_rot = rotate ? r.n_rot : 0;
+    for (int pp = lane_id; pp < hd / 2; pp += lanes) {
+        int i0, i1;
+        float x0, x1;
+        if (pp < n_rot / 2) {
+            rope_pair_index(r.rope_type, pp, n_rot, i0, i1);
+            const float a = src[i0], b = src[i1];
+            const float c = s_cos[pp], s = s_sin[pp];
+            x0 = a * c - b * s;
+            x1 = a * s + b * c;
+        } else {
+            i0 = n_rot + 2 * (pp - n_rot / 2);
+            i1 = i0 + 1;
+            x0 = src[i0];
+            x1 = src[i1];
+        }
+        store(i0, x0);
+        store(i1, x1);
+    }
+}
+
+template <int HD, bool WIDE>
+__global__ void __launch_bounds__(kThreads, 2) decode_split_kernel(const DecodeArgs p) {
+    using L = DecodeSmem<HD>;
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int split = blockIdx.x, kvh = blockIdx.y;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int r = lane >> 2, t = lane & 3;
+    const int G = p.n_head / p.n_kv;
+
+    const int npos = clamp_len(*p.d_pos + p.pos_bias, p.n_ctx);
+    const SplitPlan plan = plan_splits(npos, p.n_splits, p.min_tiles);
+    if (split >= plan.active) return;
+    const int tile0 = split * plan.tiles_per_split;
+    const int tile1 = min(tile0 + plan.tiles_per_split, plan.n_tiles);
+    const int nt = tile1 - tile0;
+
+    const bool append = (p.fuse & 4) != 0;
+    const bool owner = append && split == plan.active - 1;   // this CTA's last tile holds row npos-1
+    const int new_pos = npos - 1;
+    // rows the async copies may read: the new row is not in the cache yet when it is fused
+    const int nload = owner ? new_pos : npos;
+
+    const __half* Kg = reinterpret_cast<const __half*>(p.kc) + (size_t)kvh * p.n_ctx * HD;
+    const __half* Vg = reinterpret_cast<const __half*>(p.vc) + (size_t)kvh * p.n_ctx * HD;
+    const uint32_t smem_base = smem_u32(smem);
+
+    auto load_tile = [&](int rel, int stage) {
+        const int row0 = (tile0 + rel) * DECODE_TILE;
+        const uint32_t sb = smem_base + stage * L::STAGE_BYTES;
+        constexpr int PER_MAT = DECODE_TILE * L::CHUNKS;
+#pragma unroll
+        for (int i = 0; i < 2 * PER_MAT / kThreads; ++i) {
+            const int idx = tid + i * kThreads;
+            const int which = idx / PER_MAT;
+            const int rem = idx % PER_MAT;
+            const int row = rem / L::CHUNKS, chunk = rem % L::CHUNKS;
+            const int grow = row0 + row;
+            const bool ok = grow < nload;
+            const __half* src = (which ? Vg : Kg) + (size_t)(ok ? grow : 0) * HD + chunk * 8;
+            cp_async_16(sb + which * L::TILE_BYTES + swz<L::ROWB>(row, chunk), src, ok ? 16 : 0);
+        }
+    };
+
+#pragma unroll
+    for (int s = 0; s < kStages - 1; ++s) {
+        if (s < nt) load_tile(s, s);
+        cp_async_commit();
+    }
+
+    // ---- prologue: RoPE table, Q -> fp16 fragments, new K/V row ------------------------------
+    float* s_cos = reinterpret_cast<float*>(smem + L::CS_OFF);
+    float* s_sin = s_cos + HD / 2;
+    const bool rope_q = (p.fuse & 1) != 0, rope_k = (p.fuse & 2) != 0;
+    if (rope_q || (rope_k && owner)) {
+        for (int i = tid; i < p.rope.n_rot / 2; i += kThreads) {
+            const float f = rope_freq(i, p.rope.n_rot, p.rope.theta, p.rope.freq_factors);
+            rope_cs(new_pos, f, s_cos[i], s_sin[i]);
+        }
+        __syncthreads();
+    }
+    {
+        // rows >= G of the 16-row query tile are zero
+        for (int i = tid; i < 16 * L::CHUNKS; i += kThreads) {
+            const int row = i / L::CHUNKS;
+            if (row >= G) *reinterpret_cast<uint4*>(smem + L::Q_OFF + swz<L::ROWB>(row, i % L::CHUNKS)) = make_uint4(0, 0, 0, 0);
+        }
+        // one warp per head row, round-robin
+        for (int h = warp; h < G; h += kThreads / 32) {
+            const float* src = p.q + (size_t)(kvh * G + h) * HD;
+            rope_row_to_half(src, HD, rope_q, p.rope, s_cos, s_sin, lane, 32, [&](int e, float v) {
+                *reinterpret_cast<__half*>(smem + L::Q_OFF + swz<L::ROWB>(h, e >> 3) + (e & 7) * 2) = __float2half_rn(v);
+            });
+        }
+        if (owner) {
+            __half* s_k = reinterpret_cast<__half*>(smem + L::KNEW_OFF);
+            __half* s_v = reinterpret_cast<__half*>(smem + L::VNEW_OFF);
+            if (warp == 0) {
+                rope_row_to_half(p.k_new + (size_t)kvh * HD, HD, rope_k, p.rope, s_cos, s_sin, lane, 32,
+                                 [&](int e, float v) { s_k[e] = __float2half_rn(v); });
+            } else if (warp == 1) {
+                for (int e = lane; e < HD; e += 32) s_v[e] = __float2half_rn(p.v_new[(size_t)kvh * HD + e]);
+            }
+        }
+    }
+    __syncthreads();
+    if (owner && tid < 2 * L::CHUNKS) {
+        // store the new row into the cache (kv_store_k, src/kernels.cu:1660-1678)
+        const int which = tid / L::CHUNKS, chunk = tid % L::CHUNKS;
+        const uint4 v = *reinterpret_cast<const uint4*>(smem + (which ? L::VNEW_OFF : L::KNEW_OFF) + chunk * 16);
+        __half* dst = const_cast<__half*>(which ? Vg : Kg) + (size_t)new_pos * HD + chunk * 8;
+        *reinterpret_cast<uint4*>(dst) = v;
+    }
+
+    uint32_t qa[HD / 16][4];
+#pragma unroll
+    for (int kk = 0; kk < HD / 16; ++kk) {
+        const int row = (lane & 7) + 8 * ((lane >> 3) & 1);
+        const int chunk = 2 * kk + (lane >> 4);
+        ldmatrix_x4(smem_base + L::Q_OFF + swz<L::ROWB>(row, chunk), qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3]);
+        if (!WIDE) { qa[kk][1] = 0u; qa[kk][3] = 0u; }
+    }
+
+    constexpr int NH = WIDE ? 2 : 1;           // row halves that carry real heads
+    float o[HD / 8][4];
+#pragma unroll
+    for (int j = 0; j < HD / 8; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
+    float m_run[2] = {-CUDART_INF_F, -CUDART_INF_F};
+    float l_run[2] = {0.f, 0.f};
+    const float c = p.scale * LOG2E;
+    const int wr0 = warp * 16;
+
+    for (int it = 0; it < nt; ++it) {
+        cp_async_wait<kStages - 2>();
+        __syncthreads();
+        {
+            const int nxt = it + kStages - 1;
+            if (nxt < nt) load_tile(nxt, nxt % kStages);
+            cp_async_commit();
+        }
+        const int stage = it % kStages;
+        const int row0 = (tile0 + it) * DECODE_TILE;
+        const uint32_t sK = smem_base + stage * L::STAGE_BYTES;
+        const uint32_t sV = sK + L::TILE_BYTES;
+
+        if (owner && it == nt - 1) {
+            // patch the new token's row into this CTA's copy of the tile
+            const int prow = new_pos - row0;
+            if (tid < 2 * L::CHUNKS) {
+                const int which = tid / L::CHUNKS, chunk = tid % L::CHUNKS;
+                const uint4 v = *reinterpret_cast<const uint4*>(smem + (which ? L::VNEW_OFF : L::KNEW_OFF) + chunk * 16);
+                *reinterpret_cast<uint4*>(smem + stage * L::STAGE_BYTES + which * L::TILE_BYTES + swz<L::ROWB>(prow, chunk)) = v;
+            }
+            __syncthreads();
+        }
+        if (row0 + wr0 >= npos) continue;   // this warp's 16 rows are all past the end (warp-uniform)
+
+        // ---- S = Q K^T for 16 rows: two 8-row n-tiles ----------------------------------------
+        float s[2][4];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f; }
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+            uint32_t b0, b1, b2, b3;
+            const int row = wr0 + 8 * (lane >> 4) + (lane & 7);
+            const int chunk = 2 * kk + ((lane >> 3) & 1);
+            ldmatrix_x4(sK + swz<L::ROWB>(row, chunk), b0, b1, b2, b3);
+            mma_16816(s[0], qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3], b0, b1);
+            mma_16816(s[1], qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3], b2, b3);
+        }
+        if (row0 + DECODE_TILE > npos) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    if (row0 + wr0 + 8 * j + 2 * t + (e & 1) >= npos) s[j][e] = -CUDART_INF_F;
+        }
+
+        // ---- online softmax ------------------------------------------------------------------
+        float alpha[2] = {1.f, 1.f};
+#pragma unroll
+        for (int hh = 0; hh < NH; ++hh) {
+            float mx = fmaxf(fmaxf(s[0][2 * hh], s[0][2 * hh + 1]), fmaxf(s[1][2 * hh], s[1][2 * hh + 1]));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            const float m_new = fmaxf(m_run[hh], mx);
+            const float m_safe = (m_new == -CUDART_INF_F) ? 0.f : m_new;
+            alpha[hh] = fast_exp2((m_run[hh] - m_safe) * c);
+            const float mc = m_safe * c;
+            float sum = 0.f;
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                s[j][2 * hh] = fast_exp2(fmaf(s[j][2 * hh], c, -mc));
+                s[j][2 * hh + 1] = fast_exp2(fmaf(s[j][2 * hh + 1], c, -mc));
+                sum += s[j][2 * hh] + s[j][2 * hh + 1];
+            }
+            l_run[hh] = l_run[hh] * alpha[hh] + sum;
+            m_run[hh] = m_new;
+        }
+        const bool rescale = WIDE ? (alpha[0] != 1.f || alpha[1] != 1.f) : (alpha[0] != 1.f);
+        if (__any_sync(0xffffffffu, rescale)) {
+#pragma unroll
+            for (int j = 0; j < HD / 8; ++j) {
+                o[j][0] *= alpha[0];
+                o[j][1] *= alpha[0];
+                if (WIDE) { o[j][2] *= alpha[1]; o[j][3] *= alpha[1]; }
+            }
+        }
+        const uint32_t pa0 = pack_half2(s[0][0], s[0][1]);
+        const uint32_t pa2 = pack_half2(s[1][0], s[1][1]);
+        const uint32_t pa1 = WIDE ? pack_half2(s[0][2], s[0][3]) : 0u;
+        const uint32_t pa3 = WIDE ? pack_half2(s[1][2], s[1][3]) : 0u;
+
+        // ---- O += P V ------------------------------------------------------------------------
+#pragma unroll
+        for (int jp = 0; jp < HD / 16; ++jp) {
+            uint32_t b0, b1, b2, b3;
+            const int row = wr0 + (lane & 7) + 8 * ((lane >> 3) & 1);
+            const int chunk = 2 * jp + (lane >> 4);
+            ldmatrix_x4_trans(sV + swz<L::ROWB>(row, chunk), b0, b1, b2, b3);
+            mma_16816(o[2 * jp], pa0, pa1, pa2, pa3, b0, b1);
+            mma_16816(o[2 * jp + 1], pa0, pa1, pa2, pa3, b2, b3);
+        }
+    }
+
+    // ---- merge the four warps ------------------------------------------------------------------
+    cp_async_wait<0>();
+    __syncthreads();
+    float* mO = reinterpret_cast<float*>(smem);                        // [4][16][HD]
+    float* mML = reinterpret_cast<float*>(smem + L::MERGE_ML_OFF);     // [4][16][2]
+#pragma unroll
+    for (int hh = 0; hh < NH; ++hh) {
+        float l = l_run[hh];
+        l += __shfl_xor_sync(0xffffffffu, l, 1);
+        l += __shfl_xor_sync(0xffffffffu, l, 2);
+        const int row = r + 8 * hh;
+        if (t == 0) {
+            mML[(warp * 16 + row) * 2 + 0] = m_run[hh];
+            mML[(warp * 16 + row) * 2 + 1] = l;
+        }
+#pragma unroll
+        for (int j = 0; j < HD / 8; ++j) {
+            float2 v = make_float2(o[j][2 * hh], o[j][2 * hh + 1]);
+            *reinterpret_cast<float2*>(&mO[(warp * 16 + row) * HD + 8 * j + 2 * t]) = v;
+        }
+    }
+    __syncthreads();
+    const bool direct = (plan.active == 1) && !p.emit_partial;
+    for (int idx = tid; idx < G * HD; idx += kThreads) {
+        const int row = idx / HD, d = idx % HD;
+        float M = -CUDART_INF_F;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, mML[(w * 16 + row) * 2]);
+        float Lsum = 0.f, O = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float mw = mML[(w * 16 + row) * 2];
+            const float wgt = (mw == -CUDART_INF_F) ? 0.f : fast_exp2((mw - M) * c);
+            Lsum += wgt * mML[(w * 16 + row) * 2 + 1];
+            O += wgt * mO[(w * 16 + row) * HD + d];
+        }
+        const int head = kvh * G + row;
+        if (direct) {
+            p.out[(size_t)head * HD + d] = O / Lsum;
+        } else {
+            p.ws_o[((size_t)head * p.n_splits + split) * HD + d] = O;
+            if (d == 0) {
+                p.ws_ml[((size_t)head * p.n_splits + split) * 2 + 0] = M * p.scale;
+                p.ws_ml[((size_t)head * p.n_splits + split) * 2 + 1] = Lsum;
+            }
+        }
+    }
+}
+
+// ---- log-sum-exp combine -----------------------------------------------------------------------
+// One CTA per head, 8 warps.  Part s of head h: O at o_base + h*o_hs + s*o_ss (hd floats), (m, l)
+// at ml_base + h*ml_hs + s*ml_ss.  n_parts < 0: derive the number of parts from *d_pos with the
+// same plan as the split kernel (and do nothing when that kernel already wrote the result).
+struct CombineArgs {
+    const float* o_base;
+    const float* ml_base;
+    long long o_hs, o_ss, ml_hs, ml_ss;
+    float* out;
+    int head_dim;
+    int n_parts;
+    const int* d_pos;
+    int pos_bias, n_ctx, n_splits, min_tiles;
+    int emit_partial;
+};
+
+constexpr int kCombineThreads = 256;
+
+__global__ void __launch_bounds__(kCombineThreads) combine_kernel(const CombineArgs p) {
+    __shared__ float s_w[DECODE_MAX_SPLITS];
+    __shared__ float s_red[kCombineThreads / 32];
+    __shared__ float4 s_acc[kCombineThreads / 32][32];
+    const int h = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int hd = p.head_dim;
+
+    int n = p.n_parts;
+    if (n < 0) {
+        const int npos = clamp_len(*p.d_pos + p.pos_bias, p.n_ctx);
+        const SplitPlan plan = plan_splits(npos, p.n_splits, p.min_tiles);
+        n = plan.active;
+        if (n == 1 && !p.emit_partial) return;   // the split kernel wrote the output itself
+    }
+    const float* ml = p.ml_base + (size_t)h * p.ml_hs;
+    const float* ob = p.o_base + (size_t)h * p.o_hs;
+
+    // M = max m
+    float mx = -CUDART_INF_F;
+    for (int s = tid; s < n; s += kCombineThreads) mx = fmaxf(mx, ml[(size_t)s * p.ml_ss]);
+#pragma unroll
+    for (int off = 16; off; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+    if (lane == 0) s_red[warp] = mx;
+    __syncthreads();
+    float M = -CUDART_INF_F;
+#pragma unroll
+    for (int w = 0; w < kCombineThreads / 32; ++w) M = fmaxf(M, s_red[w]);
+    __syncthreads();
+
+    // weights and L
+    float lsum = 0.f;
+    for (int s = tid; s < n; s += kCombineThreads) {
+        const float m = ml[(size_t)s * p.ml_ss];
+        const float w = (m == -CUDART_INF_F) ? 0.f : __expf(m - M);
+        s_w[s] = w;
+        lsum += w * ml[(size_t)s * p.ml_ss + 1];
+    }
+#pragma unroll
+    for (int off = 16; off; off >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, off);
+    if (lane == 0) s_red[warp] = lsum;
+    __syncthreads();
+    float Lsum = 0.f;
+#pragma unroll
+    for (int w = 0; w < kCombineThreads / 32; ++w) Lsum += s_red[w];
+
+    // O: warp w takes parts w, w+8, ...; lane takes 4 consecutive dims
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (lane * 4 < hd) {
+        for (int s = warp; s < n; s += kCombineThreads / 32) {
+            const float w = s_w[s];
+            const float4 v = *reinterpret_cast<const float4*>(ob + (size_t)s * p.o_ss + lane * 4);
+            acc.x = fmaf(w, v.x, acc.x);
+            acc.y = fmaf(w, v.y, acc.y);
+            acc.z = fmaf(w, v.z, acc.z);
+            acc.w = fmaf(w, v.w, acc.w);
+        }
+    }
+    s_acc[warp][lane] = acc;
+    __syncthreads();
+    if (tid < hd) {
+        const int l4 = tid >> 2, e = tid & 3;
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < kCombineThreads / 32; ++w) {
+            const float4 a = s_acc[w][l4];
+            v += (e == 0) ? a.x : (e == 1) ? a.y : (e == 2) ? a.z : a.w;
+        }
+        if (p.emit_partial) {
+            float* rec = p.out + (size_t)h * (hd + PART_PAD);
+            rec[tid] = v;
+            if (tid == 0) {
+                rec[hd + 0] = M;
+                rec[hd + 1] = Lsum;
+                rec[hd + 2] = 0.f;
+                rec[hd + 3] = 0.f;
+            }
+        } else {
+            p.out[(size_t)h * hd + tid] = v / Lsum;
+        }
+    }
+}
+
+template <int HD, bool WIDE>
+cudaError_t launch_split(const DecodeArgs& a, cudaStream_t stream) {
+    dim3 grid(a.n_splits, a.n_kv);
+    decode_split_kernel<HD, WIDE><<<grid, kThreads, DecodeSmem<HD>::TOTAL, stream>>>(a);
+    return cudaGetLastError();
+}
+
+} // namespace
+
+int decode_num_splits(int n_kv, int sm_count) {
+    int s = (2 * sm_count) / (n_kv > 0 ? n_kv : 1);
+    if (s < 1) s = 1;
+    if (s > DECODE_MAX_SPLITS) s = DECODE_MAX_SPLITS;
+    return s;
+}
+
+cudaError_t decode_set_attributes() {
+    cudaError_t e;
+    e = cudaFuncSetAttribute(decode_split_kernel<128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DecodeSmem<128>::TOTAL);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(decode_split_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DecodeSmem<128>::TOTAL);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(decode_split_kernel<64, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DecodeSmem<64>::TOTAL);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(decode_split_kernel<64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DecodeSmem<64>::TOTAL);
+    return e;
+}
+
+cudaError_t launch_decode(const DecodeArgs& a, cudaStream_t stream, unsigned long long* launches,
+                          cudaEvent_t ev_start, cudaEvent_t ev_stop) {
+    const int G = a.n_head / a.n_kv;
+    const bool wide = G > 8;
+    cudaError_t e;
+    if (ev_start) cudaEventRecord(ev_start, stream);
+    if (a.head_dim == 128) e = wide ? launch_split<128, true>(a, stream) : launch_split<128, false>(a, stream);
+    else                   e = wide ? launch_split<64, true>(a, stream) : launch_split<64, false>(a, stream);
+    if (ev_stop) cudaEventRecord(ev_stop, stream);
+    if (e != cudaSuccess) return e;
+    CombineArgs c;
+    c.o_base = a.ws_o;
+    c.ml_base = a.ws_ml;
+    c.o_hs = (long long)a.n_splits * a.head_dim;
+    c.o_ss = a.head_dim;
+    c.ml_hs = (long long)a.n_splits * 2;
+    c.ml_ss = 2;
+    c.out = a.out;
+    c.head_dim = a.head_dim;
+    c.n_parts = -1;
+    c.d_pos = a.d_pos;
+    c.pos_bias = a.pos_bias;
+    c.n_ctx = a.n_ctx;
+    c.n_splits = a.n_splits;
+    c.min_tiles = a.min_tiles;
+    c.emit_partial = a.emit_partial;
+    combine_kernel<<<a.n_head, kCombineThreads, 0, stream>>>(c);
+    if (launches) *launches += 2;
+    return cudaGetLastError();
+}
+
+cudaError_t launch_combine_records(const float* parts, int n_parts, float* out, int n_head, int head_dim,
+                                   cudaStream_t stream, unsigned long long* launches) {
+    CombineArgs c;
+    const long long rec = head_dim + PART_PAD;
+    c.o_base = parts;
+    c.ml_base = parts + head_dim;
+    c.o_hs = rec;
+    c.o_ss = rec * n_head;
+    c.ml_hs = rec;
+    c.ml_ss = rec * n_head;
+    c.out = out;
+    c.head_dim = head_dim;
+    c.n_parts = n_parts;
+    c.d_pos = nullptr;
+    c.pos_bias = 0;
+    c.n_ctx = 0;
+    c.n_splits = 0;
+    c.min_tiles = 1;
+    c.emit_partial = 0;
+    combine_kernel<<<n_head, kCombineThreads, 0, stream>>>(c);
+    if (launches) *launches += 1;
+    return cudaGetLastError();
+}
+
+} // namespace oattn

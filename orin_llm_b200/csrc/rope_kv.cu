@@ -1,0 +1,191 @@
+// RoPE, KV-cache store, KV-cache shift, and the prefill prologue (RoPE + fp16 conversion of a
+// chunk's q, k, v in one launch).
+#include "attn_internal.h"
+
+namespace oattn {
+
+namespace {
+
+// ---- standalone RoPE: rope_neox_k / rope_normal_k (src/kernels.cu:1622-1657) --------------------
+// One CTA rotates ROWS_PER_CTA consecutive rows; the n_rot/2 frequencies are computed once per
+// CTA.  Position of row r: *d_pos when given, else n_past + r/heads (src/kernels.cu:1627-1629).
+constexpr int kRopeThreads = 256;
+constexpr int kRopeRows = 32;
+
+__global__ void __launch_bounds__(kRopeThreads) rope_kernel(float* x, int rows, int head_dim, RopeArgs r, int n_past,
+                                                            int heads, const int* d_pos) {
+    __shared__ float s_freq[128];
+    const int half = r.n_rot / 2;
+    for (int i = threadIdx.x; i < half; i += kRopeThreads) s_freq[i] = rope_freq(i, r.n_rot, r.theta, r.freq_factors);
+    __syncthreads();
+    const int row0 = blockIdx.x * kRopeRows;
+    const int nrow = min(kRopeRows, rows - row0);
+    const int pos_ind = d_pos ? *d_pos : 0;
+    for (int idx = threadIdx.x; idx < nrow * half; idx += kRopeThreads) {
+        const int row = row0 + idx / half, pair = idx % half;
+        const int pos = d_pos ? pos_ind : n_past + row / heads;
+        float c, s;
+        rope_cs(pos, s_freq[pair], c, s);
+        int i0, i1;
+        rope_pair_index(r.rope_type, pair, r.n_rot, i0, i1);
+        float* xr = x + (size_t)row * head_dim;
+        const float x0 = xr[i0], x1 = xr[i1];
+        xr[i0] = x0 * c - x1 * s;
+        xr[i1] = x0 * s + x1 * c;
+    }
+}
+
+// ---- standalone KV store: kv_store_k (src/kernels.cu:1660-1678) ---------------------------------
+// One CTA per (token, head) row; fp32 -> fp16 round-to-nearest, cache layout [head][pos][hd].
+__global__ void __launch_bounds__(128) kv_store_kernel(uint16_t* kc, uint16_t* vc, const float* k, const float* v,
+                                                       int heads, int head_dim, int n_ctx, int pos_base,
+                                                       const int* d_pos) {
+    const int head = blockIdx.x % heads, b = blockIdx.x / heads;
+    const int pos = d_pos ? *d_pos : pos_base + b;
+    if (pos < 0 || pos >= n_ctx) return;
+    const size_t src = (size_t)blockIdx.x * head_dim;
+    const size_t dst = ((size_t)head * n_ctx + pos) * head_dim;
+    for (int i = threadIdx.x; i < head_dim; i += blockDim.x) {
+        kc[dst + i] = __half_as_ushort(__float2half_rn(k[src + i]));
+        vc[dst + i] = __half_as_ushort(__float2half_rn(v[src + i]));
+    }
+}
+
+// ---- KV shift: kv_shift_k (src/kernels.cu:1682-1700) --------------------------------------------
+// The reference moves one element per thread per position in a serial loop.  A row only ever
+// moves to the same columns of a lower row, so 32-byte column slices of one (layer, head) are
+// independent: grid = (row_bytes/32, n_kv, n_layer), each CTA slides its slice 256 rows at a time
+// (read, barrier, write), then zeroes the tail.  K and V are handled by the same CTA.
+constexpr int kShiftThreads = 256;
+
+__global__ void __launch_bounds__(kShiftThreads) kv_shift_kernel(uint16_t* kc, uint16_t* vc, int n_kv, int head_dim,
+                                                                 int n_ctx, int n_keep, int shift) {
+    const int col = blockIdx.x, head = blockIdx.y, layer = blockIdx.z;
+    const size_t row_bytes = (size_t)head_dim * 2;
+    const size_t base = ((size_t)layer * n_kv + head) * n_ctx * row_bytes + (size_t)col * 32;
+    uint8_t* kb = reinterpret_cast<uint8_t*>(kc) + base;
+    uint8_t* vb = reinterpret_cast<uint8_t*>(vc) + base;
+    const int last = n_ctx - shift;   // first row of the zeroed tail
+    for (int row0 = n_keep; row0 < last; row0 += kShiftThreads) {
+        const int row = row0 + threadIdx.x;
+        uint4 k0, k1, v0, v1;
+        const bool ok = row < last;
+        if (ok) {
+            const uint4* ks = reinterpret_cast<const uint4*>(kb + (size_t)(row + shift) * row_bytes);
+            const uint4* vs = reinterpret_cast<const uint4*>(vb + (size_t)(row + shift) * row_bytes);
+            k0 = ks[0]; k1 = ks[1]; v0 = vs[0]; v1 = vs[1];
+        }
+        __syncthreads();
+        if (ok) {
+            uint4* kd = reinterpret_cast<uint4*>(kb + (size_t)row * row_bytes);
+            uint4* vd = reinterpret_cast<uint4*>(vb + (size_t)row * row_bytes);
+            kd[0] = k0; kd[1] = k1; vd[0] = v0; vd[1] = v1;
+        }
+    }
+    const uint4 z = make_uint4(0, 0, 0, 0);
+    for (int row = max(last, 0) + threadIdx.x; row < n_ctx; row += kShiftThreads) {
+        uint4* kd = reinterpret_cast<uint4*>(kb + (size_t)row * row_bytes);
+        uint4* vd = reinterpret_cast<uint4*>(vb + (size_t)row * row_bytes);
+        kd[0] = z; kd[1] = z; vd[0] = z; vd[1] = z;
+    }
+}
+
+// ---- prefill prologue ---------------------------------------------------------------------------
+// One CTA per chunk token b (position n_past + b).  cos/sin of the n_rot/2 angles are computed
+// once and reused by all query heads and kv heads of the token:
+//   q  -> [RoPE] -> * scale*log2(e) -> fp16 -> q16[b][head][hd]
+//   k  -> [RoPE] -> fp16 -> kc[head][n_past+b][hd]         (when appending)
+//   v  ->           fp16 -> vc[head][n_past+b][hd]
+// This is rope_*_batch(q), rope_*_batch(k), kv_store_batch of src/model_gpu.cu:379-383 plus the
+// fp16 conversion of Q that the reference does inside its attention kernel (src/kernels.cu:1393-1410).
+constexpr int kPrologueThreads = 256;
+
+__global__ void __launch_bounds__(kPrologueThreads) prefill_prologue_kernel(const PrefillArgs p) {
+    __shared__ float s_cos[64], s_sin[64];
+    const int b = blockIdx.x, tid = threadIdx.x;
+    const int hd = p.head_dim, pos = p.n_past + b;
+    const bool rope_q = (p.fuse & 1) != 0, rope_k = (p.fuse & 2) != 0, append = (p.fuse & 4) != 0;
+    if (rope_q || rope_k) {
+        for (int i = tid; i < p.rope.n_rot / 2; i += kPrologueThreads) {
+            const float f = rope_freq(i, p.rope.n_rot, p.rope.theta, p.rope.freq_factors);
+            rope_cs(pos, f, s_cos[i], s_sin[i]);
+        }
+        __syncthreads();
+    }
+    const float qs = p.scale * LOG2E;
+    const int half = hd / 2;
+    const int q_items = p.n_head * half;
+    const int k_items = append ? p.n_kv * half : 0;
+    for (int idx = tid; idx < q_items + k_items; idx += kPrologueThreads) {
+        const bool is_q = idx < q_items;
+        const int li = is_q ? idx : idx - q_items;
+        const int head = li / half, pp = li % half;
+        const bool rot = is_q ? rope_q : rope_k;
+        const int n_rot = rot ? p.rope.n_rot : 0;
+        const float* src = is_q ? p.q + ((size_t)b * p.n_head + head) * hd : p.k_new + ((size_t)b * p.n_kv + head) * hd;
+        int i0, i1;
+        float x0, x1;
+        if (pp < n_rot / 2) {
+            rope_pair_index(p.rope.rope_type, pp, n_rot, i0, i1);
+            const float a = src[i0], c2 = src[i1];
+            x0 = a * s_cos[pp] - c2 * s_sin[pp];
+            x1 = a * s_sin[pp] + c2 * s_cos[pp];
+        } else {
+            i0 = n_rot + 2 * (pp - n_rot / 2);
+            i1 = i0 + 1;
+            x0 = src[i0];
+            x1 = src[i1];
+        }
+        if (is_q) {
+            __half* dst = p.q16 + ((size_t)b * p.n_head + head) * hd;
+            dst[i0] = __float2half_rn(x0 * qs);
+            dst[i1] = __float2half_rn(x1 * qs);
+        } else {
+            uint16_t* dst = p.kc + ((size_t)head * p.n_ctx + pos) * hd;
+            dst[i0] = __half_as_ushort(__float2half_rn(x0));
+            dst[i1] = __half_as_ushort(__float2half_rn(x1));
+        }
+    }
+    if (append) {
+        for (int idx = tid; idx < p.n_kv * hd; idx += kPrologueThreads) {
+            const int head = idx / hd, i = idx % hd;
+            p.vc[((size_t)head * p.n_ctx + pos) * hd + i] =
+                __half_as_ushort(__float2half_rn(p.v_new[((size_t)b * p.n_kv + head) * hd + i]));
+        }
+    }
+}
+
+} // namespace
+
+cudaError_t launch_rope(float* x, int rows, int head_dim, const RopeArgs& r, int n_past, int heads,
+                        const int* d_pos, cudaStream_t stream, unsigned long long* launches) {
+    if (rows <= 0) return cudaSuccess;
+    const int grid = (rows + kRopeRows - 1) / kRopeRows;
+    rope_kernel<<<grid, kRopeThreads, 0, stream>>>(x, rows, head_dim, r, n_past, heads > 0 ? heads : 1, d_pos);
+    if (launches) *launches += 1;
+    return cudaGetLastError();
+}
+
+cudaError_t launch_kv_store(uint16_t* kc, uint16_t* vc, const float* k, const float* v, int heads, int head_dim,
+                            int n_ctx, int pos_base, int batch, const int* d_pos, cudaStream_t stream,
+                            unsigned long long* launches) {
+    kv_store_kernel<<<batch * heads, 128, 0, stream>>>(kc, vc, k, v, heads, head_dim, n_ctx, pos_base, d_pos);
+    if (launches) *launches += 1;
+    return cudaGetLastError();
+}
+
+cudaError_t launch_kv_shift(uint16_t* kc, uint16_t* vc, int n_layer, int n_kv, int head_dim, int n_ctx, int n_keep,
+                            int shift, cudaStream_t stream, unsigned long long* launches) {
+    dim3 grid(head_dim * 2 / 32, n_kv, n_layer);
+    kv_shift_kernel<<<grid, kShiftThreads, 0, stream>>>(kc, vc, n_kv, head_dim, n_ctx, n_keep, shift);
+    if (launches) *launches += 1;
+    return cudaGetLastError();
+}
+
+cudaError_t launch_prefill_prologue(const PrefillArgs& a, cudaStream_t stream, unsigned long long* launches) {
+    prefill_prologue_kernel<<<a.batch, kPrologueThreads, 0, stream>>>(a);
+    if (launches) *launches += 1;
+    return cudaGetLastError();
+}
+
+} // namespace oattn

@@ -1,0 +1,74 @@
+"""Split-KV decode attention across the GPUs of one node.
+
+The reference is single-device; this is the one multi-GPU step the path has.  The KV sequence of
+every kv head is cut into `world` contiguous slices, rank r keeping rows
+[bounds[r], bounds[r+1]) in its own HBM.  A decode step is
+    local partial (m, l, O) over the slice      oattn_decode_partial
+    all-gather of the world records             NCCL over NVLink (torch.distributed)
+    log-sum-exp combine on every rank           oattn_combine
+The record of one rank is [n_head][head_dim + 4] fp32 = {O, m, l, 0, 0}: 8448 bytes for 16 heads
+of 128, so the exchange is latency-bound; it is issued on the compute stream and is
+graph-capturable together with the two kernels.
+
+The slicing and the gather are plain host logic that also runs on CPU tensors with the gloo
+backend (that is how they are tested without GPUs); the kernels are reached only through
+orin_llm_b200.ops and have no CPU counterpart.
+"""
+import torch
+import torch.distributed as dist
+
+PART_PAD = 4
+TILE = 64   # slices start on a multiple of the decode kernel's tile
+
+
+def slice_bounds(n_rows, world):
+    """Contiguous, tile-aligned, near-equal slices of [0, n_rows): returns world+1 boundaries."""
+    n_tiles = (n_rows + TILE - 1) // TILE
+    bounds = [min(n_rows, ((r * n_tiles) // world) * TILE) for r in range(world)]
+    bounds.append(n_rows)
+    return bounds
+
+
+def gather_records(local, world_buf, group=None):
+    """All-gather one record per rank.  local: [n_head][hd+4]; world_buf: [world][n_head][hd+4]."""
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    if world == 1:
+        world_buf[0].copy_(local)
+        return world_buf
+    if local.is_cuda:
+        dist.all_gather_into_tensor(world_buf, local, group=group)
+    else:   # gloo: list form
+        chunks = [world_buf[r] for r in range(world)]
+        dist.all_gather(chunks, local, group=group)
+    return world_buf
+
+
+class SplitKVDecoder:
+    """Decode attention over a KV sequence that is sharded by rows across the ranks of `group`."""
+
+    def __init__(self, n_head, n_kv, head_dim, group=None):
+        from . import ops
+        self.ops = ops
+        self.n_head, self.n_kv, self.head_dim = n_head, n_kv, head_dim
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        rec = head_dim + PART_PAD
+        self.local = torch.zeros(n_head, rec, device="cuda")
+        self.parts = torch.zeros(self.world, n_head, rec, device="cuda")
+        self.workspace = ops.decode_workspace(n_head, n_kv, head_dim)
+
+    def decode(self, q, kc_local, vc_local, n_ctx_local, d_len_local, scale, out):
+        """q [n_head][hd] (replicated); kc/vc_local [n_kv][n_ctx_local][hd] fp16 holding this rank's rows;
+        d_len_local: device int32 scalar, valid local rows.  out [n_head][hd] is written on every rank."""
+        o = self.ops
+        if self.world == 1:
+            # no exchange: the split kernel's partials go straight through the in-launch combine
+            o.attn_decode_partial(q, kc_local, vc_local, self.parts[0], self.n_head, self.n_kv, self.head_dim,
+                                  n_ctx_local, d_len_local, scale, self.workspace)
+        else:
+            o.attn_decode_partial(q, kc_local, vc_local, self.local, self.n_head, self.n_kv, self.head_dim,
+                                  n_ctx_local, d_len_local, scale, self.workspace)
+            gather_records(self.local, self.parts, self.group)
+        o.attn_combine(self.parts, self.world, out, self.n_head, self.head_dim)
+        return out

@@ -1,0 +1,216 @@
+"""Host-side mirror of the reference's kernel wrappers for the attention path.
+
+Function names, argument order and meaning follow `namespace llm::cuda` in the reference
+(src/kernels.h:53-81); tensors are torch CUDA tensors where the reference takes raw device
+pointers.  Everything is forwarded to the C ABI (include/orin_attn_b200.h) through ctypes --
+torch is used only for device memory and streams.  There is no CPU implementation here.
+"""
+import ctypes
+import math
+
+import torch
+
+from . import capi
+from .capi import FUSE_ALL, FUSE_NONE, ROPE_NEOX, ROPE_NORMAL, PART_PAD  # noqa: F401
+
+_state = {"device": None, "stream": None, "decode_ws": {}, "prefill_ws": {}}
+
+
+def _ptr(t):
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream():
+    s = _state["stream"]
+    if s is None:
+        s = torch.cuda.current_stream().cuda_stream
+    return ctypes.c_void_p(s)
+
+
+def init(device=0):
+    """cuda::init (src/kernels.cu:1730-1737) for `device`; must precede every other call."""
+    if not torch.cuda.is_available():
+        raise RuntimeError("orin_llm_b200 needs a CUDA device (B200, sm_100a); there is no CPU path")
+    torch.cuda.set_device(device)
+    torch.cuda.current_stream()  # make sure the primary context exists
+    capi.check(capi.lib().oattn_init(device))
+    _state["device"] = device
+    return 0
+
+
+def set_stream(stream):
+    """cuda::set_stream (src/kernels.cu:1726-1728).  `stream`: torch.cuda.Stream, raw handle or None."""
+    if stream is None:
+        _state["stream"] = None
+    elif isinstance(stream, torch.cuda.Stream):
+        _state["stream"] = stream.cuda_stream
+    else:
+        _state["stream"] = int(stream)
+
+
+def sm_count():
+    return capi.lib().oattn_sm_count()
+
+
+def launch_count():
+    return int(capi.lib().oattn_launch_count())
+
+
+def _rope(x, rows, head_dim, rope_type, n_rot, theta, n_past, heads, d_pos, freq_factors):
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    capi.check(capi.lib().oattn_rope(_ptr(x), rows, head_dim, rope_type, n_rot, theta, n_past, heads, _ptr(d_pos),
+                                     _ptr(freq_factors), _stream()))
+
+
+def rope_neox_batch(x, rows, head_dim, n_rot, theta, n_past, heads, freq_factors=None):
+    _rope(x, rows, head_dim, ROPE_NEOX, n_rot, theta, n_past, heads, None, freq_factors)
+
+
+def rope_normal_batch(x, rows, head_dim, n_rot, theta, n_past, heads, freq_factors=None):
+    _rope(x, rows, head_dim, ROPE_NORMAL, n_rot, theta, n_past, heads, None, freq_factors)
+
+
+def rope_neox_ind(x, rows, head_dim, n_rot, theta, d_pos, freq_factors=None):
+    _rope(x, rows, head_dim, ROPE_NEOX, n_rot, theta, 0, 1, d_pos, freq_factors)
+
+
+def rope_normal_ind(x, rows, head_dim, n_rot, theta, d_pos, freq_factors=None):
+    _rope(x, rows, head_dim, ROPE_NORMAL, n_rot, theta, 0, 1, d_pos, freq_factors)
+
+
+def kv_store_batch(kc, vc, k, v, heads, head_dim, n_ctx, pos_base, batch):
+    capi.check(capi.lib().oattn_kv_store(_ptr(kc), _ptr(vc), _ptr(k), _ptr(v), heads, head_dim, n_ctx, pos_base, batch,
+                                         None, _stream()))
+
+
+def kv_store_ind(kc, vc, k, v, heads, head_dim, n_ctx, d_pos):
+    capi.check(capi.lib().oattn_kv_store(_ptr(kc), _ptr(vc), _ptr(k), _ptr(v), heads, head_dim, n_ctx, 0, 1, _ptr(d_pos),
+                                         _stream()))
+
+
+def kv_shift(kc, vc, n_layer, n_kv, head_dim, n_ctx, n_keep, shift):
+    capi.check(capi.lib().oattn_kv_shift(_ptr(kc), _ptr(vc), n_layer, n_kv, head_dim, n_ctx, n_keep, shift, _stream()))
+
+
+def decode_workspace(n_head, n_kv, head_dim, device=None):
+    """Scratch for the decode calls, allocated once per shape (scratch_size/scratch_assign pattern,
+    src/kernels.cu:1753-1776)."""
+    key = (n_head, n_kv, head_dim, torch.cuda.current_device())
+    ws = _state["decode_ws"].get(key)
+    if ws is None:
+        nbytes = capi.lib().oattn_decode_workspace_bytes(n_head, n_kv, head_dim)
+        if nbytes == 0:
+            raise capi.AttnError(capi.ERR_UNSUPPORTED, "decode shape not supported or init() not called")
+        ws = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+        _state["decode_ws"][key] = ws
+    return ws
+
+
+def prefill_workspace(n_head, n_kv, head_dim, batch):
+    key = (n_head, n_kv, head_dim, torch.cuda.current_device())
+    ws = _state["prefill_ws"].get(key)
+    nbytes = capi.lib().oattn_prefill_workspace_bytes(n_head, n_kv, head_dim, batch)
+    if nbytes == 0:
+        raise capi.AttnError(capi.ERR_UNSUPPORTED, "prefill shape not supported")
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+        _state["prefill_ws"][key] = ws
+    return ws
+
+
+def _rope_params(rope):
+    if rope is None:
+        return None, None
+    rope_type, n_rot, theta, ff = rope
+    p = capi.RopeParams(rope_type, n_rot, theta, 0 if ff is None else ff.data_ptr())
+    return ctypes.byref(p), p
+
+
+def flash_attention(q, kc, vc, out, n_head, n_kv, head_dim, n_ctx, n_past, batch, scale, workspace=None):
+    """cuda::flash_attention (src/kernels.cu:1974-1981): q already rotated, cache already written."""
+    attn_prefill(q, None, None, kc, vc, out, n_head, n_kv, head_dim, n_ctx, n_past, batch, scale, FUSE_NONE, None,
+                 workspace)
+
+
+def flash_attention_decode_ind(q, kc, vc, out, n_head, n_kv, head_dim, n_ctx, d_pos, scale, workspace=None):
+    """cuda::flash_attention_decode_ind (src/kernels.cu:1993-2000)."""
+    attn_decode(q, None, None, kc, vc, out, n_head, n_kv, head_dim, n_ctx, d_pos, scale, FUSE_NONE, None, workspace)
+
+
+def attn_decode(q, k_new, v_new, kc, vc, out, n_head, n_kv, head_dim, n_ctx, d_pos, scale, fuse=FUSE_ALL, rope=None,
+                workspace=None):
+    """Fused decode step of one layer (src/model_gpu.cu:277-282).  rope = (rope_type, n_rot, theta, freq_factors)."""
+    ws = workspace if workspace is not None else decode_workspace(n_head, n_kv, head_dim)
+    ref, keep = _rope_params(rope)
+    capi.check(capi.lib().oattn_decode(_ptr(q), _ptr(k_new), _ptr(v_new), _ptr(kc), _ptr(vc), _ptr(out), n_head, n_kv,
+                                       head_dim, n_ctx, _ptr(d_pos), scale, fuse, ref, _ptr(ws), ws.numel(), _stream()))
+    del keep
+
+
+def attn_decode_partial(q, kc, vc, part, n_head, n_kv, head_dim, n_ctx, d_len, scale, workspace=None):
+    """Partial (m, l, O) over the local cache rows [0, *d_len); part [n_head][head_dim+4] fp32."""
+    ws = workspace if workspace is not None else decode_workspace(n_head, n_kv, head_dim)
+    capi.check(capi.lib().oattn_decode_partial(_ptr(q), _ptr(kc), _ptr(vc), _ptr(part), n_head, n_kv, head_dim, n_ctx,
+                                               _ptr(d_len), scale, _ptr(ws), ws.numel(), _stream()))
+
+
+def attn_combine(parts, n_parts, out, n_head, head_dim):
+    capi.check(capi.lib().oattn_combine(_ptr(parts), n_parts, _ptr(out), n_head, head_dim, _stream()))
+
+
+def attn_prefill(q, k_new, v_new, kc, vc, out, n_head, n_kv, head_dim, n_ctx, n_past, batch, scale, fuse=FUSE_ALL,
+                 rope=None, workspace=None):
+    """Fused prefill step of one layer (src/model_gpu.cu:379-384)."""
+    ws = workspace if workspace is not None else prefill_workspace(n_head, n_kv, head_dim, batch)
+    ref, keep = _rope_params(rope)
+    capi.check(capi.lib().oattn_prefill(_ptr(q), _ptr(k_new), _ptr(v_new), _ptr(kc), _ptr(vc), _ptr(out), n_head, n_kv,
+                                        head_dim, n_ctx, n_past, batch, scale, fuse, ref, _ptr(ws), ws.numel(),
+                                        _stream()))
+    del keep
+
+
+def set_prefill_impl(impl):
+    capi.check(capi.lib().oattn_set_prefill_impl(impl))
+
+
+def set_decode_min_tiles(tiles):
+    capi.check(capi.lib().oattn_set_decode_min_tiles(tiles))
+
+
+def profile_enable(max_records):
+    """Time the split-KV kernel of the next `max_records` decode calls (0 switches it off)."""
+    capi.check(capi.lib().oattn_profile_enable(max_records))
+
+
+def profile_collect(capacity=65536):
+    """Milliseconds of the split-KV kernel for each decode call recorded since the last collect."""
+    buf = (ctypes.c_float * capacity)()
+    n = ctypes.c_int(0)
+    capi.check(capi.lib().oattn_profile_collect(buf, capacity, ctypes.byref(n)))
+    return [buf[i] for i in range(n.value)]
+
+
+class KVCache:
+    """Device KV cache with the reference's layout (src/model_gpu.cu:229-235, 255-260): one
+    allocation, K of all layers first, then V; per layer [n_kv][n_ctx][head_dim] fp16.  Unlike the
+    reference it is zero-filled once, so rows that were never written are finite."""
+
+    def __init__(self, n_layer, n_kv, n_ctx, head_dim, device="cuda"):
+        self.n_layer, self.n_kv, self.n_ctx, self.head_dim = n_layer, n_kv, n_ctx, head_dim
+        self.per_layer = n_kv * n_ctx * head_dim
+        self.buf = torch.zeros(2 * n_layer * self.per_layer, dtype=torch.float16, device=device)
+        self.k = self.buf[: n_layer * self.per_layer].view(n_layer, n_kv, n_ctx, head_dim)
+        self.v = self.buf[n_layer * self.per_layer:].view(n_layer, n_kv, n_ctx, head_dim)
+
+    def layer(self, l):
+        return self.k[l], self.v[l]
+
+    def shift(self, n_keep, shift):
+        """Model::kv_shift (src/model_gpu.cu:413-416)."""
+        if shift <= 0 or shift > self.n_ctx:
+            return
+        kv_shift(self.k, self.v, self.n_layer, self.n_kv, self.head_dim, self.n_ctx, n_keep, shift)
+
+
+def default_scale(head_dim):
+    return 1.0 / math.sqrt(head_dim)
