@@ -1,0 +1,362 @@
+#!/usr/bin/env python
+"""Benchmark of the decode-attention hot path (split-KV flash decoding over the fp16 KV cache).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--workload NAME]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Default workload `decode_3b_L1048576`: Qwen2.5-3B attention shape (16 query / 2 kv heads, head_dim 128,
+36 layers), KV length 1,048,576, fp16 KV i.i.d. N(0,1).  One STEP is the attention of one decoded token:
+36 decode-attention calls, one per layer, each over that layer's own KV buffers (1 GiB per layer, 36 GiB
+in all, so every call streams from HBM, never from L2).  With N GPUs the KV rows are cut into N contiguous
+slices (strong scaling); each call is local partial -> NCCL all-gather of the (m, l, O) records -> combine.
+
+The metric is KV GB/s: algorithmic KV bytes (2 * n_kv * L * head_dim * 2 B per call) per second of step time.
+Prints ONE JSON line (rank 0).
+"""
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: n_head, n_kv, head_dim, layers, L
+    "decode_3b_L1048576": dict(n_head=16, n_kv=2, head_dim=128, layers=36, L=1048576),
+    "decode_3b_L131072": dict(n_head=16, n_kv=2, head_dim=128, layers=36, L=131072),
+    "decode_7b_L32768": dict(n_head=28, n_kv=4, head_dim=128, layers=28, L=32768),
+    "decode_7b_L16384": dict(n_head=28, n_kv=4, head_dim=128, layers=28, L=16384),
+    "decode_7b_L4096": dict(n_head=28, n_kv=4, head_dim=128, layers=28, L=4096),
+    "decode_7b_L1024": dict(n_head=28, n_kv=4, head_dim=128, layers=28, L=1024),
+}
+CPU_SAMPLE_L = 131072      # rows of ONE layer call the CPU baseline / reference arm processes per step
+
+
+def kv_bytes(w, L=None):
+    L = w["L"] if L is None else L
+    return 2 * w["n_kv"] * L * w["head_dim"] * 2
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return json.load(open(p)), "measured"
+        except Exception:
+            pass
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback"
+
+
+# ---------------------------------------------------------------------------------------------------
+# clocks: read-only NVML sampling during the timed region
+class ClockSampler:
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._t = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = None
+            try:
+                import torch
+                uuid = str(torch.cuda.get_device_properties(index).uuid)
+                self.h = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid).encode())
+            except Exception:
+                self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self._reasons_fn = getattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                pynvml.nvmlDeviceGetCurrentClocksThrottleReasons
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                self.samples.append(self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM))
+                mask = self._reasons_fn(self.h)
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.005)
+
+    def start(self):
+        if self.nv:
+            self._t = threading.Thread(target=self._run, daemon=True)
+            self._t.start()
+
+    def stop(self):
+        if self._t:
+            self._stop.set()
+            self._t.join()
+        return {"sm_mhz": float(np.median(self.samples)) if self.samples else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# ---------------------------------------------------------------------------------------------------
+# CPU side: the reference's own scalar attention (oracle/_ref) or its C restatement (oracle/)
+def cpu_attention_sample(w, threads=None):
+    """Times ONE decode-attention call of the workload's shape over CPU_SAMPLE_L rows on the host cores.
+    Returns (seconds, kind, cores, sample description)."""
+    from oracle.oracle import Oracle, RefLib
+    L = min(CPU_SAMPLE_L, w["L"])
+    n_head, n_kv, hd = w["n_head"], w["n_kv"], w["head_dim"]
+    rng = np.random.default_rng(7)
+    q = rng.standard_normal((n_head, hd), dtype=np.float32).astype(np.float16).astype(np.float32)
+    kc = rng.standard_normal((n_kv, L, hd), dtype=np.float32).astype(np.float16).astype(np.float32)
+    vc = rng.standard_normal((n_kv, L, hd), dtype=np.float32).astype(np.float16).astype(np.float32)
+    scale = np.float32(1.0 / np.sqrt(hd))
+    ncpu = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    threads = threads or min(n_head, ncpu)
+    if RefLib.available():
+        ref = RefLib()
+        t0 = time.perf_counter()
+        _, used = ref.attend_mt(q, kc, vc, L, scale, threads)
+        dt = time.perf_counter() - t0
+        kind = "reference"
+    else:
+        import ctypes
+        orc = Oracle()
+        out = np.empty_like(q)
+        f32p = ctypes.POINTER(ctypes.c_float)
+        fn = orc.L.oracle_attend_head
+        fn.argtypes = [f32p] * 4 + [ctypes.c_int] * 6 + [ctypes.c_float, f32p]
+        used = threads
+
+        def work(t):
+            score = np.empty(L, np.float32)
+            for h in range(t, n_head, threads):
+                fn(q.ctypes.data_as(f32p), kc.ctypes.data_as(f32p), vc.ctypes.data_as(f32p), out.ctypes.data_as(f32p),
+                   h, n_head, n_kv, hd, L, L, scale, score.ctypes.data_as(f32p))
+        th = [threading.Thread(target=work, args=(t,)) for t in range(threads)]
+        t0 = time.perf_counter()
+        for x in th:
+            x.start()
+        for x in th:
+            x.join()
+        dt = time.perf_counter() - t0
+        kind = "port"
+    sample = "one layer call of the workload shape over the first %d KV rows (fp32 cache, %d host threads, one per query head)" % (L, used)
+    return dt, kind, used, sample, L
+
+
+def run_reference_arm(args, w):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    times = []
+    for i in range(args.warmup + args.steps):
+        dt, kind, cores, sample, L = cpu_attention_sample(w)
+        if i >= args.warmup:
+            times.append(dt)
+    ms = 1e3 * float(np.mean(times))
+    gbs = kv_bytes(w, L) / (ms * 1e-3) / 1e9
+    line = {
+        "impl": "reference", "metric": "decode_attn_kv_gbs", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "sample": sample, **{k: w[k] for k in ("n_head", "n_kv", "head_dim")}},
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": kind, "sample": sample},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+# ---------------------------------------------------------------------------------------------------
+def run_b200(args, w):
+    import torch
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit("--gpus %d but WORLD_SIZE=%d: launch with torch.distributed.run --nproc-per-node %d" % (args.gpus, world, args.gpus))
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    from orin_llm_b200 import build, ops
+    from orin_llm_b200.dist import SplitKVDecoder, slice_bounds
+    build.build()
+    ops.init(local_rank)
+
+    n_head, n_kv, hd, layers, L = w["n_head"], w["n_kv"], w["head_dim"], w["layers"], w["L"]
+    scale = 1.0 / float(np.sqrt(hd))
+    bounds = slice_bounds(L, world)
+    lo, hi = bounds[rank], bounds[rank + 1]
+    n_loc = hi - lo
+    gen = torch.Generator("cuda").manual_seed(1234 + rank)
+    Kc = [torch.randn(n_kv, n_loc, hd, device="cuda", dtype=torch.float16, generator=gen) for _ in range(layers)]
+    Vc = [torch.randn(n_kv, n_loc, hd, device="cuda", dtype=torch.float16, generator=gen) for _ in range(layers)]
+    gq = torch.Generator("cuda").manual_seed(99)       # q is replicated: same seed on every rank
+    q = torch.randn(layers, n_head, hd, device="cuda", generator=gq).half().float()
+    out = torch.zeros(layers, n_head, hd, device="cuda")
+    d_len = torch.tensor([n_loc], dtype=torch.int32, device="cuda")
+    d_pos = torch.tensor([n_loc - 1], dtype=torch.int32, device="cuda")
+    dec = SplitKVDecoder(n_head, n_kv, hd)
+
+    def step():
+        if world == 1:
+            for l in range(layers):
+                ops.flash_attention_decode_ind(q[l], Kc[l], Vc[l], out[l], n_head, n_kv, hd, n_loc, d_pos, scale)
+        else:
+            for l in range(layers):
+                dec.decode(q[l], Kc[l], Vc[l], n_loc, d_len, scale, out[l])
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    def timed(fn, steps):
+        barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+
+    # ---- timed region: kernel path with everything resident in HBM ----
+    n_prof = min(args.steps * layers, 4096)
+    ops.profile_enable(n_prof)
+    sampler = ClockSampler(local_rank)
+    l0 = ops.launch_count()
+    sampler.start()
+    total_ms = timed(step, args.steps)
+    clocks = sampler.stop()
+    launches = ops.launch_count() - l0
+    kern_ms = ops.profile_collect()
+    ops.profile_enable(0)
+    ms_per_step = total_ms / args.steps
+    bytes_per_step = kv_bytes(w) * layers
+    value = bytes_per_step / (ms_per_step * 1e-3) / 1e9
+
+    # ---- end to end through the public API with HOST buffers ----
+    # Per layer call: q, k_new, v_new come from pinned host memory, the call appends the new row to the
+    # cache (fused) and attends, the result goes back to host memory; one stream sync per step (token).
+    hq = torch.randn(layers, n_head, hd).half().float().pin_memory()
+    hk = torch.randn(layers, n_kv, hd).pin_memory()
+    hv = torch.randn(layers, n_kv, hd).pin_memory()
+    hout = torch.empty(layers, n_head, hd).pin_memory()
+    dq = torch.empty(layers, n_head, hd, device="cuda")
+    dk = torch.empty(layers, n_kv, hd, device="cuda")
+    dv = torch.empty(layers, n_kv, hd, device="cuda")
+    owner = rank == world - 1       # the rank whose slice holds the newest row
+
+    def e2e_step():
+        for l in range(layers):
+            dq[l].copy_(hq[l], non_blocking=True)
+            if owner:
+                dk[l].copy_(hk[l], non_blocking=True)
+                dv[l].copy_(hv[l], non_blocking=True)
+            if world == 1:
+                ops.attn_decode(dq[l], dk[l], dv[l], Kc[l], Vc[l], out[l], n_head, n_kv, hd, n_loc, d_pos, scale,
+                                ops.FUSE_KV_APPEND, None)
+            else:
+                if owner:
+                    ops.kv_store_ind(Kc[l], Vc[l], dk[l], dv[l], n_kv, hd, n_loc, d_pos)
+                dec.decode(dq[l], Kc[l], Vc[l], n_loc, d_len, scale, out[l])
+            hout[l].copy_(out[l], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for _ in range(3):
+        e2e_step()
+    e2e_ms = timed(e2e_step, args.steps) / args.steps
+    e2e_value = bytes_per_step / (e2e_ms * 1e-3) / 1e9
+    h2d = layers * (n_head + 2 * n_kv) * hd * 4
+    d2h = layers * n_head * hd * 4
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peaks, peak_kind = measured_peaks()
+    k_ms = float(np.mean(kern_ms)) if kern_ms else None
+    per_launch_bytes = kv_bytes(w, n_loc)
+    achieved = per_launch_bytes / (k_ms * 1e-3) / 1e9 if k_ms else None
+    roofline = {
+        "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+        "frac": (achieved / peaks["hbm_gbs"]) if achieved else None,
+        "traffic": None, "kernel": "decode_split_kernel<128,false>", "kernel_ms": k_ms, "launches_timed": len(kern_ms),
+        "algorithmic_bytes_per_launch": per_launch_bytes, "peak_source": peak_kind + " (MEASURED_PEAKS.json hbm_gbs)",
+        "frac_of_nominal_8tbs": (achieved / 8000.0) if achieved else None,
+    }
+    ncu_traffic = os.path.join(ROOT, "profiles", "decode_split_traffic.json")
+    if os.path.exists(ncu_traffic):
+        try:
+            t = json.load(open(ncu_traffic))
+            roofline["traffic"] = t["dram_bytes_per_kv_byte"] * per_launch_bytes
+            roofline["traffic_source"] = t.get("source")
+        except Exception:
+            pass
+
+    cpu = None
+    if not args.no_cpu_baseline:
+        dt, kind, cores, sample, Ls = cpu_attention_sample(w)
+        cpu = {"value": kv_bytes(w, Ls) / dt / 1e9, "unit": "GB/s", "cores": cores, "kind": kind, "sample": sample,
+               "seconds": dt}
+
+    line = {
+        "metric": "decode_attn_kv_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": args.workload, "n_head": n_head, "n_kv": n_kv, "head_dim": hd, "layers_per_step": layers,
+                   "kv_len": L, "kv_rows_per_gpu": n_loc, "parallelism": "kv-split x%d" % world,
+                   "l2": "inputs larger than L2: each of the %d layer calls of a step reads its own %.0f MiB of KV" % (
+                       layers, per_launch_bytes / 2**20)},
+        "pct_of_8tbs": 100.0 * value / (8000.0 * world),
+        "roofline": roofline, "cpu_baseline": cpu,
+        "e2e": {"value": e2e_value, "unit": "GB/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h},
+        "gpu_launches": int(launches), "clocks": clocks,
+    }
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="decode_3b_L1048576", choices=sorted(WORKLOADS))
+    ap.add_argument("--layers", type=int, default=None, help="override the layer calls per step")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    w = dict(WORKLOADS[args.workload])
+    if args.layers:
+        w["layers"] = args.layers
+    if args.impl == "reference":
+        run_reference_arm(args, w)
+    else:
+        run_b200(args, w)
+
+
+if __name__ == "__main__":
+    main()

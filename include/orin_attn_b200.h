@@ -144,6 +144,11 @@ int oattn_prefill(const float* q, const float* k_new, const float* v_new, uint16
                   float scale, int fuse, const oattn_rope_params* rope, void* workspace, size_t workspace_bytes,
                   void* stream);
 
+/* Reads back the status word the last oattn_prefill call on `workspace` left (same n_head, head_dim,
+ * batch as that call): 0 = completed; 1 = the tcgen05 kernel gave up on one of its bounded waits and
+ * the output is not valid.  SYNCHRONOUS (a blocking device-to-host copy): for tests and diagnostics. */
+int oattn_prefill_status(const void* workspace, int n_head, int head_dim, int batch, int* status);
+
 /* Which prefill kernel oattn_prefill launches: 0 = tcgen05/TMEM kernel (default),
  * 1 = the warp-level mma.sync kernel kept as an in-library cross-check.  Process-wide. */
 int oattn_set_prefill_impl(int impl);

@@ -21,6 +21,7 @@ EXPORTS = [
     "oattn_strerror", "oattn_last_cuda_error", "oattn_init", "oattn_sm_count", "oattn_rope",
     "oattn_kv_store", "oattn_kv_shift", "oattn_decode_workspace_bytes", "oattn_decode",
     "oattn_decode_partial", "oattn_combine", "oattn_prefill_workspace_bytes", "oattn_prefill",
+    "oattn_prefill_status",
     "oattn_set_prefill_impl", "oattn_set_decode_min_tiles", "oattn_profile_enable", "oattn_profile_collect",
     "oattn_launch_count",
 ]
@@ -69,6 +70,7 @@ def lib():
     L.oattn_prefill_workspace_bytes.restype = sz
     L.oattn_prefill_workspace_bytes.argtypes = [i, i, i, i]
     L.oattn_prefill.argtypes = [vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, f, i, rp, vp, sz, vp]
+    L.oattn_prefill_status.argtypes = [vp, i, i, i, ctypes.POINTER(ctypes.c_int)]
     L.oattn_set_prefill_impl.argtypes = [i]
     L.oattn_set_decode_min_tiles.argtypes = [i]
     L.oattn_profile_enable.argtypes = [i]

@@ -49,6 +49,7 @@ struct PrefillArgs {
     uint16_t* vc;
     float* out;            // [batch][n_head][hd] fp32
     __half* q16;           // workspace: [batch][n_head][hd] fp16, rotated and pre-scaled by scale*log2(e)
+    int* status;           // workspace: 0 = ok, non-zero = the tcgen05 kernel gave up on a bounded wait
     int n_head, n_kv, head_dim, n_ctx, n_past, batch;
     float scale;
     int fuse;

@@ -203,7 +203,14 @@ int oattn_combine(const float* parts, int n_parts, float* out, int n_head, int h
 
 size_t oattn_prefill_workspace_bytes(int n_head, int n_kv, int head_dim, int max_batch) {
     if (check_shape(n_head, n_kv, head_dim) != OATTN_OK || max_batch <= 0) return 0;
-    return align256((size_t)max_batch * n_head * head_dim * sizeof(__half));
+    return align256((size_t)max_batch * n_head * head_dim * sizeof(__half)) + 256;   // fp16 queries + status word
+}
+
+int oattn_prefill_status(const void* workspace, int n_head, int head_dim, int batch, int* status) {
+    if (!workspace || !status || n_head <= 0 || head_dim <= 0 || batch <= 0) return OATTN_ERR_ARG;
+    const size_t off = align256((size_t)batch * n_head * head_dim * sizeof(__half));
+    cudaError_t e = cudaMemcpy(status, reinterpret_cast<const uint8_t*>(workspace) + off, sizeof(int), cudaMemcpyDeviceToHost);
+    return e == cudaSuccess ? OATTN_OK : cuda_fail(e, "prefill status read");
 }
 
 int oattn_prefill(const float* q, const float* k_new, const float* v_new, uint16_t* kc, uint16_t* vc, float* out,
@@ -223,6 +230,7 @@ int oattn_prefill(const float* q, const float* k_new, const float* v_new, uint16
     if (!workspace || ((uintptr_t)workspace & 255) || workspace_bytes < need) return OATTN_ERR_WORKSPACE;
     a.q = q; a.k_new = k_new; a.v_new = v_new; a.kc = kc; a.vc = vc; a.out = out;
     a.q16 = reinterpret_cast<__half*>(workspace);
+    a.status = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(workspace) + need - 256);
     a.n_head = n_head; a.n_kv = n_kv; a.head_dim = head_dim; a.n_ctx = n_ctx; a.n_past = n_past; a.batch = batch;
     a.scale = scale; a.fuse = fuse;
     cudaStream_t s = (cudaStream_t)stream;

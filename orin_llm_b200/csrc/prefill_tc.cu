@@ -1,6 +1,440 @@
-// placeholder until the tcgen05 kernel lands
+// Chunked-prefill causal GQA attention on the 5th-generation tensor cores (tcgen05 + TMEM + TMA).
+//
+// Stands in for flash_attention_prefill_mma_k (src/kernels.cu:1351-1568).  Query token t of the
+// chunk sees cache rows 0..n_past+t.  q16 holds the chunk's queries already rotated, multiplied by
+// scale*log2(e) and converted to fp16 (prefill_prologue_kernel), so the score matrix is in the
+// log2 domain and the softmax is exp2.
+//
+// One CTA = one 128-row query tile of ONE kv head; a row is a (token, head-in-group) pair, row
+// R -> token t0 + R/G, head kvh*G + R%G (G = n_head/n_kv must divide 128), so a single pass over the
+// kv head's K/V rows serves all G query heads of 128/G tokens.  192 threads in three roles:
+//   warp 0   (one lane)  TMA producer: Q tile once, then 128-row K and V blocks into two-stage rings
+//                        (cp.async.bulk.tensor, 128-byte swizzle, no multicast); rows past the
+//                        chunk are outside the tensor map and arrive as zeros
+//   warp 1   (one lane)  tcgen05.mma issuer: S_j = Q K_j^T (M128 N128 K16 x8) into one of two TMEM
+//                        score buffers, O += P_j V_j (V as MN-major B operand) into a TMEM accumulator;
+//                        tcgen05.commit signals the mbarriers
+//   warps 2-5            softmax, one thread per row: tcgen05.ld of the score row, causal mask, running
+//                        max with lazy rescale of O (only when the max grows by more than 2^8), exp2,
+//                        fp16 P written to shared memory in the swizzled K-major layout the MMA reads;
+//                        finally O/l to global memory
+// S_{j+1} is issued before P_j V_j, so the tensor pipe computes the next scores while the softmax
+// warps work on the current ones.
+//
+// Every mbarrier wait is bounded: after about a second without progress the kernel raises an abort
+// flag, every role leaves its loop, outstanding copies and MMAs are drained (bounded again), TMEM is
+// released and a non-zero status word is left for the host.
+#include <cuda.h>
+
 #include "attn_internal.h"
+
 namespace oattn {
-cudaError_t prefill_tc_set_attributes() { return cudaSuccess; }
-cudaError_t launch_prefill_tc(const PrefillArgs&, int, cudaStream_t, unsigned long long*) { return cudaErrorNotSupported; }
+
+namespace {
+
+constexpr int kThreads = 192;
+constexpr int BM = 128, BN = 128, HD = 128;
+constexpr int SLAB = 128 * 128;                 // bytes of one 128-row x 64-element fp16 slab
+constexpr int TILE = 2 * SLAB;                  // a 128 x 128 fp16 tile = two slabs
+constexpr int OFF_Q = 0;
+constexpr int OFF_K = OFF_Q + TILE;             // 2 stages
+constexpr int OFF_V = OFF_K + 2 * TILE;         // 2 stages
+constexpr int OFF_P = OFF_V + 2 * TILE;
+constexpr int OFF_BAR = OFF_P + TILE;
+constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;   // + barrier block + slack for 1024-byte alignment
+constexpr long long kWaitCycles = 2000000000LL;    // ~1 s
+constexpr long long kDrainCycles = 200000000LL;    // ~0.1 s
+constexpr float kRescaleThreshold = 8.0f;          // log2 units
+
+enum Bar { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, P_FULL = 11, PV_DONE = 12, DRAIN = 13, NBAR = 14 };
+
+struct TcArgs {
+    float* out;
+    int* status;
+    int n_head, n_kv, n_past, batch, G, TQ;
+};
+
+// ---- PTX wrappers ---------------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
 }
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false when the abort flag is up or the time limit passed (and raises the flag).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* s_abort) {
+    if (mbar_try(bar, parity)) return true;
+    const long long t0 = clock64();
+    int spins = 0;
+    while (!mbar_try(bar, parity)) {
+        if ((++spins & 31) == 0) {
+            if (*s_abort) return false;
+            if (clock64() - t0 > kWaitCycles) { *s_abort = 1; return false; }
+        }
+    }
+    return true;
+}
+// Teardown wait: ignores the abort flag, shorter limit.
+__device__ __forceinline__ void mbar_drain(uint32_t bar, uint32_t parity) {
+    const long long t0 = clock64();
+    while (!mbar_try(bar, parity)) {
+        if (clock64() - t0 > kDrainCycles) break;
+    }
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];\n"
+                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+// D[tmem] (+)= A[smem desc] * B[smem desc], fp16 inputs, fp32 accumulate, M128 N128 K16.
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}\n"
+                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+                 "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n"
+                 ::"r"(taddr),
+                   "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+                   "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+                   "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+                   "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+                   "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+                   "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+                   "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+                   "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+                 : "memory");
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1 (sm_100).
+// K-major operand (rows 128 B apart, 8-row groups 1024 B apart): LBO field 1, SBO 1024 B.
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t addr) {
+    return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+           ((uint64_t)2 << 61);
+}
+// MN-major operand: 64 elements contiguous along N, next 64 at LBO = one slab; 8-row K groups 1024 B apart.
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t addr) {
+    return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)(SLAB >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// Instruction descriptor: fp32 accumulate, fp16 A and B, A K-major, N = 128, M = 128; bit 16 = B is MN-major.
+constexpr uint32_t IDESC_S = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+constexpr uint32_t IDESC_PV = IDESC_S | (1u << 16);
+
+__global__ void __launch_bounds__(kThreads, 1)
+prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                  const __grid_constant__ CUtensorMap tmV, const TcArgs p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t sbase = (raw + 1023u) & ~1023u;
+    uint8_t* smem = smem_raw + (sbase - raw);
+    const uint32_t bars = sbase + OFF_BAR;
+    volatile int* s_abort = reinterpret_cast<volatile int*>(smem + OFF_BAR + NBAR * 8 + 8);
+    uint32_t* s_tmem = reinterpret_cast<uint32_t*>(smem + OFF_BAR + NBAR * 8);
+    auto bar = [&](int i) { return bars + 8u * i; };
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int kvh = blockIdx.y;
+    const int tile = gridDim.x - 1 - blockIdx.x;          // latest (longest) tiles first
+    const int t0 = tile * p.TQ;
+    const int ntok = min(p.TQ, p.batch - t0);
+    const int kv_end = p.n_past + t0 + ntok;              // rows any query of this tile may see
+    const int nb = (kv_end + BN - 1) / BN;
+
+    if (tid == 0) {
+        mbar_init(bar(Q_FULL), 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(bar(K_FULL + s), 1);
+            mbar_init(bar(K_EMPTY + s), 1);
+            mbar_init(bar(V_FULL + s), 1);
+            mbar_init(bar(V_EMPTY + s), 1);
+            mbar_init(bar(S_FULL + s), 1);
+        }
+        mbar_init(bar(P_FULL), 128);
+        mbar_init(bar(PV_DONE), 1);
+        mbar_init(bar(DRAIN), 1);
+        *s_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(s_tmem)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *s_tmem;
+    const uint32_t TM_S = tmem, TM_O = tmem + 256;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            bool ok = true;
+            int k_issued[2] = {0, 0}, v_issued[2] = {0, 0};
+            mbar_expect_tx(bar(Q_FULL), TILE);
+            tma_load_3d(sbase + OFF_Q, &tmQ, 0, kvh * p.G, t0, bar(Q_FULL));
+            tma_load_3d(sbase + OFF_Q + SLAB, &tmQ, 64, kvh * p.G, t0, bar(Q_FULL));
+            auto load_k = [&](int j) {
+                const int s = j & 1;
+                if (j >= 2) ok = mbar_wait(bar(K_EMPTY + s), ((j >> 1) - 1) & 1, s_abort);
+                if (!ok) return;
+                mbar_expect_tx(bar(K_FULL + s), TILE);
+                tma_load_3d(sbase + OFF_K + s * TILE, &tmK, 0, j * BN, kvh, bar(K_FULL + s));
+                tma_load_3d(sbase + OFF_K + s * TILE + SLAB, &tmK, 64, j * BN, kvh, bar(K_FULL + s));
+                ++k_issued[s];
+            };
+            auto load_v = [&](int j) {
+                const int s = j & 1;
+                if (j >= 2) ok = mbar_wait(bar(V_EMPTY + s), ((j >> 1) - 1) & 1, s_abort);
+                if (!ok) return;
+                mbar_expect_tx(bar(V_FULL + s), TILE);
+                tma_load_3d(sbase + OFF_V + s * TILE, &tmV, 0, j * BN, kvh, bar(V_FULL + s));
+                tma_load_3d(sbase + OFF_V + s * TILE + SLAB, &tmV, 64, j * BN, kvh, bar(V_FULL + s));
+                ++v_issued[s];
+            };
+            load_k(0);
+            for (int j = 0; j < nb && ok; ++j) {
+                if (j + 1 < nb) load_k(j + 1);
+                if (ok) load_v(j);
+            }
+            if (*s_abort) {
+                // make sure no copy is still writing this CTA's shared memory when it exits
+                mbar_drain(bar(Q_FULL), 0);
+                for (int s = 0; s < 2; ++s) {
+                    if (k_issued[s]) mbar_drain(bar(K_FULL + s), (k_issued[s] - 1) & 1);
+                    if (v_issued[s]) mbar_drain(bar(V_FULL + s), (v_issued[s] - 1) & 1);
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            bool ok = mbar_wait(bar(Q_FULL), 0, s_abort);
+            auto issue_s = [&](int j) {
+                const int s = j & 1;
+                ok = mbar_wait(bar(K_FULL + s), (j >> 1) & 1, s_abort);
+                if (!ok) return;
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < HD / 16; ++kk) {
+                    const uint32_t off = (kk >> 2) * SLAB + (kk & 3) * 32;
+                    tc_mma(TM_S + s * BN, desc_kmajor(sbase + OFF_Q + off), desc_kmajor(sbase + OFF_K + s * TILE + off), IDESC_S, kk > 0);
+                }
+                tc_commit(bar(S_FULL + s));
+                tc_commit(bar(K_EMPTY + s));
+            };
+            if (ok) issue_s(0);
+            for (int j = 0; j < nb && ok; ++j) {
+                if (j + 1 < nb) issue_s(j + 1);
+                if (!ok) break;
+                ok = mbar_wait(bar(P_FULL), j & 1, s_abort);
+                if (ok) ok = mbar_wait(bar(V_FULL + (j & 1)), (j >> 1) & 1, s_abort);
+                if (!ok) break;
+                tc_fence_after();
+                const int s = j & 1;
+#pragma unroll
+                for (int kk = 0; kk < BN / 16; ++kk) {
+                    const uint32_t a_off = (kk >> 2) * SLAB + (kk & 3) * 32;      // P: K-major, 64 positions per slab
+                    const uint32_t b_off = kk * 2048;                             // V: 16 rows of 128 B per k-step
+                    tc_mma(TM_O, desc_kmajor(sbase + OFF_P + a_off), desc_mnmajor(sbase + OFF_V + s * TILE + b_off), IDESC_PV,
+                           (j > 0 || kk > 0) ? 1u : 0u);
+                }
+                tc_commit(bar(PV_DONE));
+                tc_commit(bar(V_EMPTY + s));
+            }
+            if (*s_abort) {
+                tc_commit(bar(DRAIN));
+                mbar_drain(bar(DRAIN), 0);
+            }
+        }
+        __syncwarp();
+    } else {
+        // ---------------------------------------------------------------- softmax + epilogue
+        const int quad = warp & 3;                          // TMEM lane quadrant this warp may access
+        const int row = quad * 32 + lane;
+        const int tok = row / p.G, hg = row - tok * p.G;
+        const int tglob = t0 + tok;
+        const bool valid = tok < ntok;
+        const int vis = p.n_past + tglob;                   // last visible cache row
+        const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
+        uint8_t* prow = smem + OFF_P + row * 128;
+        const int rsw = row & 7;
+        float m_ref = -CUDART_INF_F, l = 0.f;
+        bool ok = true;
+
+        for (int j = 0; j < nb && ok; ++j) {
+            const int b = j & 1;
+            ok = mbar_wait(bar(S_FULL + b), (j >> 1) & 1, s_abort);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t ts = TM_S + lane_addr + b * BN;
+            const bool need_mask = (j * BN + BN - 1 > p.n_past + t0);
+            const int lim = vis - j * BN;                   // columns <= lim are visible
+            float v[32];
+            float mx = -CUDART_INF_F;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                tmem_ld32(ts + 32 * c, v);
+                if (need_mask) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) if (32 * c + i > lim) v[i] = -CUDART_INF_F;
+                }
+#pragma unroll
+                for (int i = 0; i < 32; ++i) mx = fmaxf(mx, v[i]);
+            }
+            float m_new = m_ref;
+            if (j == 0 || mx > m_ref + kRescaleThreshold) m_new = mx;
+            const bool need = (j > 0) && (m_new != m_ref);
+            if (j > 0) {
+                ok = mbar_wait(bar(PV_DONE), (j - 1) & 1, s_abort);   // P buffer free, O quiescent
+                if (!ok) break;
+                tc_fence_after();
+            }
+            if (__any_sync(0xffffffffu, need)) {
+                const float alpha = need ? fast_exp2(m_ref - m_new) : 1.f;
+                l *= alpha;
+#pragma unroll 1
+                for (int c = 0; c < 4; ++c) {
+                    tmem_ld32(TM_O + lane_addr + 32 * c, v);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] *= alpha;
+                    tmem_st32(TM_O + lane_addr + 32 * c, v);
+                }
+                asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+            }
+            m_ref = m_new;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                tmem_ld32(ts + 32 * c, v);
+                if (need_mask) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) if (32 * c + i > lim) v[i] = -CUDART_INF_F;
+                }
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float p0 = fast_exp2(v[2 * i] - m_ref), p1 = fast_exp2(v[2 * i + 1] - m_ref);
+                    l += p0 + p1;
+                    pk[i] = pack_half2(p0, p1);
+                }
+                // columns 32c..32c+31 = 16-byte chunks 4c..4c+3; slab = chunk/8, swizzled inside the 128-byte row
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    const int chunk = 4 * c + q4;
+                    uint8_t* dst = prow + (chunk >> 3) * SLAB + (((chunk & 7) ^ rsw) << 4);
+                    *reinterpret_cast<uint4*>(dst) = make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            tc_fence_before();
+            mbar_arrive(bar(P_FULL));
+        }
+        if (ok) ok = mbar_wait(bar(PV_DONE), (nb - 1) & 1, s_abort);
+        if (ok) {
+            tc_fence_after();
+            const float inv = 1.f / l;
+            float* dst = p.out + ((size_t)tglob * p.n_head + kvh * p.G + hg) * HD;
+            float v[32];
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                tmem_ld32(TM_O + lane_addr + 32 * c, v);
+                if (valid) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        *reinterpret_cast<float4*>(dst + 32 * c + 4 * i) =
+                            make_float4(v[4 * i] * inv, v[4 * i + 1] * inv, v[4 * i + 2] * inv, v[4 * i + 3] * inv);
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(512u) : "memory");
+    }
+    if (tid == 0 && *s_abort && p.status) atomicExch(p.status, 1);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+
+// fp16 tensor [d2][d1][128] with the given strides (bytes); box = 64 x b1 x b2, 128-byte swizzle, zero fill.
+bool make_map(CUtensorMap* m, const void* base, uint64_t d1, uint64_t d2, uint64_t stride1, uint64_t stride2, uint32_t b1,
+              uint32_t b2) {
+    cuuint64_t dims[3] = {(cuuint64_t)HD, d1, d2};
+    cuuint64_t strides[2] = {stride1, stride2};
+    cuuint32_t box[3] = {64, b1, b2};
+    cuuint32_t estr[3] = {1, 1, 1};
+    return g_encode(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+} // namespace
+
+cudaError_t prefill_tc_set_attributes() {
+    if (!g_encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+        if (e != cudaSuccess) return e;
+        if (qres != cudaDriverEntryPointSuccess || !fn) return cudaErrorNotSupported;
+        g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+    return cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+}
+
+cudaError_t launch_prefill_tc(const PrefillArgs& a, int sm_count, cudaStream_t stream, unsigned long long* launches) {
+    (void)sm_count;
+    const int G = a.n_head / a.n_kv;
+    if (a.head_dim != HD || (128 % G) != 0 || !g_encode) return cudaErrorNotSupported;
+    const int TQ = 128 / G;
+    const uint64_t rows = (uint64_t)a.n_past + a.batch;          // rows past the chunk are never read (zero fill)
+    CUtensorMap tmQ, tmK, tmV;
+    const uint64_t rowb = HD * sizeof(__half);
+    if (!make_map(&tmQ, a.q16, a.n_head, a.batch, rowb, rowb * a.n_head, G, TQ)) return cudaErrorInvalidValue;
+    if (!make_map(&tmK, a.kc, rows, a.n_kv, rowb, rowb * a.n_ctx, BN, 1)) return cudaErrorInvalidValue;
+    if (!make_map(&tmV, a.vc, rows, a.n_kv, rowb, rowb * a.n_ctx, BN, 1)) return cudaErrorInvalidValue;
+    TcArgs t;
+    t.out = a.out;
+    t.status = a.status;
+    t.n_head = a.n_head; t.n_kv = a.n_kv; t.n_past = a.n_past; t.batch = a.batch; t.G = G; t.TQ = TQ;
+    dim3 grid((a.batch + TQ - 1) / TQ, a.n_kv);
+    prefill_tc_kernel<<<grid, kThreads, SMEM_BYTES, stream>>>(tmQ, tmK, tmV, t);
+    if (launches) *launches += 1;
+    return cudaGetLastError();
+}
+
+} // namespace oattn

@@ -105,6 +105,7 @@ __global__ void __launch_bounds__(kPrologueThreads) prefill_prologue_kernel(cons
     const int b = blockIdx.x, tid = threadIdx.x;
     const int hd = p.head_dim, pos = p.n_past + b;
     const bool rope_q = (p.fuse & 1) != 0, rope_k = (p.fuse & 2) != 0, append = (p.fuse & 4) != 0;
+    if (b == 0 && tid == 0 && p.status) *p.status = 0;
     if (rope_q || rope_k) {
         for (int i = tid; i < p.rope.n_rot / 2; i += kPrologueThreads) {
             const float f = rope_freq(i, p.rope.n_rot, p.rope.theta, p.rope.freq_factors);

@@ -11,7 +11,8 @@ import math
 import torch
 
 from . import capi
-from .capi import FUSE_ALL, FUSE_NONE, ROPE_NEOX, ROPE_NORMAL, PART_PAD  # noqa: F401
+from .capi import (FUSE_ALL, FUSE_KV_APPEND, FUSE_NONE, FUSE_ROPE_K, FUSE_ROPE_Q, PART_PAD, ROPE_NEOX,  # noqa: F401
+                   ROPE_NORMAL)
 
 _state = {"device": None, "stream": None, "decode_ws": {}, "prefill_ws": {}}
 
@@ -167,6 +168,14 @@ def attn_prefill(q, k_new, v_new, kc, vc, out, n_head, n_kv, head_dim, n_ctx, n_
                                         head_dim, n_ctx, n_past, batch, scale, fuse, ref, _ptr(ws), ws.numel(),
                                         _stream()))
     del keep
+
+
+def prefill_status(n_head, n_kv, head_dim, batch, workspace=None):
+    """Status word of the last attn_prefill call with this shape (blocking read; 0 = completed)."""
+    ws = workspace if workspace is not None else prefill_workspace(n_head, n_kv, head_dim, batch)
+    st = ctypes.c_int(-1)
+    capi.check(capi.lib().oattn_prefill_status(_ptr(ws), n_head, head_dim, batch, ctypes.byref(st)))
+    return st.value
 
 
 def set_prefill_impl(impl):

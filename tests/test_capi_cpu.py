@@ -53,7 +53,7 @@ def test_no_compute_without_device(lib):
 
 
 def test_prefill_workspace_size(lib):
-    assert lib.oattn_prefill_workspace_bytes(32, 8, 128, 512) == 512 * 32 * 128 * 2
+    assert lib.oattn_prefill_workspace_bytes(32, 8, 128, 512) == 512 * 32 * 128 * 2 + 256
     assert lib.oattn_prefill_workspace_bytes(32, 8, 96, 512) == 0      # head_dim not covered
     assert lib.oattn_prefill_workspace_bytes(34, 8, 128, 512) == 0     # n_head not a multiple of n_kv
 

@@ -47,6 +47,7 @@ def test_prefill_matches_oracle(ops, oracle, impl, n_head, n_kv, hd, n_past, bat
     try:
         ops.flash_attention(dev(q), dev(K), dev(V), out, n_head, n_kv, hd, n_ctx, n_past, batch, float(scale))
         torch.cuda.synchronize()
+        assert ops.prefill_status(n_head, n_kv, hd, batch) == 0, "kernel reported a timed-out wait"
     finally:
         ops.set_prefill_impl(0)
     want = oracle_prefill(oracle, q, K[:, :n_rows], V[:, :n_rows], n_past, scale)
