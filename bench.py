@@ -34,6 +34,12 @@ WORKLOADS = {
     "decode_7b_L4096": dict(n_head=28, n_kv=4, head_dim=128, layers=28, L=4096),
     "decode_7b_L1024": dict(n_head=28, n_kv=4, head_dim=128, layers=28, L=1024),
 }
+PREFILL_WORKLOADS = {
+    # Llama-3-8B attention shape: one 512-token chunk at KV offset n_past, RoPE theta 5e5 (normal pairing)
+    "prefill_8b_off0": dict(n_head=32, n_kv=8, head_dim=128, batch=512, n_past=0, theta=5e5, layers=32),
+    "prefill_8b_off4096": dict(n_head=32, n_kv=8, head_dim=128, batch=512, n_past=4096, theta=5e5, layers=32),
+    "prefill_8b_off8192": dict(n_head=32, n_kv=8, head_dim=128, batch=512, n_past=8192, theta=5e5, layers=32),
+}
 CPU_SAMPLE_L = 131072      # rows of ONE layer call the CPU baseline / reference arm processes per step
 
 
@@ -339,16 +345,93 @@ def run_b200(args, w):
         dist.destroy_process_group()
 
 
+def prefill_flops(w):
+    """Causal algorithmic FLOPs of one chunk: 4 * head_dim * n_head * sum_t (n_past + t + 1)."""
+    b, n_past = w["batch"], w["n_past"]
+    return 4 * w["head_dim"] * w["n_head"] * (b * n_past + b * (b + 1) // 2)
+
+
+def run_b200_prefill(args, w):
+    """Secondary workloads: chunked-prefill attention, one GPU.  A step = `layers` fused prefill calls
+    (RoPE q/k, KV append, causal attention), each on its own KV buffers."""
+    import torch
+    from orin_llm_b200 import build, ops
+    if args.gpus != 1:
+        raise SystemExit("prefill runs on one GPU")
+    build.build()
+    torch.cuda.set_device(0)
+    ops.init(0)
+    n_head, n_kv, hd, batch, n_past, layers = w["n_head"], w["n_kv"], w["head_dim"], w["batch"], w["n_past"], w["layers"]
+    n_ctx = n_past + batch
+    scale = 1.0 / float(np.sqrt(hd))
+    gen = torch.Generator("cuda").manual_seed(5)
+    Kc = [torch.randn(n_kv, n_ctx, hd, device="cuda", dtype=torch.float16, generator=gen) for _ in range(layers)]
+    Vc = [torch.randn(n_kv, n_ctx, hd, device="cuda", dtype=torch.float16, generator=gen) for _ in range(layers)]
+    q = torch.randn(layers, batch, n_head, hd, device="cuda", generator=gen)
+    k = torch.randn(layers, batch, n_kv, hd, device="cuda", generator=gen)
+    v = torch.randn(layers, batch, n_kv, hd, device="cuda", generator=gen)
+    out = torch.empty(layers, batch, n_head, hd, device="cuda")
+    rope = (ops.ROPE_NORMAL, hd, w["theta"], None)
+
+    def step():
+        for l in range(layers):
+            ops.attn_prefill(q[l], k[l], v[l], Kc[l], Vc[l], out[l], n_head, n_kv, hd, n_ctx, n_past, batch, scale,
+                             ops.FUSE_ALL, rope)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(0)
+    l0 = ops.launch_count()
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    launches = ops.launch_count() - l0
+    ms = e0.elapsed_time(e1) / args.steps
+    flops = prefill_flops(w) * layers
+    tflops = flops / (ms * 1e-3) / 1e12
+    peaks, peak_kind = measured_peaks()
+    assert ops.prefill_status(n_head, n_kv, hd, batch) == 0
+    line = {
+        "metric": "prefill_attn_tflops", "value": tflops, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": args.workload, "n_head": n_head, "n_kv": n_kv, "head_dim": hd, "chunk": batch,
+                   "kv_offset": n_past, "layers_per_step": layers, "rope_theta": w["theta"],
+                   "l2": "K/V of one call (%.0f MiB) are re-read by the 16 query tiles of a kv head from L2 by design; "
+                         "the %d layer calls of a step use distinct buffers" % (2 * n_kv * n_ctx * hd * 2 / 2**20, layers)},
+        "roofline": {"bound": "tensor", "achieved": tflops, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                     "frac": tflops / peaks["bf16_tflops"], "traffic": None,
+                     "peak_source": peak_kind + " (MEASURED_PEAKS.json bf16_tflops, burst)",
+                     "frac_of_nominal_2250": tflops / 2250.0,
+                     "note": "achieved = causal algorithmic FLOPs / step time, prologue kernel included"},
+        "gpu_launches": int(launches), "clocks": clocks,
+    }
+    print(json.dumps(line))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="decode_3b_L1048576", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="decode_3b_L1048576", choices=sorted(WORKLOADS) + sorted(PREFILL_WORKLOADS))
     ap.add_argument("--layers", type=int, default=None, help="override the layer calls per step")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
+    if args.workload in PREFILL_WORKLOADS:
+        w = dict(PREFILL_WORKLOADS[args.workload])
+        if args.layers:
+            w["layers"] = args.layers
+        if args.impl == "reference":
+            raise SystemExit("the reference arm is defined for the decode workloads")
+        return run_b200_prefill(args, w)
     w = dict(WORKLOADS[args.workload])
     if args.layers:
         w["layers"] = args.layers

@@ -7,17 +7,21 @@
 //
 // One CTA = one 128-row query tile of ONE kv head; a row is a (token, head-in-group) pair, row
 // R -> token t0 + R/G, head kvh*G + R%G (G = n_head/n_kv must divide 128), so a single pass over the
-// kv head's K/V rows serves all G query heads of 128/G tokens.  192 threads in three roles:
+// kv head's K/V rows serves all G query heads of 128/G tokens.  320 threads in three roles:
 //   warp 0   (one lane)  TMA producer: Q tile once, then 128-row K and V blocks into two-stage rings
 //                        (cp.async.bulk.tensor, 128-byte swizzle, no multicast); rows past the
 //                        chunk are outside the tensor map and arrive as zeros
-//   warp 1   (one lane)  tcgen05.mma issuer: S_j = Q K_j^T (M128 N128 K16 x8) into one of two TMEM
-//                        score buffers, O += P_j V_j (V as MN-major B operand) into a TMEM accumulator;
-//                        tcgen05.commit signals the mbarriers
-//   warps 2-5            softmax, one thread per row: tcgen05.ld of the score row, causal mask, running
-//                        max with lazy rescale of O (only when the max grows by more than 2^8), exp2,
-//                        fp16 P written to shared memory in the swizzled K-major layout the MMA reads;
-//                        finally O/l to global memory
+//   warp 1   (one lane)  tcgen05.mma issuer: S_j = Q K_j^T (M128 N128 K16 x8, both operands from shared
+//                        memory) into one of two TMEM score buffers; O += P_j V_j with P read straight
+//                        from TMEM (it overwrites the first 64 columns of its own score buffer as packed
+//                        fp16 pairs) and V as MN-major B operand from shared memory, into a TMEM
+//                        accumulator; tcgen05.commit signals the mbarriers
+//   warps 2-9            softmax, two threads per row (64 of the 128 score columns each; a warp can only
+//                        reach the TMEM lanes of its quadrant, so the split is by columns): tcgen05.ld of
+//                        the half row, causal mask, row max exchanged with the partner thread through
+//                        shared memory, lazy rescale of O (only when the max grows by more than 2^8),
+//                        exp2, fp16 P stored back to TMEM (tcgen05.st) where the next MMA takes it as
+//                        its A operand; finally O/l to global memory
 // S_{j+1} is issued before P_j V_j, so the tensor pipe computes the next scores while the softmax
 // warps work on the current ones.
 //
@@ -32,21 +36,21 @@ namespace oattn {
 
 namespace {
 
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;
 constexpr int BM = 128, BN = 128, HD = 128;
 constexpr int SLAB = 128 * 128;                 // bytes of one 128-row x 64-element fp16 slab
 constexpr int TILE = 2 * SLAB;                  // a 128 x 128 fp16 tile = two slabs
 constexpr int OFF_Q = 0;
 constexpr int OFF_K = OFF_Q + TILE;             // 2 stages
 constexpr int OFF_V = OFF_K + 2 * TILE;         // 2 stages
-constexpr int OFF_P = OFF_V + 2 * TILE;
-constexpr int OFF_BAR = OFF_P + TILE;
-constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;   // + barrier block + slack for 1024-byte alignment
+constexpr int OFF_BAR = OFF_V + 2 * TILE;
+constexpr int OFF_MX = OFF_BAR + 256;           // float [2 parities][2 column halves][128 rows]
+constexpr int SMEM_BYTES = OFF_MX + 2048 + 1024;   // + slack for 1024-byte alignment
 constexpr long long kWaitCycles = 2000000000LL;    // ~1 s
 constexpr long long kDrainCycles = 200000000LL;    // ~0.1 s
 constexpr float kRescaleThreshold = 8.0f;          // log2 units
 
-enum Bar { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, P_FULL = 11, PV_DONE = 12, DRAIN = 13, NBAR = 14 };
+enum Bar { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, P_FULL = 11, PV_DONE = 12, DRAIN = 13, MX = 14, NBAR = 16 };
 
 struct TcArgs {
     float* out;
@@ -105,7 +109,14 @@ __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_
                  "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}\n"
                  ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
 }
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+// Same with the A operand taken from TMEM (128 lanes x 8 columns of packed fp16 pairs per K16 step).
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n}\n"
+                 ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+// Issues the load; the values may be used only after tmem_wait_ld().
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
     uint32_t r[32];
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
                  "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
@@ -114,11 +125,11 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
                    "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
                    "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
                  : "r"(taddr) : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
                  "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n"
                  ::"r"(taddr),
@@ -177,7 +188,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             mbar_init(bar(V_EMPTY + s), 1);
             mbar_init(bar(S_FULL + s), 1);
         }
-        mbar_init(bar(P_FULL), 128);
+        mbar_init(bar(P_FULL), 256);
+        mbar_init(bar(MX), 256);
+        mbar_init(bar(MX + 1), 256);
         mbar_init(bar(PV_DONE), 1);
         mbar_init(bar(DRAIN), 1);
         *s_abort = 0;
@@ -263,10 +276,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 const int s = j & 1;
 #pragma unroll
                 for (int kk = 0; kk < BN / 16; ++kk) {
-                    const uint32_t a_off = (kk >> 2) * SLAB + (kk & 3) * 32;      // P: K-major, 64 positions per slab
                     const uint32_t b_off = kk * 2048;                             // V: 16 rows of 128 B per k-step
-                    tc_mma(TM_O, desc_kmajor(sbase + OFF_P + a_off), desc_mnmajor(sbase + OFF_V + s * TILE + b_off), IDESC_PV,
-                           (j > 0 || kk > 0) ? 1u : 0u);
+                    tc_mma_ts(TM_O, TM_S + s * BN + kk * 8, desc_mnmajor(sbase + OFF_V + s * TILE + b_off), IDESC_PV,
+                              (j > 0 || kk > 0) ? 1u : 0u);
                 }
                 tc_commit(bar(PV_DONE));
                 tc_commit(bar(V_EMPTY + s));
@@ -280,99 +292,102 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     } else {
         // ---------------------------------------------------------------- softmax + epilogue
         const int quad = warp & 3;                          // TMEM lane quadrant this warp may access
+        const int g = (warp - 2) >> 2;                      // which 64-column half of the row this thread owns
         const int row = quad * 32 + lane;
         const int tok = row / p.G, hg = row - tok * p.G;
         const int tglob = t0 + tok;
         const bool valid = tok < ntok;
         const int vis = p.n_past + tglob;                   // last visible cache row
         const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
-        uint8_t* prow = smem + OFF_P + row * 128;
-        const int rsw = row & 7;
+        float* s_mx = reinterpret_cast<float*>(smem + OFF_MX);
         float m_ref = -CUDART_INF_F, l = 0.f;
         bool ok = true;
+        float v[64];
+
+        // Exchange one float with the thread that owns the other half of this row (bounded wait).
+        auto exchange = [&](int it, float mine, float& other) -> bool {
+            const int par = it & 1;
+            s_mx[(par * 2 + g) * 128 + row] = mine;
+            tc_fence_before();                              // this thread's TMEM loads are done: the partner may overwrite
+            mbar_arrive(bar(MX + par));
+            if (!mbar_wait(bar(MX + par), (it >> 1) & 1, s_abort)) return false;
+            tc_fence_after();
+            other = s_mx[(par * 2 + (1 - g)) * 128 + row];
+            return true;
+        };
 
         for (int j = 0; j < nb && ok; ++j) {
             const int b = j & 1;
             ok = mbar_wait(bar(S_FULL + b), (j >> 1) & 1, s_abort);
             if (!ok) break;
             tc_fence_after();
-            const uint32_t ts = TM_S + lane_addr + b * BN;
-            const bool need_mask = (j * BN + BN - 1 > p.n_past + t0);
-            const int lim = vis - j * BN;                   // columns <= lim are visible
-            float v[32];
-            float mx = -CUDART_INF_F;
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                tmem_ld32(ts + 32 * c, v);
-                if (need_mask) {
+            const uint32_t ts = TM_S + lane_addr + b * BN + 64 * g;
+            tmem_ld32(ts, v);
+            tmem_ld32(ts + 32, v + 32);
+            tmem_wait_ld();
+            if (j * BN + BN - 1 > p.n_past + t0) {          // block reaches past the tile's first query: mask
+                const int lim = vis - j * BN - 64 * g;      // own columns <= lim are visible
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) if (32 * c + i > lim) v[i] = -CUDART_INF_F;
-                }
-#pragma unroll
-                for (int i = 0; i < 32; ++i) mx = fmaxf(mx, v[i]);
+                for (int i = 0; i < 64; ++i) if (i > lim) v[i] = -CUDART_INF_F;
             }
+            float mx = -CUDART_INF_F;
+#pragma unroll
+            for (int i = 0; i < 64; ++i) mx = fmaxf(mx, v[i]);
+            float other;
+            ok = exchange(j, mx, other);
+            if (!ok) break;
+            mx = fmaxf(mx, other);
             float m_new = m_ref;
             if (j == 0 || mx > m_ref + kRescaleThreshold) m_new = mx;
             const bool need = (j > 0) && (m_new != m_ref);
-            if (j > 0) {
-                ok = mbar_wait(bar(PV_DONE), (j - 1) & 1, s_abort);   // P buffer free, O quiescent
+            if (__any_sync(0xffffffffu, need)) {
+                ok = mbar_wait(bar(PV_DONE), (j - 1) & 1, s_abort);   // O must be quiescent while it is rescaled
                 if (!ok) break;
                 tc_fence_after();
-            }
-            if (__any_sync(0xffffffffu, need)) {
                 const float alpha = need ? fast_exp2(m_ref - m_new) : 1.f;
                 l *= alpha;
+                float o[32];
 #pragma unroll 1
-                for (int c = 0; c < 4; ++c) {
-                    tmem_ld32(TM_O + lane_addr + 32 * c, v);
+                for (int c = 0; c < 2; ++c) {
+                    const uint32_t to = TM_O + lane_addr + 64 * g + 32 * c;
+                    tmem_ld32(to, o);
+                    tmem_wait_ld();
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] *= alpha;
-                    tmem_st32(TM_O + lane_addr + 32 * c, v);
+                    for (int i = 0; i < 32; ++i) o[i] *= alpha;
+                    tmem_st32(to, o);
                 }
                 asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
             }
             m_ref = m_new;
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                tmem_ld32(ts + 32 * c, v);
-                if (need_mask) {
+            // P (fp16 pairs) goes over the first 64 columns of this score buffer: columns 32g..32g+31 are this
+            // thread's.  All 256 threads loaded their scores before the exchange above, so nothing is lost.
+            float pk[32];
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) if (32 * c + i > lim) v[i] = -CUDART_INF_F;
-                }
-                uint32_t pk[16];
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    const float p0 = fast_exp2(v[2 * i] - m_ref), p1 = fast_exp2(v[2 * i + 1] - m_ref);
-                    l += p0 + p1;
-                    pk[i] = pack_half2(p0, p1);
-                }
-                // columns 32c..32c+31 = 16-byte chunks 4c..4c+3; slab = chunk/8, swizzled inside the 128-byte row
-#pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    const int chunk = 4 * c + q4;
-                    uint8_t* dst = prow + (chunk >> 3) * SLAB + (((chunk & 7) ^ rsw) << 4);
-                    *reinterpret_cast<uint4*>(dst) = make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
-                }
+            for (int i = 0; i < 32; ++i) {
+                const float p0 = fast_exp2(v[2 * i] - m_ref), p1 = fast_exp2(v[2 * i + 1] - m_ref);
+                l += p0 + p1;
+                pk[i] = __uint_as_float(pack_half2(p0, p1));
             }
-            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            tmem_st32(TM_S + lane_addr + b * BN + 32 * g, pk);
+            asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
             tc_fence_before();
             mbar_arrive(bar(P_FULL));
         }
+        float l_other = 0.f;
+        if (ok) ok = exchange(nb, l, l_other);
         if (ok) ok = mbar_wait(bar(PV_DONE), (nb - 1) & 1, s_abort);
         if (ok) {
             tc_fence_after();
-            const float inv = 1.f / l;
-            float* dst = p.out + ((size_t)tglob * p.n_head + kvh * p.G + hg) * HD;
-            float v[32];
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                tmem_ld32(TM_O + lane_addr + 32 * c, v);
-                if (valid) {
+            const float inv = 1.f / (l + l_other);
+            float* dst = p.out + ((size_t)tglob * p.n_head + kvh * p.G + hg) * HD + 64 * g;
+            tmem_ld32(TM_O + lane_addr + 64 * g, v);
+            tmem_ld32(TM_O + lane_addr + 64 * g + 32, v + 32);
+            tmem_wait_ld();
+            if (valid) {
 #pragma unroll
-                    for (int i = 0; i < 8; ++i)
-                        *reinterpret_cast<float4*>(dst + 32 * c + 4 * i) =
-                            make_float4(v[4 * i] * inv, v[4 * i + 1] * inv, v[4 * i + 2] * inv, v[4 * i + 3] * inv);
-                }
+                for (int i = 0; i < 16; ++i)
+                    *reinterpret_cast<float4*>(dst + 4 * i) =
+                        make_float4(v[4 * i] * inv, v[4 * i + 1] * inv, v[4 * i + 2] * inv, v[4 * i + 3] * inv);
             }
         }
     }
