@@ -16,14 +16,16 @@
 //                        from TMEM (it overwrites the first 64 columns of its own score buffer as packed
 //                        fp16 pairs) and V as MN-major B operand from shared memory, into a TMEM
 //                        accumulator; tcgen05.commit signals the mbarriers
-//   warps 2-9            softmax, two threads per row (64 of the 128 score columns each; a warp can only
-//                        reach the TMEM lanes of its quadrant, so the split is by columns): tcgen05.ld of
-//                        the half row, causal mask, row max exchanged with the partner thread through
-//                        shared memory, lazy rescale of O (only when the max grows by more than 2^8),
-//                        exp2, fp16 P stored back to TMEM (tcgen05.st) where the next MMA takes it as
-//                        its A operand; finally O/l to global memory
-// S_{j+1} is issued before P_j V_j, so the tensor pipe computes the next scores while the softmax
-// warps work on the current ones.
+//   warps 2-5, 6-9       two softmax teams, one thread per row each.  Team t takes KV blocks j = t, t+2, ...
+//                        and owns score buffer t and its OWN accumulator O_t with its own running
+//                        reference max and row sum, so consecutive blocks never wait on each other (an
+//                        in-CTA split of the KV sequence by block parity).  Per block: tcgen05.ld of the
+//                        128-column score row, causal mask, row max, lazy rescale of O_t (only when the max
+//                        grows by more than 2^8), exp2, fp16 P stored back to TMEM (tcgen05.st) where the
+//                        next MMA takes it as its A operand.  At the end the two (m, l, O) are merged
+//                        log-sum-exp style and O/l goes to global memory.
+// S_{j+1} is issued before P_j V_j, so the tensor pipe computes the next scores while a softmax team
+// works on the current ones, and each team has two MMA block times for one block of softmax.
 //
 // Every mbarrier wait is bounded: after about a second without progress the kernel raises an abort
 // flag, every role leaves its loop, outstanding copies and MMAs are drained (bounded again), TMEM is
@@ -41,16 +43,30 @@ constexpr int BM = 128, BN = 128, HD = 128;
 constexpr int SLAB = 128 * 128;                 // bytes of one 128-row x 64-element fp16 slab
 constexpr int TILE = 2 * SLAB;                  // a 128 x 128 fp16 tile = two slabs
 constexpr int OFF_Q = 0;
-constexpr int OFF_K = OFF_Q + TILE;             // 2 stages
-constexpr int OFF_V = OFF_K + 2 * TILE;         // 2 stages
-constexpr int OFF_BAR = OFF_V + 2 * TILE;
-constexpr int OFF_MX = OFF_BAR + 256;           // float [2 parities][2 column halves][128 rows]
+constexpr int NST = 2;                          // K and V ring depth
+constexpr int OFF_K = OFF_Q + TILE;
+constexpr int OFF_V = OFF_K + NST * TILE;
+constexpr int OFF_BAR = OFF_V + NST * TILE;
+constexpr int OFF_MX = OFF_BAR + 256;           // float2 [2 teams][128 rows]: (m, l) exchanged at the end
 constexpr int SMEM_BYTES = OFF_MX + 2048 + 1024;   // + slack for 1024-byte alignment
+static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 constexpr long long kWaitCycles = 2000000000LL;    // ~1 s
 constexpr long long kDrainCycles = 200000000LL;    // ~0.1 s
-constexpr float kRescaleThreshold = 8.0f;          // log2 units
+constexpr float kRescaleThreshold = 4.0f;          // log2 units: P stays below 2^4 relative to the reference max
 
-enum Bar { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, P_FULL = 11, PV_DONE = 12, DRAIN = 13, MX = 14, NBAR = 16 };
+enum Bar { Q_FULL = 0, K_FULL = 1, K_EMPTY = 4, V_FULL = 7, V_EMPTY = 10, S_FULL = 13, P_FULL = 15, PV_DONE = 17, DRAIN = 19, XCH = 20, NBAR = 21 };
+
+#ifndef OATTN_TC_POLY
+#define OATTN_TC_POLY 0
+#endif
+
+#ifdef OATTN_TC_TRACE
+// Debug build only: per-event clock stamps of CTA (0,0).  [role][event][block]
+__device__ long long g_trace[3][8][128];
+#define TRACE(role, ev, blk) do { if (blockIdx.x == 0 && blockIdx.y == 0 && (blk) < 128) g_trace[role][ev][blk] = clock64(); } while (0)
+#else
+#define TRACE(role, ev, blk) do { } while (0)
+#endif
 
 struct TcArgs {
     float* out;
@@ -70,8 +86,10 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 }
 __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
     uint32_t ok;
-    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    // the third operand is a suspend-time hint: the thread sleeps in hardware until the phase completes
+    // (or the hint runs out) instead of taking issue slots from the warps that have work
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(ok) : "r"(bar), "r"(parity), "r"(1000000u) : "memory");
     return ok != 0;
 }
 // Bounded wait.  Returns false when the abort flag is up or the time limit passed (and raises the flag).
@@ -144,6 +162,22 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
                  : "memory");
 }
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;\n" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+// 2^x without the special-function unit: x = n + f with n = round(x), f in [-0.5, 0.5]; 2^f from a
+// degree-3 polynomial (relative error 7.7e-5, well below the fp16 rounding of P); 2^n by adding n to the
+// exponent field.  Inputs below -125 (including -inf for masked scores) give ~2^-125, which becomes 0 in fp16.
+__device__ __forceinline__ float exp2_poly(float x) {
+    x = fmaxf(x, -125.f);
+    const float fi = x + 12582912.f;        // 1.5 * 2^23: n lands in the low mantissa bits
+    const float f = x - (fi - 12582912.f);
+    const float q = fmaf(fmaf(fmaf(0.05508868f, f, 0.24260405f), f, 0.69327624f), f, 0.99992894f);
+    return __int_as_float(__float_as_int(q) + (__float_as_int(fi) << 23));
+}
+
 // Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1 (sm_100).
 // K-major operand (rows 128 B apart, 8-row groups 1024 B apart): LBO field 1, SBO 1024 B.
 __device__ __forceinline__ uint64_t desc_kmajor(uint32_t addr) {
@@ -181,17 +215,19 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 
     if (tid == 0) {
         mbar_init(bar(Q_FULL), 1);
-        for (int s = 0; s < 2; ++s) {
+        for (int s = 0; s < NST; ++s) {
             mbar_init(bar(K_FULL + s), 1);
             mbar_init(bar(K_EMPTY + s), 1);
             mbar_init(bar(V_FULL + s), 1);
             mbar_init(bar(V_EMPTY + s), 1);
-            mbar_init(bar(S_FULL + s), 1);
         }
-        mbar_init(bar(P_FULL), 256);
-        mbar_init(bar(MX), 256);
-        mbar_init(bar(MX + 1), 256);
+        mbar_init(bar(S_FULL), 1);
+        mbar_init(bar(S_FULL + 1), 1);
+        mbar_init(bar(P_FULL), 128);
+        mbar_init(bar(P_FULL + 1), 128);
+        mbar_init(bar(XCH), 256);
         mbar_init(bar(PV_DONE), 1);
+        mbar_init(bar(PV_DONE + 1), 1);
         mbar_init(bar(DRAIN), 1);
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -205,19 +241,19 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *s_tmem;
-    const uint32_t TM_S = tmem, TM_O = tmem + 256;
+    const uint32_t TM_S = tmem, TM_O = tmem + 256;   // S_t at TM_S + 128 t, O_t at TM_O + 128 t
 
     if (warp == 0) {
         // ---------------------------------------------------------------- TMA producer
         if (lane == 0) {
             bool ok = true;
-            int k_issued[2] = {0, 0}, v_issued[2] = {0, 0};
+            int k_issued[NST] = {}, v_issued[NST] = {};
             mbar_expect_tx(bar(Q_FULL), TILE);
             tma_load_3d(sbase + OFF_Q, &tmQ, 0, kvh * p.G, t0, bar(Q_FULL));
             tma_load_3d(sbase + OFF_Q + SLAB, &tmQ, 64, kvh * p.G, t0, bar(Q_FULL));
             auto load_k = [&](int j) {
-                const int s = j & 1;
-                if (j >= 2) ok = mbar_wait(bar(K_EMPTY + s), ((j >> 1) - 1) & 1, s_abort);
+                const int s = j % NST;
+                if (j >= NST) ok = mbar_wait(bar(K_EMPTY + s), ((j / NST) - 1) & 1, s_abort);
                 if (!ok) return;
                 mbar_expect_tx(bar(K_FULL + s), TILE);
                 tma_load_3d(sbase + OFF_K + s * TILE, &tmK, 0, j * BN, kvh, bar(K_FULL + s));
@@ -225,8 +261,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 ++k_issued[s];
             };
             auto load_v = [&](int j) {
-                const int s = j & 1;
-                if (j >= 2) ok = mbar_wait(bar(V_EMPTY + s), ((j >> 1) - 1) & 1, s_abort);
+                const int s = j % NST;
+                if (j >= NST) ok = mbar_wait(bar(V_EMPTY + s), ((j / NST) - 1) & 1, s_abort);
                 if (!ok) return;
                 mbar_expect_tx(bar(V_FULL + s), TILE);
                 tma_load_3d(sbase + OFF_V + s * TILE, &tmV, 0, j * BN, kvh, bar(V_FULL + s));
@@ -241,7 +277,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             if (*s_abort) {
                 // make sure no copy is still writing this CTA's shared memory when it exits
                 mbar_drain(bar(Q_FULL), 0);
-                for (int s = 0; s < 2; ++s) {
+                for (int s = 0; s < NST; ++s) {
                     if (k_issued[s]) mbar_drain(bar(K_FULL + s), (k_issued[s] - 1) & 1);
                     if (v_issued[s]) mbar_drain(bar(V_FULL + s), (v_issued[s] - 1) & 1);
                 }
@@ -253,35 +289,39 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         if (lane == 0) {
             bool ok = mbar_wait(bar(Q_FULL), 0, s_abort);
             auto issue_s = [&](int j) {
-                const int s = j & 1;
-                ok = mbar_wait(bar(K_FULL + s), (j >> 1) & 1, s_abort);
+                const int s = j % NST, b = j & 1;
+                ok = mbar_wait(bar(K_FULL + s), (j / NST) & 1, s_abort);
                 if (!ok) return;
+                TRACE(0, 0, j);
                 tc_fence_after();
 #pragma unroll
                 for (int kk = 0; kk < HD / 16; ++kk) {
                     const uint32_t off = (kk >> 2) * SLAB + (kk & 3) * 32;
-                    tc_mma(TM_S + s * BN, desc_kmajor(sbase + OFF_Q + off), desc_kmajor(sbase + OFF_K + s * TILE + off), IDESC_S, kk > 0);
+                    tc_mma(TM_S + b * BN, desc_kmajor(sbase + OFF_Q + off), desc_kmajor(sbase + OFF_K + s * TILE + off), IDESC_S, kk > 0);
                 }
-                tc_commit(bar(S_FULL + s));
+                tc_commit(bar(S_FULL + b));
                 tc_commit(bar(K_EMPTY + s));
             };
             if (ok) issue_s(0);
             for (int j = 0; j < nb && ok; ++j) {
                 if (j + 1 < nb) issue_s(j + 1);
                 if (!ok) break;
-                ok = mbar_wait(bar(P_FULL), j & 1, s_abort);
-                if (ok) ok = mbar_wait(bar(V_FULL + (j & 1)), (j >> 1) & 1, s_abort);
+                const int s = j & 1, sv = j % NST;
+                ok = mbar_wait(bar(P_FULL + s), (j >> 1) & 1, s_abort);
+                TRACE(0, 1, j);
+                if (ok) ok = mbar_wait(bar(V_FULL + sv), (j / NST) & 1, s_abort);
                 if (!ok) break;
+                TRACE(0, 2, j);
                 tc_fence_after();
-                const int s = j & 1;
 #pragma unroll
                 for (int kk = 0; kk < BN / 16; ++kk) {
                     const uint32_t b_off = kk * 2048;                             // V: 16 rows of 128 B per k-step
-                    tc_mma_ts(TM_O, TM_S + s * BN + kk * 8, desc_mnmajor(sbase + OFF_V + s * TILE + b_off), IDESC_PV,
-                              (j > 0 || kk > 0) ? 1u : 0u);
+                    tc_mma_ts(TM_O + s * HD, TM_S + s * BN + kk * 8, desc_mnmajor(sbase + OFF_V + sv * TILE + b_off), IDESC_PV,
+                              (j > 1 || kk > 0) ? 1u : 0u);
                 }
-                tc_commit(bar(PV_DONE));
-                tc_commit(bar(V_EMPTY + s));
+                tc_commit(bar(PV_DONE + s));
+                tc_commit(bar(V_EMPTY + sv));
+                TRACE(0, 3, j);
             }
             if (*s_abort) {
                 tc_commit(bar(DRAIN));
@@ -292,102 +332,136 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     } else {
         // ---------------------------------------------------------------- softmax + epilogue
         const int quad = warp & 3;                          // TMEM lane quadrant this warp may access
-        const int g = (warp - 2) >> 2;                      // which 64-column half of the row this thread owns
+        const int team = (warp - 2) >> 2;                   // 0: even KV blocks, 1: odd KV blocks
         const int row = quad * 32 + lane;
         const int tok = row / p.G, hg = row - tok * p.G;
         const int tglob = t0 + tok;
         const bool valid = tok < ntok;
         const int vis = p.n_past + tglob;                   // last visible cache row
         const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
-        float* s_mx = reinterpret_cast<float*>(smem + OFF_MX);
+        const uint32_t ts = TM_S + lane_addr + team * BN;   // this team's score buffer, this thread's lane
+        const uint32_t to = TM_O + lane_addr + team * HD;   // this team's accumulator
         float m_ref = -CUDART_INF_F, l = 0.f;
         bool ok = true;
-        float v[64];
+        int n_done = 0;                                     // blocks this team has handed to the MMA warp
 
-        // Exchange one float with the thread that owns the other half of this row (bounded wait).
-        auto exchange = [&](int it, float mine, float& other) -> bool {
-            const int par = it & 1;
-            s_mx[(par * 2 + g) * 128 + row] = mine;
-            tc_fence_before();                              // this thread's TMEM loads are done: the partner may overwrite
-            mbar_arrive(bar(MX + par));
-            if (!mbar_wait(bar(MX + par), (it >> 1) & 1, s_abort)) return false;
-            tc_fence_after();
-            other = s_mx[(par * 2 + (1 - g)) * 128 + row];
-            return true;
-        };
-
-        for (int j = 0; j < nb && ok; ++j) {
-            const int b = j & 1;
-            ok = mbar_wait(bar(S_FULL + b), (j >> 1) & 1, s_abort);
+        for (int j = team; j < nb && ok; j += 2, ++n_done) {
+            if (tid == 64 || tid == 192) TRACE(1 + team, 0, j);
+            ok = mbar_wait(bar(S_FULL + team), n_done & 1, s_abort);
             if (!ok) break;
+            if (tid == 64 || tid == 192) TRACE(1 + team, 1, j);
             tc_fence_after();
-            const uint32_t ts = TM_S + lane_addr + b * BN + 64 * g;
+            float v[128];
             tmem_ld32(ts, v);
             tmem_ld32(ts + 32, v + 32);
+            tmem_ld32(ts + 64, v + 64);
+            tmem_ld32(ts + 96, v + 96);
             tmem_wait_ld();
+            if (tid == 64 || tid == 192) TRACE(1 + team, 2, j);
             if (j * BN + BN - 1 > p.n_past + t0) {          // block reaches past the tile's first query: mask
-                const int lim = vis - j * BN - 64 * g;      // own columns <= lim are visible
+                const int lim = vis - j * BN;               // columns <= lim are visible
 #pragma unroll
-                for (int i = 0; i < 64; ++i) if (i > lim) v[i] = -CUDART_INF_F;
+                for (int i = 0; i < 128; ++i) if (i > lim) v[i] = -CUDART_INF_F;
             }
-            float mx = -CUDART_INF_F;
+            float mxc[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
 #pragma unroll
-            for (int i = 0; i < 64; ++i) mx = fmaxf(mx, v[i]);
-            float other;
-            ok = exchange(j, mx, other);
-            if (!ok) break;
-            mx = fmaxf(mx, other);
+            for (int i = 0; i < 128; i += 8) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) mxc[c] = max3(mxc[c], v[i + 2 * c], v[i + 2 * c + 1]);
+            }
+            const float mx = fmaxf(fmaxf(mxc[0], mxc[1]), fmaxf(mxc[2], mxc[3]));
             float m_new = m_ref;
-            if (j == 0 || mx > m_ref + kRescaleThreshold) m_new = mx;
-            const bool need = (j > 0) && (m_new != m_ref);
+            if (n_done == 0 || mx > m_ref + kRescaleThreshold) m_new = mx;
+            // a row that is fully masked so far keeps m_ref = -inf; use 0 as the exponent base then (all p = 0)
+            const float m_use = (m_new == -CUDART_INF_F) ? 0.f : m_new;
+            const bool need = (n_done > 0) && (m_new != m_ref) && (m_ref != -CUDART_INF_F);
             if (__any_sync(0xffffffffu, need)) {
-                ok = mbar_wait(bar(PV_DONE), (j - 1) & 1, s_abort);   // O must be quiescent while it is rescaled
+                ok = mbar_wait(bar(PV_DONE + team), (n_done - 1) & 1, s_abort);   // O_t must be quiescent while it is rescaled
                 if (!ok) break;
                 tc_fence_after();
                 const float alpha = need ? fast_exp2(m_ref - m_new) : 1.f;
                 l *= alpha;
                 float o[32];
 #pragma unroll 1
-                for (int c = 0; c < 2; ++c) {
-                    const uint32_t to = TM_O + lane_addr + 64 * g + 32 * c;
-                    tmem_ld32(to, o);
+                for (int c = 0; c < 4; ++c) {
+                    tmem_ld32(to + 32 * c, o);
                     tmem_wait_ld();
 #pragma unroll
                     for (int i = 0; i < 32; ++i) o[i] *= alpha;
-                    tmem_st32(to, o);
+                    tmem_st32(to + 32 * c, o);
                 }
                 asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
             }
             m_ref = m_new;
-            // P (fp16 pairs) goes over the first 64 columns of this score buffer: columns 32g..32g+31 are this
-            // thread's.  All 256 threads loaded their scores before the exchange above, so nothing is lost.
-            float pk[32];
+            if (tid == 64 || tid == 192) TRACE(1 + team, 3, j);
+            // P (fp16 pairs) goes over the first 64 columns of this thread's own score row.
+            // The special-function unit (ex2, and the fp32->fp16 conversion) has 16 lanes per SM, which for a
+            // 128 x 128 score block is as long as the two MMAs themselves.  Every other pair of elements
+            // therefore takes its exponential from a degree-3 polynomial on the FMA pipe instead.
+            uint32_t pk[64];
+            float l4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                const float p0 = fast_exp2(v[2 * i] - m_ref), p1 = fast_exp2(v[2 * i + 1] - m_ref);
-                l += p0 + p1;
-                pk[i] = __uint_as_float(pack_half2(p0, p1));
+            for (int i = 0; i < 64; ++i) {
+                const float x0 = v[2 * i] - m_use, x1 = v[2 * i + 1] - m_use;
+                float p0, p1;
+                if (OATTN_TC_POLY && (i & 1)) { p0 = exp2_poly(x0); p1 = exp2_poly(x1); }
+                else       { p0 = fast_exp2(x0); p1 = fast_exp2(x1); }
+                l4[i & 3] += p0 + p1;
+                pk[i] = pack_half2(p0, p1);
             }
-            tmem_st32(TM_S + lane_addr + b * BN + 32 * g, pk);
+            l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+            if (tid == 64 || tid == 192) TRACE(1 + team, 4, j);
+            tmem_st32(ts, reinterpret_cast<const float*>(pk));
+            tmem_st32(ts + 32, reinterpret_cast<const float*>(pk + 32));
             asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
             tc_fence_before();
-            mbar_arrive(bar(P_FULL));
+            mbar_arrive(bar(P_FULL + team));
+            if (tid == 64 || tid == 192) TRACE(1 + team, 5, j);
         }
-        float l_other = 0.f;
-        if (ok) ok = exchange(nb, l, l_other);
-        if (ok) ok = mbar_wait(bar(PV_DONE), (nb - 1) & 1, s_abort);
+        // ---- merge the two teams' (m, l, O) and write the output --------------------------------------
+        float2* s_x = reinterpret_cast<float2*>(smem + OFF_MX);
+        if (ok) {
+            s_x[team * 128 + row] = make_float2(m_ref, l);
+            mbar_arrive(bar(XCH));
+            ok = mbar_wait(bar(XCH), 0, s_abort);
+        }
+        if (ok && n_done > 0) ok = mbar_wait(bar(PV_DONE + team), (n_done - 1) & 1, s_abort);
+        // the other team's accumulator must be complete too before it is read
+        const int n_other = (nb - (1 - team) + 1) / 2;
+        if (ok && n_other > 0) ok = mbar_wait(bar(PV_DONE + (1 - team)), (n_other - 1) & 1, s_abort);
         if (ok) {
             tc_fence_after();
-            const float inv = 1.f / (l + l_other);
-            float* dst = p.out + ((size_t)tglob * p.n_head + kvh * p.G + hg) * HD + 64 * g;
-            tmem_ld32(TM_O + lane_addr + 64 * g, v);
-            tmem_ld32(TM_O + lane_addr + 64 * g + 32, v + 32);
-            tmem_wait_ld();
-            if (valid) {
+            const float2 mine = make_float2(m_ref, l), other = s_x[(1 - team) * 128 + row];
+            const float M = fmaxf(mine.x, other.x);
+            const float w_me = (mine.x == -CUDART_INF_F) ? 0.f : fast_exp2(mine.x - M);
+            const float w_ot = (other.x == -CUDART_INF_F) ? 0.f : fast_exp2(other.x - M);
+            const float inv = 1.f / (w_me * mine.y + w_ot * other.y);
+            const float a_me = w_me * inv, a_ot = w_ot * inv;
+            // this thread writes columns [64 team, 64 team + 64) of its row
+            float* dst = p.out + ((size_t)tglob * p.n_head + kvh * p.G + hg) * HD + 64 * team;
+            const uint32_t o_me = TM_O + lane_addr + team * HD + 64 * team;
+            const uint32_t o_ot = TM_O + lane_addr + (1 - team) * HD + 64 * team;
+            const bool ld_me = __any_sync(0xffffffffu, w_me != 0.f);   // tcgen05.ld is warp-collective
+            const bool ld_ot = __any_sync(0xffffffffu, w_ot != 0.f);   // (an unused accumulator is never read)
+#pragma unroll 1
+            for (int c = 0; c < 2; ++c) {
+                float a[32], b2[32];
 #pragma unroll
-                for (int i = 0; i < 16; ++i)
-                    *reinterpret_cast<float4*>(dst + 4 * i) =
-                        make_float4(v[4 * i] * inv, v[4 * i + 1] * inv, v[4 * i + 2] * inv, v[4 * i + 3] * inv);
+                for (int i = 0; i < 32; ++i) { a[i] = 0.f; b2[i] = 0.f; }
+                if (ld_me) tmem_ld32(o_me + 32 * c, a);
+                if (ld_ot) tmem_ld32(o_ot + 32 * c, b2);
+                tmem_wait_ld();
+                if (valid) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        float4 r;
+                        r.x = (w_me != 0.f ? a[4 * i] * a_me : 0.f) + (w_ot != 0.f ? b2[4 * i] * a_ot : 0.f);
+                        r.y = (w_me != 0.f ? a[4 * i + 1] * a_me : 0.f) + (w_ot != 0.f ? b2[4 * i + 1] * a_ot : 0.f);
+                        r.z = (w_me != 0.f ? a[4 * i + 2] * a_me : 0.f) + (w_ot != 0.f ? b2[4 * i + 2] * a_ot : 0.f);
+                        r.w = (w_me != 0.f ? a[4 * i + 3] * a_me : 0.f) + (w_ot != 0.f ? b2[4 * i + 3] * a_ot : 0.f);
+                        *reinterpret_cast<float4*>(dst + 32 * c + 4 * i) = r;
+                    }
+                }
             }
         }
     }
@@ -418,6 +492,12 @@ bool make_map(CUtensorMap* m, const void* base, uint64_t d1, uint64_t d2, uint64
 }
 
 } // namespace
+
+#ifdef OATTN_TC_TRACE
+extern "C" int oattn_debug_trace_read(long long* host) {
+    return (int)cudaMemcpyFromSymbol(host, g_trace, sizeof(g_trace));
+}
+#endif
 
 cudaError_t prefill_tc_set_attributes() {
     if (!g_encode) {
