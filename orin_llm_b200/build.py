@@ -30,6 +30,24 @@ def _nvcc():
     raise RuntimeError("nvcc not found")
 
 
+HOST_LIB = os.path.join(LIBDIR, "liborin_attn_host.so")
+HOST_SRC = os.path.join(HERE, "host", "kernels.cpp")
+
+
+def build_host(force=False):
+    """The C++ wrappers with the reference's names (host/kernels.h), linked against the C-ABI library."""
+    build(force=False)
+    deps = [HOST_SRC, os.path.join(HERE, "host", "kernels.h"), LIB]
+    if not force and os.path.exists(HOST_LIB) and all(os.path.getmtime(d) <= os.path.getmtime(HOST_LIB) for d in deps):
+        return HOST_LIB
+    cmd = ["g++", "-std=c++17", "-O2", "-fPIC", "-shared", "-fno-exceptions", "-fno-rtti", "-o", HOST_LIB, HOST_SRC,
+           "-L" + LIBDIR, "-lorin_attn_b200", "-Wl,-rpath,$ORIGIN"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("g++ failed:\n" + r.stdout + r.stderr)
+    return HOST_LIB
+
+
 def needs_build():
     if not os.path.exists(LIB):
         return True
@@ -54,3 +72,4 @@ def build(force=False, verbose=False):
 
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build_host(force="--force" in sys.argv))

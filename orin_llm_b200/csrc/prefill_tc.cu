@@ -7,25 +7,27 @@
 //
 // One CTA = one 128-row query tile of ONE kv head; a row is a (token, head-in-group) pair, row
 // R -> token t0 + R/G, head kvh*G + R%G (G = n_head/n_kv must divide 128), so a single pass over the
-// kv head's K/V rows serves all G query heads of 128/G tokens.  320 threads in three roles:
-//   warp 0   (one lane)  TMA producer: Q tile once, then 128-row K and V blocks into two-stage rings
-//                        (cp.async.bulk.tensor, 128-byte swizzle, no multicast); rows past the
-//                        chunk are outside the tensor map and arrive as zeros
-//   warp 1   (one lane)  tcgen05.mma issuer: S_j = Q K_j^T (M128 N128 K16 x8, both operands from shared
-//                        memory) into one of two TMEM score buffers; O += P_j V_j with P read straight
-//                        from TMEM (it overwrites the first 64 columns of its own score buffer as packed
-//                        fp16 pairs) and V as MN-major B operand from shared memory, into a TMEM
-//                        accumulator; tcgen05.commit signals the mbarriers
+// kv head's K/V rows serves all G query heads of 128/G tokens.  The KV sequence is walked in blocks of
+// 64 rows.  320 threads in three roles:
+//   warp 0   (one lane)  TMA producer: Q tile once, then 64-row K blocks (six-stage ring) and V blocks
+//                        (four-stage ring) with cp.async.bulk.tensor, 128-byte swizzle, no multicast;
+//                        rows past the chunk are outside the tensor map and arrive as zeros
+//   warp 1   (one lane)  tcgen05.mma issuer: S_j = Q K_j^T (M128 N64, K16 x8, both operands from shared
+//                        memory) into one of FOUR 64-column TMEM score buffers, so that four score blocks
+//                        are in flight; O_(j mod 2) += P_j V_j (M128 N128, K16 x4) with P read straight
+//                        from TMEM (it overwrites the first 32 columns of its own score buffer as packed
+//                        fp16 pairs) and V as MN-major B operand from shared memory; tcgen05.commit
+//                        signals the mbarriers
 //   warps 2-5, 6-9       two softmax teams, one thread per row each.  Team t takes KV blocks j = t, t+2, ...
-//                        and owns score buffer t and its OWN accumulator O_t with its own running
-//                        reference max and row sum, so consecutive blocks never wait on each other (an
-//                        in-CTA split of the KV sequence by block parity).  Per block: tcgen05.ld of the
-//                        128-column score row, causal mask, row max, lazy rescale of O_t (only when the max
-//                        grows by more than 2^8), exp2, fp16 P stored back to TMEM (tcgen05.st) where the
-//                        next MMA takes it as its A operand.  At the end the two (m, l, O) are merged
-//                        log-sum-exp style and O/l goes to global memory.
-// S_{j+1} is issued before P_j V_j, so the tensor pipe computes the next scores while a softmax team
-// works on the current ones, and each team has two MMA block times for one block of softmax.
+//                        and owns accumulator O_t with its own running reference max and row sum (an
+//                        in-CTA split of the KV sequence by block parity), so the teams never wait on each
+//                        other.  Per block: tcgen05.ld of the 64-column score row, causal mask, row max,
+//                        lazy rescale of O_t (only when the max grows by more than 2^4), exp2, fp16 P stored
+//                        back to TMEM (tcgen05.st).  At the end the two (m, l, O) are merged log-sum-exp
+//                        style and O/l goes to global memory.
+// The exponentials run on the 16-lane special-function unit, which for a 128 x 128 score block takes about
+// as long as the MMAs themselves; with four score buffers both teams work while the tensor pipe runs ahead,
+// so the loop is bound by the tensor pipe, not by the S -> softmax -> P V dependency chain.
 //
 // Every mbarrier wait is bounded: after about a second without progress the kernel raises an abort
 // flag, every role leaves its loop, outstanding copies and MMAs are drained (bounded again), TMEM is
@@ -39,22 +41,27 @@ namespace oattn {
 namespace {
 
 constexpr int kThreads = 320;
-constexpr int BM = 128, BN = 128, HD = 128;
-constexpr int SLAB = 128 * 128;                 // bytes of one 128-row x 64-element fp16 slab
-constexpr int TILE = 2 * SLAB;                  // a 128 x 128 fp16 tile = two slabs
+constexpr int BM = 128, BN = 64, HD = 128;
+constexpr int QSLAB = 128 * 128;                // bytes of one 128-row x 64-element fp16 slab (Q)
+constexpr int QTILE = 2 * QSLAB;
+constexpr int SLAB = BN * 128;                  // bytes of one 64-row x 64-element fp16 slab (K, V)
+constexpr int TILE = 2 * SLAB;                  // a 64 x 128 fp16 block = two slabs
+constexpr int NK = 6, NV = 4;                   // K and V ring depths
+constexpr int NSB = 4;                          // score buffers in TMEM
 constexpr int OFF_Q = 0;
-constexpr int NST = 2;                          // K and V ring depth
-constexpr int OFF_K = OFF_Q + TILE;
-constexpr int OFF_V = OFF_K + NST * TILE;
-constexpr int OFF_BAR = OFF_V + NST * TILE;
-constexpr int OFF_MX = OFF_BAR + 256;           // float2 [2 teams][128 rows]: (m, l) exchanged at the end
+constexpr int OFF_K = OFF_Q + QTILE;
+constexpr int OFF_V = OFF_K + NK * TILE;
+constexpr int OFF_BAR = OFF_V + NV * TILE;
+constexpr int OFF_MX = OFF_BAR + 512;           // float2 [2 teams][128 rows]: (m, l) exchanged at the end
 constexpr int SMEM_BYTES = OFF_MX + 2048 + 1024;   // + slack for 1024-byte alignment
 static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 constexpr long long kWaitCycles = 2000000000LL;    // ~1 s
 constexpr long long kDrainCycles = 200000000LL;    // ~0.1 s
 constexpr float kRescaleThreshold = 4.0f;          // log2 units: P stays below 2^4 relative to the reference max
 
-enum Bar { Q_FULL = 0, K_FULL = 1, K_EMPTY = 4, V_FULL = 7, V_EMPTY = 10, S_FULL = 13, P_FULL = 15, PV_DONE = 17, DRAIN = 19, XCH = 20, NBAR = 21 };
+enum Bar { Q_FULL = 0, K_FULL = 1, K_EMPTY = K_FULL + NK, V_FULL = K_EMPTY + NK, V_EMPTY = V_FULL + NV, S_FULL = V_EMPTY + NV,
+           P_FULL = S_FULL + NSB, PV_DONE = P_FULL + NSB, DRAIN = PV_DONE + 2, XCH = DRAIN + 1, ALL_DONE = XCH + 1, NBAR = ALL_DONE + 1 };
+static_assert(NBAR * 8 + 16 <= 512, "barrier block");
 
 #ifndef OATTN_TC_POLY
 #define OATTN_TC_POLY 0
@@ -133,20 +140,17 @@ __device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint
                  "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n}\n"
                  ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
 }
-// Issues the load; the values may be used only after tmem_wait_ld().
+// TMEM -> registers.  The load and its wait sit in ONE asm statement: the destination registers are
+// written asynchronously, and nothing (not even a compiler-generated register move) may touch them before
+// tcgen05.wait::ld has returned.  The outputs are early-clobber so that the address register can never be
+// allocated on top of a destination register.  One load per statement: a second load issued before the wait
+// would read its address while the first is still writing registers.
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
-    uint32_t r[32];
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+                 "tcgen05.wait::ld.sync.aligned;\n"
+                 : "=&f"(v[0]), "=&f"(v[1]), "=&f"(v[2]), "=&f"(v[3]), "=&f"(v[4]), "=&f"(v[5]), "=&f"(v[6]), "=&f"(v[7]), "=&f"(v[8]), "=&f"(v[9]), "=&f"(v[10]), "=&f"(v[11]), "=&f"(v[12]), "=&f"(v[13]), "=&f"(v[14]), "=&f"(v[15]), "=&f"(v[16]), "=&f"(v[17]), "=&f"(v[18]), "=&f"(v[19]), "=&f"(v[20]), "=&f"(v[21]), "=&f"(v[22]), "=&f"(v[23]), "=&f"(v[24]), "=&f"(v[25]), "=&f"(v[26]), "=&f"(v[27]), "=&f"(v[28]), "=&f"(v[29]), "=&f"(v[30]), "=&f"(v[31])
                  : "r"(taddr) : "memory");
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
-__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
                  "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n"
@@ -189,9 +193,10 @@ __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t addr) {
     return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)(SLAB >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
            ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
 }
-// Instruction descriptor: fp32 accumulate, fp16 A and B, A K-major, N = 128, M = 128; bit 16 = B is MN-major.
+// Instruction descriptor: fp32 accumulate, fp16 A and B, A K-major, M = 128; N = 64 for S, 128 for P V;
+// bit 16 = B is MN-major.
 constexpr uint32_t IDESC_S = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-constexpr uint32_t IDESC_PV = IDESC_S | (1u << 16);
+constexpr uint32_t IDESC_PV = (1u << 4) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -215,20 +220,14 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 
     if (tid == 0) {
         mbar_init(bar(Q_FULL), 1);
-        for (int s = 0; s < NST; ++s) {
-            mbar_init(bar(K_FULL + s), 1);
-            mbar_init(bar(K_EMPTY + s), 1);
-            mbar_init(bar(V_FULL + s), 1);
-            mbar_init(bar(V_EMPTY + s), 1);
-        }
-        mbar_init(bar(S_FULL), 1);
-        mbar_init(bar(S_FULL + 1), 1);
-        mbar_init(bar(P_FULL), 128);
-        mbar_init(bar(P_FULL + 1), 128);
-        mbar_init(bar(XCH), 256);
+        for (int s = 0; s < NK; ++s) { mbar_init(bar(K_FULL + s), 1); mbar_init(bar(K_EMPTY + s), 1); }
+        for (int s = 0; s < NV; ++s) { mbar_init(bar(V_FULL + s), 1); mbar_init(bar(V_EMPTY + s), 1); }
+        for (int s = 0; s < NSB; ++s) { mbar_init(bar(S_FULL + s), 1); mbar_init(bar(P_FULL + s), 128); }
         mbar_init(bar(PV_DONE), 1);
         mbar_init(bar(PV_DONE + 1), 1);
+        mbar_init(bar(XCH), 256);
         mbar_init(bar(DRAIN), 1);
+        mbar_init(bar(ALL_DONE), 1);
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
@@ -241,19 +240,19 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *s_tmem;
-    const uint32_t TM_S = tmem, TM_O = tmem + 256;   // S_t at TM_S + 128 t, O_t at TM_O + 128 t
+    const uint32_t TM_S = tmem, TM_O = tmem + 256;   // score buffer b at TM_S + 64 b, O_t at TM_O + 128 t
 
     if (warp == 0) {
         // ---------------------------------------------------------------- TMA producer
         if (lane == 0) {
             bool ok = true;
-            int k_issued[NST] = {}, v_issued[NST] = {};
-            mbar_expect_tx(bar(Q_FULL), TILE);
+            int k_issued[NK] = {}, v_issued[NV] = {};
+            mbar_expect_tx(bar(Q_FULL), QTILE);
             tma_load_3d(sbase + OFF_Q, &tmQ, 0, kvh * p.G, t0, bar(Q_FULL));
-            tma_load_3d(sbase + OFF_Q + SLAB, &tmQ, 64, kvh * p.G, t0, bar(Q_FULL));
+            tma_load_3d(sbase + OFF_Q + QSLAB, &tmQ, 64, kvh * p.G, t0, bar(Q_FULL));
             auto load_k = [&](int j) {
-                const int s = j % NST;
-                if (j >= NST) ok = mbar_wait(bar(K_EMPTY + s), ((j / NST) - 1) & 1, s_abort);
+                const int s = j % NK;
+                if (j >= NK) ok = mbar_wait(bar(K_EMPTY + s), ((j / NK) - 1) & 1, s_abort);
                 if (!ok) return;
                 mbar_expect_tx(bar(K_FULL + s), TILE);
                 tma_load_3d(sbase + OFF_K + s * TILE, &tmK, 0, j * BN, kvh, bar(K_FULL + s));
@@ -261,26 +260,27 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 ++k_issued[s];
             };
             auto load_v = [&](int j) {
-                const int s = j % NST;
-                if (j >= NST) ok = mbar_wait(bar(V_EMPTY + s), ((j / NST) - 1) & 1, s_abort);
+                const int s = j % NV;
+                if (j >= NV) ok = mbar_wait(bar(V_EMPTY + s), ((j / NV) - 1) & 1, s_abort);
                 if (!ok) return;
                 mbar_expect_tx(bar(V_FULL + s), TILE);
                 tma_load_3d(sbase + OFF_V + s * TILE, &tmV, 0, j * BN, kvh, bar(V_FULL + s));
                 tma_load_3d(sbase + OFF_V + s * TILE + SLAB, &tmV, 64, j * BN, kvh, bar(V_FULL + s));
                 ++v_issued[s];
             };
-            load_k(0);
+            // the MMA warp consumes K_0..K_3 first, then alternates V_j, K_(j+4)
+            for (int j = 0; j < NSB && j < nb && ok; ++j) load_k(j);
             for (int j = 0; j < nb && ok; ++j) {
-                if (j + 1 < nb) load_k(j + 1);
-                if (ok) load_v(j);
+                load_v(j);
+                if (ok && j + NSB < nb) load_k(j + NSB);
             }
             if (*s_abort) {
                 // make sure no copy is still writing this CTA's shared memory when it exits
                 mbar_drain(bar(Q_FULL), 0);
-                for (int s = 0; s < NST; ++s) {
+                for (int s = 0; s < NK; ++s)
                     if (k_issued[s]) mbar_drain(bar(K_FULL + s), (k_issued[s] - 1) & 1);
+                for (int s = 0; s < NV; ++s)
                     if (v_issued[s]) mbar_drain(bar(V_FULL + s), (v_issued[s] - 1) & 1);
-                }
             }
         }
         __syncwarp();
@@ -289,40 +289,42 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         if (lane == 0) {
             bool ok = mbar_wait(bar(Q_FULL), 0, s_abort);
             auto issue_s = [&](int j) {
-                const int s = j % NST, b = j & 1;
-                ok = mbar_wait(bar(K_FULL + s), (j / NST) & 1, s_abort);
+                const int s = j % NK, b = j & (NSB - 1);
+                ok = mbar_wait(bar(K_FULL + s), (j / NK) & 1, s_abort);
                 if (!ok) return;
                 TRACE(0, 0, j);
                 tc_fence_after();
 #pragma unroll
                 for (int kk = 0; kk < HD / 16; ++kk) {
-                    const uint32_t off = (kk >> 2) * SLAB + (kk & 3) * 32;
-                    tc_mma(TM_S + b * BN, desc_kmajor(sbase + OFF_Q + off), desc_kmajor(sbase + OFF_K + s * TILE + off), IDESC_S, kk > 0);
+                    const uint32_t a_off = (kk >> 2) * QSLAB + (kk & 3) * 32;
+                    const uint32_t b_off = (kk >> 2) * SLAB + (kk & 3) * 32;
+                    tc_mma(TM_S + b * BN, desc_kmajor(sbase + OFF_Q + a_off), desc_kmajor(sbase + OFF_K + s * TILE + b_off), IDESC_S, kk > 0);
                 }
                 tc_commit(bar(S_FULL + b));
                 tc_commit(bar(K_EMPTY + s));
             };
-            if (ok) issue_s(0);
+            for (int j = 0; j < NSB && j < nb && ok; ++j) issue_s(j);
             for (int j = 0; j < nb && ok; ++j) {
-                if (j + 1 < nb) issue_s(j + 1);
-                if (!ok) break;
-                const int s = j & 1, sv = j % NST;
-                ok = mbar_wait(bar(P_FULL + s), (j >> 1) & 1, s_abort);
+                const int b = j & (NSB - 1), t = j & 1, sv = j % NV;
+                ok = mbar_wait(bar(P_FULL + b), (j / NSB) & 1, s_abort);
                 TRACE(0, 1, j);
-                if (ok) ok = mbar_wait(bar(V_FULL + sv), (j / NST) & 1, s_abort);
+                if (ok) ok = mbar_wait(bar(V_FULL + sv), (j / NV) & 1, s_abort);
                 if (!ok) break;
                 TRACE(0, 2, j);
                 tc_fence_after();
 #pragma unroll
                 for (int kk = 0; kk < BN / 16; ++kk) {
                     const uint32_t b_off = kk * 2048;                             // V: 16 rows of 128 B per k-step
-                    tc_mma_ts(TM_O + s * HD, TM_S + s * BN + kk * 8, desc_mnmajor(sbase + OFF_V + sv * TILE + b_off), IDESC_PV,
+                    tc_mma_ts(TM_O + t * HD, TM_S + b * BN + kk * 8, desc_mnmajor(sbase + OFF_V + sv * TILE + b_off), IDESC_PV,
                               (j > 1 || kk > 0) ? 1u : 0u);
                 }
-                tc_commit(bar(PV_DONE + s));
+                tc_commit(bar(PV_DONE + t));
                 tc_commit(bar(V_EMPTY + sv));
                 TRACE(0, 3, j);
+                // score buffer b is free again once P_j V_j has been issued (the tensor pipe runs in order)
+                if (j + NSB < nb) issue_s(j + NSB);
             }
+            if (ok) tc_commit(bar(ALL_DONE));
             if (*s_abort) {
                 tc_commit(bar(DRAIN));
                 mbar_drain(bar(DRAIN), 0);
@@ -339,33 +341,32 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         const bool valid = tok < ntok;
         const int vis = p.n_past + tglob;                   // last visible cache row
         const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
-        const uint32_t ts = TM_S + lane_addr + team * BN;   // this team's score buffer, this thread's lane
         const uint32_t to = TM_O + lane_addr + team * HD;   // this team's accumulator
         float m_ref = -CUDART_INF_F, l = 0.f;
         bool ok = true;
         int n_done = 0;                                     // blocks this team has handed to the MMA warp
 
         for (int j = team; j < nb && ok; j += 2, ++n_done) {
+            const int b = j & (NSB - 1);
+            const uint32_t ts = TM_S + lane_addr + b * BN;  // score buffer of this block, this thread's lane
             if (tid == 64 || tid == 192) TRACE(1 + team, 0, j);
-            ok = mbar_wait(bar(S_FULL + team), n_done & 1, s_abort);
+            // every give-up decision is made warp-uniform: the TMEM loads and stores below are warp-collective
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(S_FULL + b), (j / NSB) & 1, s_abort));
             if (!ok) break;
             if (tid == 64 || tid == 192) TRACE(1 + team, 1, j);
             tc_fence_after();
-            float v[128];
+            float v[BN];
             tmem_ld32(ts, v);
             tmem_ld32(ts + 32, v + 32);
-            tmem_ld32(ts + 64, v + 64);
-            tmem_ld32(ts + 96, v + 96);
-            tmem_wait_ld();
             if (tid == 64 || tid == 192) TRACE(1 + team, 2, j);
             if (j * BN + BN - 1 > p.n_past + t0) {          // block reaches past the tile's first query: mask
                 const int lim = vis - j * BN;               // columns <= lim are visible
 #pragma unroll
-                for (int i = 0; i < 128; ++i) if (i > lim) v[i] = -CUDART_INF_F;
+                for (int i = 0; i < BN; ++i) if (i > lim) v[i] = -CUDART_INF_F;
             }
             float mxc[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
 #pragma unroll
-            for (int i = 0; i < 128; i += 8) {
+            for (int i = 0; i < BN; i += 8) {
 #pragma unroll
                 for (int c = 0; c < 4; ++c) mxc[c] = max3(mxc[c], v[i + 2 * c], v[i + 2 * c + 1]);
             }
@@ -376,7 +377,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             const float m_use = (m_new == -CUDART_INF_F) ? 0.f : m_new;
             const bool need = (n_done > 0) && (m_new != m_ref) && (m_ref != -CUDART_INF_F);
             if (__any_sync(0xffffffffu, need)) {
-                ok = mbar_wait(bar(PV_DONE + team), (n_done - 1) & 1, s_abort);   // O_t must be quiescent while it is rescaled
+                // O_t must be quiescent while it is rescaled: wait for this team's previous P V.  A parity wait is
+                // only meaningful for the current or the previous phase of a barrier; that holds here because
+                // the score block just received was issued after the P V two blocks back, and the tensor pipe
+                // completes in order, so PV_DONE[team] has seen at least n_done - 1 completions.
+                ok = __all_sync(0xffffffffu, mbar_wait(bar(PV_DONE + team), (n_done - 1) & 1, s_abort));
                 if (!ok) break;
                 tc_fence_after();
                 const float alpha = need ? fast_exp2(m_ref - m_new) : 1.f;
@@ -385,7 +390,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 #pragma unroll 1
                 for (int c = 0; c < 4; ++c) {
                     tmem_ld32(to + 32 * c, o);
-                    tmem_wait_ld();
 #pragma unroll
                     for (int i = 0; i < 32; ++i) o[i] *= alpha;
                     tmem_st32(to + 32 * c, o);
@@ -394,28 +398,24 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             }
             m_ref = m_new;
             if (tid == 64 || tid == 192) TRACE(1 + team, 3, j);
-            // P (fp16 pairs) goes over the first 64 columns of this thread's own score row.
-            // The special-function unit (ex2, and the fp32->fp16 conversion) has 16 lanes per SM, which for a
-            // 128 x 128 score block is as long as the two MMAs themselves.  Every other pair of elements
-            // therefore takes its exponential from a degree-3 polynomial on the FMA pipe instead.
-            uint32_t pk[64];
+            // P (fp16 pairs) goes over the first 32 columns of this thread's own score row.
+            uint32_t pk[BN / 2];
             float l4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int i = 0; i < 64; ++i) {
+            for (int i = 0; i < BN / 2; ++i) {
                 const float x0 = v[2 * i] - m_use, x1 = v[2 * i + 1] - m_use;
                 float p0, p1;
-                if (OATTN_TC_POLY && (i & 1)) { p0 = exp2_poly(x0); p1 = exp2_poly(x1); }
-                else       { p0 = fast_exp2(x0); p1 = fast_exp2(x1); }
+                if (OATTN_TC_POLY && (i & 3) == 3) { p0 = exp2_poly(x0); p1 = exp2_poly(x1); }
+                else                               { p0 = fast_exp2(x0); p1 = fast_exp2(x1); }
                 l4[i & 3] += p0 + p1;
                 pk[i] = pack_half2(p0, p1);
             }
             l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
             if (tid == 64 || tid == 192) TRACE(1 + team, 4, j);
             tmem_st32(ts, reinterpret_cast<const float*>(pk));
-            tmem_st32(ts + 32, reinterpret_cast<const float*>(pk + 32));
             asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
             tc_fence_before();
-            mbar_arrive(bar(P_FULL + team));
+            mbar_arrive(bar(P_FULL + b));
             if (tid == 64 || tid == 192) TRACE(1 + team, 5, j);
         }
         // ---- merge the two teams' (m, l, O) and write the output --------------------------------------
@@ -425,10 +425,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             mbar_arrive(bar(XCH));
             ok = mbar_wait(bar(XCH), 0, s_abort);
         }
-        if (ok && n_done > 0) ok = mbar_wait(bar(PV_DONE + team), (n_done - 1) & 1, s_abort);
-        // the other team's accumulator must be complete too before it is read
-        const int n_other = (nb - (1 - team) + 1) / 2;
-        if (ok && n_other > 0) ok = mbar_wait(bar(PV_DONE + (1 - team)), (n_other - 1) & 1, s_abort);
+        // both accumulators are final once every MMA of this CTA has completed (single-phase barrier, committed
+        // by the MMA warp after its last P V)
+        if (ok) ok = mbar_wait(bar(ALL_DONE), 0, s_abort);
+        ok = __all_sync(0xffffffffu, ok);
         if (ok) {
             tc_fence_after();
             const float2 mine = make_float2(m_ref, l), other = s_x[(1 - team) * 128 + row];
@@ -441,16 +441,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             float* dst = p.out + ((size_t)tglob * p.n_head + kvh * p.G + hg) * HD + 64 * team;
             const uint32_t o_me = TM_O + lane_addr + team * HD + 64 * team;
             const uint32_t o_ot = TM_O + lane_addr + (1 - team) * HD + 64 * team;
-            const bool ld_me = __any_sync(0xffffffffu, w_me != 0.f);   // tcgen05.ld is warp-collective
-            const bool ld_ot = __any_sync(0xffffffffu, w_ot != 0.f);   // (an unused accumulator is never read)
+            // Both accumulators are read unconditionally (the loads are warp-collective); one that never received
+            // a block holds whatever TMEM held before, and is discarded below by a select on its zero weight.
 #pragma unroll 1
             for (int c = 0; c < 2; ++c) {
                 float a[32], b2[32];
-#pragma unroll
-                for (int i = 0; i < 32; ++i) { a[i] = 0.f; b2[i] = 0.f; }
-                if (ld_me) tmem_ld32(o_me + 32 * c, a);
-                if (ld_ot) tmem_ld32(o_ot + 32 * c, b2);
-                tmem_wait_ld();
+                tmem_ld32(o_me + 32 * c, a);
+                tmem_ld32(o_ot + 32 * c, b2);
                 if (valid) {
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
@@ -520,7 +517,7 @@ cudaError_t launch_prefill_tc(const PrefillArgs& a, int sm_count, cudaStream_t s
     CUtensorMap tmQ, tmK, tmV;
     const uint64_t rowb = HD * sizeof(__half);
     if (!make_map(&tmQ, a.q16, a.n_head, a.batch, rowb, rowb * a.n_head, G, TQ)) return cudaErrorInvalidValue;
-    if (!make_map(&tmK, a.kc, rows, a.n_kv, rowb, rowb * a.n_ctx, BN, 1)) return cudaErrorInvalidValue;
+    if (!make_map(&tmK, a.kc, rows, a.n_kv, rowb, rowb * a.n_ctx, BN, 1)) return cudaErrorInvalidValue;   // 64-row blocks
     if (!make_map(&tmV, a.vc, rows, a.n_kv, rowb, rowb * a.n_ctx, BN, 1)) return cudaErrorInvalidValue;
     TcArgs t;
     t.out = a.out;

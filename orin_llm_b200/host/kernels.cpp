@@ -1,0 +1,109 @@
+// Definitions of the reference-named wrappers on top of the C ABI.  Plain C++ (no CUDA headers):
+// everything device-side lives behind include/orin_attn_b200.h.
+#include "kernels.h"
+
+#include <stdio.h>
+#include <stdlib.h>
+
+#include "../../include/orin_attn_b200.h"
+
+namespace llm::cuda {
+
+namespace {
+
+void* s_stream = nullptr;            // process-global stream, as in src/kernels.cu:1726
+void* g_decode_ws = nullptr;         // scratch handed over by attn_scratch_assign
+size_t g_decode_ws_bytes = 0;
+void* g_prefill_ws = nullptr;
+size_t g_prefill_ws_bytes = 0;
+
+inline size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+void check(int rc, const char* what) {
+    if (rc == OATTN_OK) return;
+    fprintf(stderr, "[cuda::%s] %s%s%s\n", what, oattn_strerror(rc), rc == OATTN_ERR_CUDA ? ": " : "",
+            rc == OATTN_ERR_CUDA ? oattn_last_cuda_error() : "");
+    abort();
+}
+
+} // namespace
+
+int init() { return init_device(0); }
+
+int init_device(int device) {
+    const int rc = oattn_init(device);
+    if (rc != OATTN_OK) {
+        fprintf(stderr, "[cuda::init] %s %s\n", oattn_strerror(rc), oattn_last_cuda_error());
+        return -1;
+    }
+    return 0;
+}
+
+void set_stream(void* stream) { s_stream = stream; }
+
+size_t attn_scratch_size(int n_head, int n_kv, int head_dim, int max_batch) {
+    return align256(oattn_decode_workspace_bytes(n_head, n_kv, head_dim)) +
+           align256(oattn_prefill_workspace_bytes(n_head, n_kv, head_dim, max_batch));
+}
+
+void attn_scratch_assign(void* base, int n_head, int n_kv, int head_dim, int max_batch) {
+    g_decode_ws = base;
+    g_decode_ws_bytes = oattn_decode_workspace_bytes(n_head, n_kv, head_dim);
+    g_prefill_ws = static_cast<uint8_t*>(base) + align256(g_decode_ws_bytes);
+    g_prefill_ws_bytes = oattn_prefill_workspace_bytes(n_head, n_kv, head_dim, max_batch);
+}
+
+void rope_neox_batch(float* x, int rows, int head_dim, int n_rot, float theta, int n_past, int heads, const float* ff) {
+    check(oattn_rope(x, rows, head_dim, OATTN_ROPE_NEOX, n_rot, theta, n_past, heads, nullptr, ff, s_stream), "rope_neox_batch");
+}
+void rope_normal_batch(float* x, int rows, int head_dim, int n_rot, float theta, int n_past, int heads, const float* ff) {
+    check(oattn_rope(x, rows, head_dim, OATTN_ROPE_NORMAL, n_rot, theta, n_past, heads, nullptr, ff, s_stream), "rope_normal_batch");
+}
+void rope_neox_ind(float* x, int rows, int head_dim, int n_rot, float theta, const int* d_pos, const float* ff) {
+    check(oattn_rope(x, rows, head_dim, OATTN_ROPE_NEOX, n_rot, theta, 0, 1, d_pos, ff, s_stream), "rope_neox_ind");
+}
+void rope_normal_ind(float* x, int rows, int head_dim, int n_rot, float theta, const int* d_pos, const float* ff) {
+    check(oattn_rope(x, rows, head_dim, OATTN_ROPE_NORMAL, n_rot, theta, 0, 1, d_pos, ff, s_stream), "rope_normal_ind");
+}
+
+void kv_store_batch(uint16_t* kc, uint16_t* vc, const float* k, const float* v, int heads, int head_dim, int n_ctx,
+                    int pos_base, int batch) {
+    check(oattn_kv_store(kc, vc, k, v, heads, head_dim, n_ctx, pos_base, batch, nullptr, s_stream), "kv_store_batch");
+}
+void kv_store_ind(uint16_t* kc, uint16_t* vc, const float* k, const float* v, int heads, int head_dim, int n_ctx,
+                  const int* d_pos) {
+    check(oattn_kv_store(kc, vc, k, v, heads, head_dim, n_ctx, 0, 1, d_pos, s_stream), "kv_store_ind");
+}
+void kv_shift(uint16_t* kc, uint16_t* vc, int n_layer, int n_kv, int head_dim, int n_ctx, int n_keep, int shift) {
+    check(oattn_kv_shift(kc, vc, n_layer, n_kv, head_dim, n_ctx, n_keep, shift, s_stream), "kv_shift");
+}
+
+void flash_attention(const float* q, const uint16_t* kc, const uint16_t* vc, float* out, int n_head, int n_kv,
+                     int head_dim, int n_ctx, int n_past, int batch, float scale) {
+    check(oattn_prefill(q, nullptr, nullptr, const_cast<uint16_t*>(kc), const_cast<uint16_t*>(vc), out, n_head, n_kv,
+                        head_dim, n_ctx, n_past, batch, scale, OATTN_FUSE_NONE, nullptr, g_prefill_ws, g_prefill_ws_bytes,
+                        s_stream), "flash_attention");
+}
+void flash_attention_decode_ind(const float* q, const uint16_t* kc, const uint16_t* vc, float* out, int n_head, int n_kv,
+                                int head_dim, int n_ctx, const int* d_pos, float scale) {
+    check(oattn_decode(q, nullptr, nullptr, const_cast<uint16_t*>(kc), const_cast<uint16_t*>(vc), out, n_head, n_kv,
+                       head_dim, n_ctx, d_pos, scale, OATTN_FUSE_NONE, nullptr, g_decode_ws, g_decode_ws_bytes, s_stream),
+          "flash_attention_decode_ind");
+}
+
+void attention_decode_fused(const float* q, const float* k, const float* v, uint16_t* kc, uint16_t* vc, float* out,
+                            int n_head, int n_kv, int head_dim, int n_ctx, const int* d_pos, float scale, int rope_type,
+                            int n_rot, float theta, const float* freq_factors) {
+    const oattn_rope_params rp = {rope_type, n_rot, theta, freq_factors};
+    check(oattn_decode(q, k, v, kc, vc, out, n_head, n_kv, head_dim, n_ctx, d_pos, scale, OATTN_FUSE_ALL, &rp, g_decode_ws,
+                       g_decode_ws_bytes, s_stream), "attention_decode_fused");
+}
+void attention_prefill_fused(const float* q, const float* k, const float* v, uint16_t* kc, uint16_t* vc, float* out,
+                             int n_head, int n_kv, int head_dim, int n_ctx, int n_past, int batch, float scale,
+                             int rope_type, int n_rot, float theta, const float* freq_factors) {
+    const oattn_rope_params rp = {rope_type, n_rot, theta, freq_factors};
+    check(oattn_prefill(q, k, v, kc, vc, out, n_head, n_kv, head_dim, n_ctx, n_past, batch, scale, OATTN_FUSE_ALL, &rp,
+                        g_prefill_ws, g_prefill_ws_bytes, s_stream), "attention_prefill_fused");
+}
+
+} // namespace llm::cuda

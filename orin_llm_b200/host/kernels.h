@@ -1,0 +1,60 @@
+// Host-side C++ interface of the attention path, with the reference's names and signatures.
+//
+// This header mirrors the attention-path part of the reference's src/kernels.h (lines 53-81):
+// same namespace, same function names, same argument order and meaning, raw device pointers.  A
+// maintainer of the reference keeps calling these from src/model_gpu.cu; the definitions
+// (kernels.cpp next to this file) forward to the C ABI in include/orin_attn_b200.h instead of
+// launching the sm_87 kernels of src/kernels.cu.
+//
+// Differences from the reference, all additive:
+//   - attn_scratch_size()/attn_scratch_assign(): the split-KV decode kernel and the tcgen05 prefill
+//     kernel need scratch (partial results, fp16 query staging).  It follows the reference's own
+//     scratch_size()/scratch_assign() pattern (src/kernels.cu:1753-1776): sized once, carved out
+//     of the caller's arena, handed over once.
+//   - attention_decode_fused()/attention_prefill_fused(): one call for the sequences
+//     rope(q), rope(k), kv_store, flash_attention* at src/model_gpu.cu:277-282 and 379-384.
+// Error convention as in the reference (src/common.h:10-22): a failed call prints and aborts.
+#pragma once
+
+#include <stddef.h>
+#include <stdint.h>
+
+namespace llm::cuda {
+
+int init();                       // src/kernels.cu:1730-1737 (device 0)
+int init_device(int device);      // same, for one process per GPU
+void set_stream(void* stream);    // src/kernels.cu:1726-1728
+
+size_t attn_scratch_size(int n_head, int n_kv, int head_dim, int max_batch);
+void attn_scratch_assign(void* base, int n_head, int n_kv, int head_dim, int max_batch);
+
+// --- RoPE (src/kernels.h:55-62) ---
+void rope_neox_batch(float* x, int rows, int head_dim, int n_rot, float theta, int n_past, int heads, const float* freq_factors = nullptr);
+void rope_normal_batch(float* x, int rows, int head_dim, int n_rot, float theta, int n_past, int heads, const float* freq_factors = nullptr);
+void rope_neox_ind(float* x, int rows, int head_dim, int n_rot, float theta, const int* d_pos, const float* freq_factors = nullptr);
+void rope_normal_ind(float* x, int rows, int head_dim, int n_rot, float theta, const int* d_pos, const float* freq_factors = nullptr);
+
+// --- KV cache (src/kernels.h:66-73) ---
+void kv_store_batch(uint16_t* kc, uint16_t* vc, const float* k, const float* v,
+                    int heads, int head_dim, int n_ctx, int pos_base, int batch);
+void kv_store_ind(uint16_t* kc, uint16_t* vc, const float* k, const float* v,
+                  int heads, int head_dim, int n_ctx, const int* d_pos);
+void kv_shift(uint16_t* kc, uint16_t* vc, int n_layer, int n_kv, int head_dim, int n_ctx, int n_keep, int shift);
+
+// --- Flash attention (src/kernels.h:77-81) ---
+void flash_attention(const float* q, const uint16_t* kc, const uint16_t* vc, float* out,
+                    int n_head, int n_kv, int head_dim, int n_ctx, int n_past, int batch, float scale);
+void flash_attention_decode_ind(const float* q, const uint16_t* kc, const uint16_t* vc, float* out,
+                                int n_head, int n_kv, int head_dim, int n_ctx, const int* d_pos, float scale);
+
+// --- fused call-site replacements ---
+// rope_type: 0 = normal, 1 = neox (HParams::rope_type, src/model.h:27-28).  q and k are NOT modified
+// (the reference rotates them in place; nothing downstream reads them after attention).
+void attention_decode_fused(const float* q, const float* k, const float* v, uint16_t* kc, uint16_t* vc, float* out,
+                            int n_head, int n_kv, int head_dim, int n_ctx, const int* d_pos, float scale,
+                            int rope_type, int n_rot, float theta, const float* freq_factors = nullptr);
+void attention_prefill_fused(const float* q, const float* k, const float* v, uint16_t* kc, uint16_t* vc, float* out,
+                             int n_head, int n_kv, int head_dim, int n_ctx, int n_past, int batch, float scale,
+                             int rope_type, int n_rot, float theta, const float* freq_factors = nullptr);
+
+} // namespace llm::cuda
