@@ -246,14 +246,30 @@ def run_b200(args, w):
     torch.cuda.synchronize()
 
     # ---- timed region: kernel path with everything resident in HBM ----
-    n_prof = min(args.steps * layers, 4096)
-    ops.profile_enable(n_prof)
+    # The step is replayed from a CUDA graph, as the reference replays its decode step
+    # (src/model_gpu.cu:295-344); --no-graph launches it eagerly instead.
+    if args.no_graph:
+        n_prof = min(args.steps * layers, 4096)
+        ops.profile_enable(n_prof)
+        run_step = step
+        l0 = ops.launch_count()
+    else:
+        ops.profile_enable(layers)            # one event pair per layer call, recorded as graph nodes
+        l0 = ops.launch_count()
+        cap_stream = torch.cuda.Stream()
+        cap_stream.wait_stream(torch.cuda.current_stream())
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=cap_stream):
+            step()
+        launches_per_step = ops.launch_count() - l0
+        graph.replay()
+        torch.cuda.synchronize()
+        run_step = graph.replay
     sampler = ClockSampler(local_rank)
-    l0 = ops.launch_count()
     sampler.start()
-    total_ms = timed(step, args.steps)
+    total_ms = timed(run_step, args.steps)
     clocks = sampler.stop()
-    launches = ops.launch_count() - l0
+    launches = (ops.launch_count() - l0) if args.no_graph else launches_per_step * args.steps
     kern_ms = ops.profile_collect()
     ops.profile_enable(0)
     ms_per_step = total_ms / args.steps
@@ -332,6 +348,7 @@ def run_b200(args, w):
         "vs_baseline": None, "dtype": "f16", "data": "synthetic",
         "config": {"workload": args.workload, "n_head": n_head, "n_kv": n_kv, "head_dim": hd, "layers_per_step": layers,
                    "kv_len": L, "kv_rows_per_gpu": n_loc, "parallelism": "kv-split x%d" % world,
+                   "launch": "eager" if args.no_graph else "cuda graph replay of the step",
                    "l2": "inputs larger than L2: each of the %d layer calls of a step reads its own %.0f MiB of KV" % (
                        layers, per_launch_bytes / 2**20)},
         "pct_of_8tbs": 100.0 * value / (8000.0 * world),
@@ -424,6 +441,7 @@ def main():
     ap.add_argument("--workload", default="decode_3b_L1048576", choices=sorted(WORKLOADS) + sorted(PREFILL_WORKLOADS))
     ap.add_argument("--layers", type=int, default=None, help="override the layer calls per step")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="launch the step eagerly instead of replaying a CUDA graph")
     args = ap.parse_args()
     if args.workload in PREFILL_WORKLOADS:
         w = dict(PREFILL_WORKLOADS[args.workload])

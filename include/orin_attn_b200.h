@@ -164,7 +164,8 @@ int oattn_set_decode_min_tiles(int tiles);
  * CUDA events on the call's stream, for the first n calls.  oattn_profile_collect waits for those
  * events, writes the elapsed milliseconds of each recorded call to ms (host, `capacity` floats),
  * stores the count in *n_written and rearms the counter.  oattn_profile_enable(0) destroys the
- * events.  Not for use during stream capture. */
+ * events.  When the call is being captured into a CUDA graph the events are recorded as external
+ * event nodes: after a replay they hold the timings of that replay. */
 int oattn_profile_enable(int max_records);
 int oattn_profile_collect(float* ms, int capacity, int* n_written);
 

@@ -475,10 +475,16 @@ cudaError_t launch_decode(const DecodeArgs& a, cudaStream_t stream, unsigned lon
     const int G = a.n_head / a.n_kv;
     const bool wide = G > 8;
     cudaError_t e;
-    if (ev_start) cudaEventRecord(ev_start, stream);
+    // inside a stream capture the timing events become external event-record nodes of the graph
+    unsigned ev_flags = cudaEventRecordDefault;
+    if (ev_start || ev_stop) {
+        cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(stream, &cs) == cudaSuccess && cs == cudaStreamCaptureStatusActive) ev_flags = cudaEventRecordExternal;
+    }
+    if (ev_start) cudaEventRecordWithFlags(ev_start, stream, ev_flags);
     if (a.head_dim == 128) e = wide ? launch_split<128, true>(a, stream) : launch_split<128, false>(a, stream);
     else                   e = wide ? launch_split<64, true>(a, stream) : launch_split<64, false>(a, stream);
-    if (ev_stop) cudaEventRecord(ev_stop, stream);
+    if (ev_stop) cudaEventRecordWithFlags(ev_stop, stream, ev_flags);
     if (e != cudaSuccess) return e;
     CombineArgs c;
     c.o_base = a.ws_o;

@@ -7,27 +7,25 @@
 //
 // One CTA = one 128-row query tile of ONE kv head; a row is a (token, head-in-group) pair, row
 // R -> token t0 + R/G, head kvh*G + R%G (G = n_head/n_kv must divide 128), so a single pass over the
-// kv head's K/V rows serves all G query heads of 128/G tokens.  The KV sequence is walked in blocks of
-// 64 rows.  320 threads in three roles:
-//   warp 0   (one lane)  TMA producer: Q tile once, then 64-row K blocks (six-stage ring) and V blocks
-//                        (four-stage ring) with cp.async.bulk.tensor, 128-byte swizzle, no multicast;
-//                        rows past the chunk are outside the tensor map and arrive as zeros
-//   warp 1   (one lane)  tcgen05.mma issuer: S_j = Q K_j^T (M128 N64, K16 x8, both operands from shared
-//                        memory) into one of FOUR 64-column TMEM score buffers, so that four score blocks
-//                        are in flight; O_(j mod 2) += P_j V_j (M128 N128, K16 x4) with P read straight
-//                        from TMEM (it overwrites the first 32 columns of its own score buffer as packed
-//                        fp16 pairs) and V as MN-major B operand from shared memory; tcgen05.commit
-//                        signals the mbarriers
+// kv head's K/V rows serves all G query heads of 128/G tokens.  320 threads in three roles:
+//   warp 0   (one lane)  TMA producer: Q tile once, then 128-row K and V blocks into two-stage rings
+//                        (cp.async.bulk.tensor, 128-byte swizzle, no multicast); rows past the
+//                        chunk are outside the tensor map and arrive as zeros
+//   warp 1   (one lane)  tcgen05.mma issuer: S_j = Q K_j^T (M128 N128 K16 x8, both operands from shared
+//                        memory) into one of two TMEM score buffers; O += P_j V_j with P read straight
+//                        from TMEM (it overwrites the first 64 columns of its own score buffer as packed
+//                        fp16 pairs) and V as MN-major B operand from shared memory, into a TMEM
+//                        accumulator; tcgen05.commit signals the mbarriers
 //   warps 2-5, 6-9       two softmax teams, one thread per row each.  Team t takes KV blocks j = t, t+2, ...
-//                        and owns accumulator O_t with its own running reference max and row sum (an
-//                        in-CTA split of the KV sequence by block parity), so the teams never wait on each
-//                        other.  Per block: tcgen05.ld of the 64-column score row, causal mask, row max,
-//                        lazy rescale of O_t (only when the max grows by more than 2^4), exp2, fp16 P stored
-//                        back to TMEM (tcgen05.st).  At the end the two (m, l, O) are merged log-sum-exp
-//                        style and O/l goes to global memory.
-// The exponentials run on the 16-lane special-function unit, which for a 128 x 128 score block takes about
-// as long as the MMAs themselves; with four score buffers both teams work while the tensor pipe runs ahead,
-// so the loop is bound by the tensor pipe, not by the S -> softmax -> P V dependency chain.
+//                        and owns score buffer t and its OWN accumulator O_t with its own running
+//                        reference max and row sum, so consecutive blocks never wait on each other (an
+//                        in-CTA split of the KV sequence by block parity).  Per block: tcgen05.ld of the
+//                        128-column score row, causal mask, row max, lazy rescale of O_t (only when the max
+//                        grows by more than 2^8), exp2, fp16 P stored back to TMEM (tcgen05.st) where the
+//                        next MMA takes it as its A operand.  At the end the two (m, l, O) are merged
+//                        log-sum-exp style and O/l goes to global memory.
+// S_{j+1} is issued before P_j V_j, so the tensor pipe computes the next scores while a softmax team
+// works on the current ones, and each team has two MMA block times for one block of softmax.
 //
 // Every mbarrier wait is bounded: after about a second without progress the kernel raises an abort
 // flag, every role leaves its loop, outstanding copies and MMAs are drained (bounded again), TMEM is
@@ -41,30 +39,28 @@ namespace oattn {
 namespace {
 
 constexpr int kThreads = 320;
-constexpr int BM = 128, BN = 64, HD = 128;
-constexpr int QSLAB = 128 * 128;                // bytes of one 128-row x 64-element fp16 slab (Q)
-constexpr int QTILE = 2 * QSLAB;
-constexpr int SLAB = BN * 128;                  // bytes of one 64-row x 64-element fp16 slab (K, V)
-constexpr int TILE = 2 * SLAB;                  // a 64 x 128 fp16 block = two slabs
-constexpr int NK = 6, NV = 4;                   // K and V ring depths
-constexpr int NSB = 4;                          // score buffers in TMEM
+constexpr int BM = 128, BN = 128, HD = 128;
+constexpr int SLAB = 128 * 128;                 // bytes of one 128-row x 64-element fp16 slab
+constexpr int TILE = 2 * SLAB;                  // a 128 x 128 fp16 tile = two slabs
 constexpr int OFF_Q = 0;
-constexpr int OFF_K = OFF_Q + QTILE;
-constexpr int OFF_V = OFF_K + NK * TILE;
-constexpr int OFF_BAR = OFF_V + NV * TILE;
-constexpr int OFF_MX = OFF_BAR + 512;           // float2 [2 teams][128 rows]: (m, l) exchanged at the end
+constexpr int NST = 2;                          // K and V ring depth
+constexpr int OFF_K = OFF_Q + TILE;
+constexpr int OFF_V = OFF_K + NST * TILE;
+constexpr int OFF_BAR = OFF_V + NST * TILE;
+constexpr int OFF_MX = OFF_BAR + 256;           // float2 [2 teams][128 rows]: (m, l) exchanged at the end
 constexpr int SMEM_BYTES = OFF_MX + 2048 + 1024;   // + slack for 1024-byte alignment
 static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 constexpr long long kWaitCycles = 2000000000LL;    // ~1 s
 constexpr long long kDrainCycles = 200000000LL;    // ~0.1 s
 constexpr float kRescaleThreshold = 4.0f;          // log2 units: P stays below 2^4 relative to the reference max
 
-enum Bar { Q_FULL = 0, K_FULL = 1, K_EMPTY = K_FULL + NK, V_FULL = K_EMPTY + NK, V_EMPTY = V_FULL + NV, S_FULL = V_EMPTY + NV,
-           P_FULL = S_FULL + NSB, PV_DONE = P_FULL + NSB, DRAIN = PV_DONE + 2, XCH = DRAIN + 1, ALL_DONE = XCH + 1, NBAR = ALL_DONE + 1 };
-static_assert(NBAR * 8 + 16 <= 512, "barrier block");
+enum Bar { Q_FULL = 0, K_FULL = 1, K_EMPTY = 4, V_FULL = 7, V_EMPTY = 10, S_FULL = 13, P_FULL = 15, PV_DONE = 17, DRAIN = 19, XCH = 20, ALL_DONE = 21, NBAR = 22 };
 
 #ifndef OATTN_TC_POLY
 #define OATTN_TC_POLY 0
+#endif
+#ifndef OATTN_TC_FAST
+#define OATTN_TC_FAST 0
 #endif
 
 #ifdef OATTN_TC_TRACE
@@ -171,6 +167,33 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
     asm("max.f32 %0, %1, %2, %3;\n" : "=f"(d) : "f"(a), "f"(b), "f"(c));
     return d;
 }
+// Packed pairs of fp32 (sm_100 f32x2 arithmetic): one instruction for two lanes of work.
+struct f2 { uint64_t u; };
+__device__ __forceinline__ f2 pack2(float a, float b) { f2 r; asm("mov.b64 %0, {%1, %2};\n" : "=l"(r.u) : "f"(a), "f"(b)); return r; }
+__device__ __forceinline__ void unpack2(f2 x, float& a, float& b) { asm("mov.b64 {%0, %1}, %2;\n" : "=f"(a), "=f"(b) : "l"(x.u)); }
+__device__ __forceinline__ f2 add2(f2 a, f2 b) { f2 r; asm("add.f32x2 %0, %1, %2;\n" : "=l"(r.u) : "l"(a.u), "l"(b.u)); return r; }
+__device__ __forceinline__ f2 sub2(f2 a, f2 b) { f2 r; asm("sub.f32x2 %0, %1, %2;\n" : "=l"(r.u) : "l"(a.u), "l"(b.u)); return r; }
+__device__ __forceinline__ f2 fma2(f2 a, f2 b, f2 c) { f2 r; asm("fma.rn.f32x2 %0, %1, %2, %3;\n" : "=l"(r.u) : "l"(a.u), "l"(b.u), "l"(c.u)); return r; }
+
+// (2^x0, 2^x1) on the FMA pipe (see exp2_poly): the float steps are packed, the exponent insertion is one integer
+// multiply-add per element (n * 2^23 + bits).
+__device__ __forceinline__ void exp2_poly2(f2 x, float& p0, float& p1) {
+    float x0, x1;
+    unpack2(x, x0, x1);
+    const f2 xc = pack2(fmaxf(x0, -125.f), fmaxf(x1, -125.f));
+    const f2 magic = pack2(12582912.f, 12582912.f);
+    const f2 fi = add2(xc, magic);
+    const f2 f = sub2(xc, sub2(fi, magic));
+    f2 q = fma2(pack2(0.05508868f, 0.05508868f), f, pack2(0.24260405f, 0.24260405f));
+    q = fma2(q, f, pack2(0.69327624f, 0.69327624f));
+    q = fma2(q, f, pack2(0.99992894f, 0.99992894f));
+    float q0, q1, n0, n1;
+    unpack2(q, q0, q1);
+    unpack2(fi, n0, n1);
+    p0 = __int_as_float(__float_as_int(n0) * 8388608 + __float_as_int(q0));
+    p1 = __int_as_float(__float_as_int(n1) * 8388608 + __float_as_int(q1));
+}
+
 // 2^x without the special-function unit: x = n + f with n = round(x), f in [-0.5, 0.5]; 2^f from a
 // degree-3 polynomial (relative error 7.7e-5, well below the fp16 rounding of P); 2^n by adding n to the
 // exponent field.  Inputs below -125 (including -inf for masked scores) give ~2^-125, which becomes 0 in fp16.
@@ -193,10 +216,9 @@ __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t addr) {
     return (uint64_t)((addr & 0x3FFFF) >> 4) | ((uint64_t)(SLAB >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
            ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
 }
-// Instruction descriptor: fp32 accumulate, fp16 A and B, A K-major, M = 128; N = 64 for S, 128 for P V;
-// bit 16 = B is MN-major.
+// Instruction descriptor: fp32 accumulate, fp16 A and B, A K-major, N = 128, M = 128; bit 16 = B is MN-major.
 constexpr uint32_t IDESC_S = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-constexpr uint32_t IDESC_PV = (1u << 4) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+constexpr uint32_t IDESC_PV = IDESC_S | (1u << 16);
 
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -220,12 +242,19 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 
     if (tid == 0) {
         mbar_init(bar(Q_FULL), 1);
-        for (int s = 0; s < NK; ++s) { mbar_init(bar(K_FULL + s), 1); mbar_init(bar(K_EMPTY + s), 1); }
-        for (int s = 0; s < NV; ++s) { mbar_init(bar(V_FULL + s), 1); mbar_init(bar(V_EMPTY + s), 1); }
-        for (int s = 0; s < NSB; ++s) { mbar_init(bar(S_FULL + s), 1); mbar_init(bar(P_FULL + s), 128); }
+        for (int s = 0; s < NST; ++s) {
+            mbar_init(bar(K_FULL + s), 1);
+            mbar_init(bar(K_EMPTY + s), 1);
+            mbar_init(bar(V_FULL + s), 1);
+            mbar_init(bar(V_EMPTY + s), 1);
+        }
+        mbar_init(bar(S_FULL), 1);
+        mbar_init(bar(S_FULL + 1), 1);
+        mbar_init(bar(P_FULL), 4);
+        mbar_init(bar(P_FULL + 1), 4);
+        mbar_init(bar(XCH), 256);
         mbar_init(bar(PV_DONE), 1);
         mbar_init(bar(PV_DONE + 1), 1);
-        mbar_init(bar(XCH), 256);
         mbar_init(bar(DRAIN), 1);
         mbar_init(bar(ALL_DONE), 1);
         *s_abort = 0;
@@ -240,19 +269,19 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *s_tmem;
-    const uint32_t TM_S = tmem, TM_O = tmem + 256;   // score buffer b at TM_S + 64 b, O_t at TM_O + 128 t
+    const uint32_t TM_S = tmem, TM_O = tmem + 256;   // S_t at TM_S + 128 t, O_t at TM_O + 128 t
 
     if (warp == 0) {
         // ---------------------------------------------------------------- TMA producer
         if (lane == 0) {
             bool ok = true;
-            int k_issued[NK] = {}, v_issued[NV] = {};
-            mbar_expect_tx(bar(Q_FULL), QTILE);
+            int k_issued[NST] = {}, v_issued[NST] = {};
+            mbar_expect_tx(bar(Q_FULL), TILE);
             tma_load_3d(sbase + OFF_Q, &tmQ, 0, kvh * p.G, t0, bar(Q_FULL));
-            tma_load_3d(sbase + OFF_Q + QSLAB, &tmQ, 64, kvh * p.G, t0, bar(Q_FULL));
+            tma_load_3d(sbase + OFF_Q + SLAB, &tmQ, 64, kvh * p.G, t0, bar(Q_FULL));
             auto load_k = [&](int j) {
-                const int s = j % NK;
-                if (j >= NK) ok = mbar_wait(bar(K_EMPTY + s), ((j / NK) - 1) & 1, s_abort);
+                const int s = j % NST;
+                if (j >= NST) ok = mbar_wait(bar(K_EMPTY + s), ((j / NST) - 1) & 1, s_abort);
                 if (!ok) return;
                 mbar_expect_tx(bar(K_FULL + s), TILE);
                 tma_load_3d(sbase + OFF_K + s * TILE, &tmK, 0, j * BN, kvh, bar(K_FULL + s));
@@ -260,27 +289,26 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 ++k_issued[s];
             };
             auto load_v = [&](int j) {
-                const int s = j % NV;
-                if (j >= NV) ok = mbar_wait(bar(V_EMPTY + s), ((j / NV) - 1) & 1, s_abort);
+                const int s = j % NST;
+                if (j >= NST) ok = mbar_wait(bar(V_EMPTY + s), ((j / NST) - 1) & 1, s_abort);
                 if (!ok) return;
                 mbar_expect_tx(bar(V_FULL + s), TILE);
                 tma_load_3d(sbase + OFF_V + s * TILE, &tmV, 0, j * BN, kvh, bar(V_FULL + s));
                 tma_load_3d(sbase + OFF_V + s * TILE + SLAB, &tmV, 64, j * BN, kvh, bar(V_FULL + s));
                 ++v_issued[s];
             };
-            // the MMA warp consumes K_0..K_3 first, then alternates V_j, K_(j+4)
-            for (int j = 0; j < NSB && j < nb && ok; ++j) load_k(j);
+            load_k(0);
             for (int j = 0; j < nb && ok; ++j) {
-                load_v(j);
-                if (ok && j + NSB < nb) load_k(j + NSB);
+                if (j + 1 < nb) load_k(j + 1);
+                if (ok) load_v(j);
             }
             if (*s_abort) {
                 // make sure no copy is still writing this CTA's shared memory when it exits
                 mbar_drain(bar(Q_FULL), 0);
-                for (int s = 0; s < NK; ++s)
+                for (int s = 0; s < NST; ++s) {
                     if (k_issued[s]) mbar_drain(bar(K_FULL + s), (k_issued[s] - 1) & 1);
-                for (int s = 0; s < NV; ++s)
                     if (v_issued[s]) mbar_drain(bar(V_FULL + s), (v_issued[s] - 1) & 1);
+                }
             }
         }
         __syncwarp();
@@ -289,40 +317,39 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         if (lane == 0) {
             bool ok = mbar_wait(bar(Q_FULL), 0, s_abort);
             auto issue_s = [&](int j) {
-                const int s = j % NK, b = j & (NSB - 1);
-                ok = mbar_wait(bar(K_FULL + s), (j / NK) & 1, s_abort);
+                const int s = j % NST, b = j & 1;
+                ok = mbar_wait(bar(K_FULL + s), (j / NST) & 1, s_abort);
                 if (!ok) return;
                 TRACE(0, 0, j);
                 tc_fence_after();
 #pragma unroll
                 for (int kk = 0; kk < HD / 16; ++kk) {
-                    const uint32_t a_off = (kk >> 2) * QSLAB + (kk & 3) * 32;
-                    const uint32_t b_off = (kk >> 2) * SLAB + (kk & 3) * 32;
-                    tc_mma(TM_S + b * BN, desc_kmajor(sbase + OFF_Q + a_off), desc_kmajor(sbase + OFF_K + s * TILE + b_off), IDESC_S, kk > 0);
+                    const uint32_t off = (kk >> 2) * SLAB + (kk & 3) * 32;
+                    tc_mma(TM_S + b * BN, desc_kmajor(sbase + OFF_Q + off), desc_kmajor(sbase + OFF_K + s * TILE + off), IDESC_S, kk > 0);
                 }
                 tc_commit(bar(S_FULL + b));
                 tc_commit(bar(K_EMPTY + s));
             };
-            for (int j = 0; j < NSB && j < nb && ok; ++j) issue_s(j);
+            if (ok) issue_s(0);
             for (int j = 0; j < nb && ok; ++j) {
-                const int b = j & (NSB - 1), t = j & 1, sv = j % NV;
-                ok = mbar_wait(bar(P_FULL + b), (j / NSB) & 1, s_abort);
+                if (j + 1 < nb) issue_s(j + 1);
+                if (!ok) break;
+                const int s = j & 1, sv = j % NST;
+                ok = mbar_wait(bar(P_FULL + s), (j >> 1) & 1, s_abort);
                 TRACE(0, 1, j);
-                if (ok) ok = mbar_wait(bar(V_FULL + sv), (j / NV) & 1, s_abort);
+                if (ok) ok = mbar_wait(bar(V_FULL + sv), (j / NST) & 1, s_abort);
                 if (!ok) break;
                 TRACE(0, 2, j);
                 tc_fence_after();
 #pragma unroll
                 for (int kk = 0; kk < BN / 16; ++kk) {
                     const uint32_t b_off = kk * 2048;                             // V: 16 rows of 128 B per k-step
-                    tc_mma_ts(TM_O + t * HD, TM_S + b * BN + kk * 8, desc_mnmajor(sbase + OFF_V + sv * TILE + b_off), IDESC_PV,
+                    tc_mma_ts(TM_O + s * HD, TM_S + s * BN + kk * 8, desc_mnmajor(sbase + OFF_V + sv * TILE + b_off), IDESC_PV,
                               (j > 1 || kk > 0) ? 1u : 0u);
                 }
-                tc_commit(bar(PV_DONE + t));
+                tc_commit(bar(PV_DONE + s));
                 tc_commit(bar(V_EMPTY + sv));
                 TRACE(0, 3, j);
-                // score buffer b is free again once P_j V_j has been issued (the tensor pipe runs in order)
-                if (j + NSB < nb) issue_s(j + NSB);
             }
             if (ok) tc_commit(bar(ALL_DONE));
             if (*s_abort) {
@@ -341,32 +368,33 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         const bool valid = tok < ntok;
         const int vis = p.n_past + tglob;                   // last visible cache row
         const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
+        const uint32_t ts = TM_S + lane_addr + team * BN;   // this team's score buffer, this thread's lane
         const uint32_t to = TM_O + lane_addr + team * HD;   // this team's accumulator
         float m_ref = -CUDART_INF_F, l = 0.f;
         bool ok = true;
         int n_done = 0;                                     // blocks this team has handed to the MMA warp
 
         for (int j = team; j < nb && ok; j += 2, ++n_done) {
-            const int b = j & (NSB - 1);
-            const uint32_t ts = TM_S + lane_addr + b * BN;  // score buffer of this block, this thread's lane
             if (tid == 64 || tid == 192) TRACE(1 + team, 0, j);
             // every give-up decision is made warp-uniform: the TMEM loads and stores below are warp-collective
-            ok = __all_sync(0xffffffffu, mbar_wait(bar(S_FULL + b), (j / NSB) & 1, s_abort));
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(S_FULL + team), n_done & 1, s_abort));
             if (!ok) break;
             if (tid == 64 || tid == 192) TRACE(1 + team, 1, j);
             tc_fence_after();
-            float v[BN];
+            float v[128];
             tmem_ld32(ts, v);
             tmem_ld32(ts + 32, v + 32);
+            tmem_ld32(ts + 64, v + 64);
+            tmem_ld32(ts + 96, v + 96);
             if (tid == 64 || tid == 192) TRACE(1 + team, 2, j);
             if (j * BN + BN - 1 > p.n_past + t0) {          // block reaches past the tile's first query: mask
                 const int lim = vis - j * BN;               // columns <= lim are visible
 #pragma unroll
-                for (int i = 0; i < BN; ++i) if (i > lim) v[i] = -CUDART_INF_F;
+                for (int i = 0; i < 128; ++i) if (i > lim) v[i] = -CUDART_INF_F;
             }
             float mxc[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
 #pragma unroll
-            for (int i = 0; i < BN; i += 8) {
+            for (int i = 0; i < 128; i += 8) {
 #pragma unroll
                 for (int c = 0; c < 4; ++c) mxc[c] = max3(mxc[c], v[i + 2 * c], v[i + 2 * c + 1]);
             }
@@ -398,24 +426,57 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             }
             m_ref = m_new;
             if (tid == 64 || tid == 192) TRACE(1 + team, 3, j);
-            // P (fp16 pairs) goes over the first 32 columns of this thread's own score row.
-            uint32_t pk[BN / 2];
+            // P (fp16 pairs) goes over the first 64 columns of this thread's own score row.
+            // The special-function unit (ex2, and the fp32->fp16 conversion) has 16 lanes per SM, which for a
+            // 128 x 128 score block is as long as the two MMAs themselves.  Every other pair of elements
+            // therefore takes its exponential from a degree-3 polynomial on the FMA pipe instead.
+            uint32_t pk[64];
+#if OATTN_TC_FAST
+            // Half of the pairs take 2^x from the special-function unit, the other half from the polynomial on the
+            // FMA pipe; subtraction and row sums run as packed f32x2 instructions.
+            const f2 m2 = pack2(m_use, m_use);
+            f2 lacc[2] = {pack2(0.f, 0.f), pack2(0.f, 0.f)};
+#pragma unroll
+            for (int i = 0; i < 64; ++i) {
+                const f2 x = sub2(pack2(v[2 * i], v[2 * i + 1]), m2);
+                float p0, p1;
+                if (i & 1) {
+                    exp2_poly2(x, p0, p1);
+                } else {
+                    float x0, x1;
+                    unpack2(x, x0, x1);
+                    p0 = fast_exp2(x0);
+                    p1 = fast_exp2(x1);
+                }
+                lacc[i & 1] = add2(lacc[i & 1], pack2(p0, p1));
+                pk[i] = pack_half2(p0, p1);
+            }
+            {
+                float a0, a1, b0, b1;
+                unpack2(lacc[0], a0, a1);
+                unpack2(lacc[1], b0, b1);
+                l += (a0 + a1) + (b0 + b1);
+            }
+#else
             float l4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int i = 0; i < BN / 2; ++i) {
+            for (int i = 0; i < 64; ++i) {
                 const float x0 = v[2 * i] - m_use, x1 = v[2 * i + 1] - m_use;
                 float p0, p1;
-                if (OATTN_TC_POLY && (i & 3) == 3) { p0 = exp2_poly(x0); p1 = exp2_poly(x1); }
-                else                               { p0 = fast_exp2(x0); p1 = fast_exp2(x1); }
+                if (OATTN_TC_POLY && (i & 1)) { p0 = exp2_poly(x0); p1 = exp2_poly(x1); }
+                else       { p0 = fast_exp2(x0); p1 = fast_exp2(x1); }
                 l4[i & 3] += p0 + p1;
                 pk[i] = pack_half2(p0, p1);
             }
             l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+#endif
             if (tid == 64 || tid == 192) TRACE(1 + team, 4, j);
             tmem_st32(ts, reinterpret_cast<const float*>(pk));
+            tmem_st32(ts + 32, reinterpret_cast<const float*>(pk + 32));
             asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
             tc_fence_before();
-            mbar_arrive(bar(P_FULL + b));
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(P_FULL + team));      // one arrival per warp (the barrier counts 4)
             if (tid == 64 || tid == 192) TRACE(1 + team, 5, j);
         }
         // ---- merge the two teams' (m, l, O) and write the output --------------------------------------
@@ -517,7 +578,7 @@ cudaError_t launch_prefill_tc(const PrefillArgs& a, int sm_count, cudaStream_t s
     CUtensorMap tmQ, tmK, tmV;
     const uint64_t rowb = HD * sizeof(__half);
     if (!make_map(&tmQ, a.q16, a.n_head, a.batch, rowb, rowb * a.n_head, G, TQ)) return cudaErrorInvalidValue;
-    if (!make_map(&tmK, a.kc, rows, a.n_kv, rowb, rowb * a.n_ctx, BN, 1)) return cudaErrorInvalidValue;   // 64-row blocks
+    if (!make_map(&tmK, a.kc, rows, a.n_kv, rowb, rowb * a.n_ctx, BN, 1)) return cudaErrorInvalidValue;
     if (!make_map(&tmV, a.vc, rows, a.n_kv, rowb, rowb * a.n_ctx, BN, 1)) return cudaErrorInvalidValue;
     TcArgs t;
     t.out = a.out;
