@@ -116,6 +116,23 @@ int oattn_decode(const float* q, const float* k_new, const float* v_new, uint16_
                  float* out, int n_head, int n_kv, int head_dim, int n_ctx, const int* d_pos, float scale,
                  int fuse, const oattn_rope_params* rope, void* workspace, size_t workspace_bytes, void* stream);
 
+/* No counterpart in the reference.  Same result as oattn_decode with OATTN_FUSE_NONE, for hosts that are not
+ * able to give the library a workspace: code that runs where device allocation is forbidden or unavailable --
+ * inside a plugin whose host owns all device memory and hands out none, in a callback that must not call
+ * cudaMalloc, or late in a process whose memory is fully committed.  The per-split partial results go to a block
+ * of oattn_decode_noalloc_max_bytes() (2 MiB) that is part of the library image in device memory; every GPU that
+ * loads the library holds that block until the process ends.  Shapes whose partials do not fit
+ * (n_head * splits * (head_dim + 2) * 4 bytes, splits = 2 * SMs / n_kv) are refused with OATTN_ERR_WORKSPACE and a
+ * message in oattn_last_cuda_error(); nothing is allocated or freed, here or later.  The first call on each device
+ * looks up the block's device address (device must be current, as after oattn_init); make that first call outside
+ * any stream capture.  All calls on a device share the one block and it keeps what the previous call wrote: nothing
+ * in it has to start at zero (each call overwrites the slots it later reads), but two calls that run on the GPU at
+ * the same time -- different streams, or a graph replay overlapping an eager call -- would overwrite each other's
+ * partials, so keep calls to this entry point ordered on one stream. */
+size_t oattn_decode_noalloc_max_bytes(void);
+int oattn_decode_noalloc(const float* q, const uint16_t* kc, const uint16_t* vc, float* out, int n_head, int n_kv,
+                         int head_dim, int n_ctx, const int* d_pos, float scale, void* stream);
+
 /* Multi-GPU building block (no reference counterpart as a function; the arithmetic is the
  * cross-warp merge of src/kernels.cu:1300-1342 lifted to KV slices).  Attends q over the LOCAL
  * cache rows [0, *d_len) and writes one un-normalised partial per head:

@@ -20,6 +20,7 @@ PART_PAD = 4
 EXPORTS = [
     "oattn_strerror", "oattn_last_cuda_error", "oattn_init", "oattn_sm_count", "oattn_rope",
     "oattn_kv_store", "oattn_kv_shift", "oattn_decode_workspace_bytes", "oattn_decode",
+    "oattn_decode_noalloc_max_bytes", "oattn_decode_noalloc",
     "oattn_decode_partial", "oattn_combine", "oattn_prefill_workspace_bytes", "oattn_prefill",
     "oattn_prefill_status",
     "oattn_set_prefill_impl", "oattn_set_decode_min_tiles", "oattn_profile_enable", "oattn_profile_collect",
@@ -65,6 +66,9 @@ def lib():
     L.oattn_decode_workspace_bytes.restype = sz
     L.oattn_decode_workspace_bytes.argtypes = [i, i, i]
     L.oattn_decode.argtypes = [vp, vp, vp, vp, vp, vp, i, i, i, i, vp, f, i, rp, vp, sz, vp]
+    L.oattn_decode_noalloc_max_bytes.restype = sz
+    L.oattn_decode_noalloc_max_bytes.argtypes = []
+    L.oattn_decode_noalloc.argtypes = [vp, vp, vp, vp, i, i, i, i, vp, f, vp]
     L.oattn_decode_partial.argtypes = [vp, vp, vp, vp, i, i, i, i, vp, f, vp, sz, vp]
     L.oattn_combine.argtypes = [vp, i, vp, i, i, vp]
     L.oattn_prefill_workspace_bytes.restype = sz

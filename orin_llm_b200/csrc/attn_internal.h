@@ -31,6 +31,11 @@ struct DecodeArgs {
     int emit_partial;      // combine writes the un-normalised record instead of the normalised output
 };
 
+// Size of the scratch block built into the library for oattn_decode_noalloc, and its device address on the
+// current device (looked up once per device).
+constexpr size_t kStaticScratchBytes = 2u << 20;
+cudaError_t decode_static_scratch(void** ptr);
+
 // Number of KV splits per kv head the decode launch uses on a device with `sm_count` SMs.
 int decode_num_splits(int n_kv, int sm_count);
 cudaError_t decode_set_attributes();

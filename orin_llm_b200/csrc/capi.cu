@@ -184,6 +184,27 @@ int oattn_decode(const float* q, const float* k_new, const float* v_new, uint16_
                          workspace, workspace_bytes, stream);
 }
 
+size_t oattn_decode_noalloc_max_bytes(void) { return kStaticScratchBytes; }
+
+int oattn_decode_noalloc(const float* q, const uint16_t* kc, const uint16_t* vc, float* out, int n_head, int n_kv,
+                         int head_dim, int n_ctx, const int* d_pos, float scale, void* stream) {
+    if (!device_ready()) return OATTN_ERR_DEVICE;
+    int rc = check_shape(n_head, n_kv, head_dim);
+    if (rc != OATTN_OK) return rc;
+    const DecodeWs w = decode_ws(n_head, n_kv, head_dim, g_dev[g_cur].sm_count);
+    if (w.total > kStaticScratchBytes) {
+        snprintf(g_cuda_err, sizeof(g_cuda_err),
+                 "oattn_decode_noalloc: this shape needs %zu bytes of scratch, the built-in block holds %zu; use oattn_decode "
+                 "with a caller-provided workspace", w.total, (size_t)kStaticScratchBytes);
+        return OATTN_ERR_WORKSPACE;
+    }
+    void* scratch = nullptr;
+    cudaError_t e = decode_static_scratch(&scratch);     // first call on a device looks the address up
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(built-in scratch)");
+    return decode_common(q, nullptr, nullptr, const_cast<uint16_t*>(kc), const_cast<uint16_t*>(vc), out, n_head, n_kv,
+                         head_dim, n_ctx, d_pos, 1, scale, OATTN_FUSE_NONE, nullptr, 0, scratch, w.total, stream);
+}
+
 int oattn_decode_partial(const float* q, const uint16_t* kc, const uint16_t* vc, float* part, int n_head, int n_kv,
                          int head_dim, int n_ctx, const int* d_len, float scale, void* workspace, size_t workspace_bytes,
                          void* stream) {

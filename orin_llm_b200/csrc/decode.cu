@@ -451,6 +451,29 @@ cudaError_t launch_split(const DecodeArgs& a, cudaStream_t stream) {
 
 } // namespace
 
+// ---- built-in scratch for callers that cannot allocate --------------------------------------------------
+// A fixed block of device memory that is part of the library image: every GPU that loads the library
+// carries it until the process exits.  In host code the name below is only a handle for the runtime, not a
+// device address; the address a kernel can use comes from cudaGetSymbolAddress, asked once per device with
+// that device current.
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+static void* g_static_scratch_addr[64] = {};
+
+cudaError_t decode_static_scratch(void** ptr) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if (!g_static_scratch_addr[dev]) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess) return e;
+        g_static_scratch_addr[dev] = p;
+    }
+    *ptr = g_static_scratch_addr[dev];
+    return cudaSuccess;
+}
+
 int decode_num_splits(int n_kv, int sm_count) {
     int s = (2 * sm_count) / (n_kv > 0 ? n_kv : 1);
     if (s < 1) s = 1;
