@@ -7,25 +7,28 @@
 //
 // One CTA = one 128-row query tile of ONE kv head; a row is a (token, head-in-group) pair, row
 // R -> token t0 + R/G, head kvh*G + R%G (G = n_head/n_kv must divide 128), so a single pass over the
-// kv head's K/V rows serves all G query heads of 128/G tokens.  320 threads in three roles:
-//   warp 0   (one lane)  TMA producer: Q tile once, then 128-row K and V blocks into two-stage rings
-//                        (cp.async.bulk.tensor, 128-byte swizzle, no multicast); rows past the
-//                        chunk are outside the tensor map and arrive as zeros
+// kv head's K/V rows serves all G query heads of 128/G tokens.  The KV sequence is walked in blocks of
+// 128 rows.  320 threads in three roles:
+//   warp 0   (one lane)  TMA producer: Q tile once, then 128-row K blocks (three-stage ring) and V blocks
+//                        (two-stage ring) with cp.async.bulk.tensor, 128-byte swizzle, no multicast; rows
+//                        past the chunk are outside the tensor map and arrive as zeros
 //   warp 1   (one lane)  tcgen05.mma issuer: S_j = Q K_j^T (M128 N128 K16 x8, both operands from shared
-//                        memory) into one of two TMEM score buffers; O += P_j V_j with P read straight
-//                        from TMEM (it overwrites the first 64 columns of its own score buffer as packed
-//                        fp16 pairs) and V as MN-major B operand from shared memory, into a TMEM
-//                        accumulator; tcgen05.commit signals the mbarriers
-//   warps 2-5, 6-9       two softmax teams, one thread per row each.  Team t takes KV blocks j = t, t+2, ...
-//                        and owns score buffer t and its OWN accumulator O_t with its own running
-//                        reference max and row sum, so consecutive blocks never wait on each other (an
-//                        in-CTA split of the KV sequence by block parity).  Per block: tcgen05.ld of the
-//                        128-column score row, causal mask, row max, lazy rescale of O_t (only when the max
-//                        grows by more than 2^8), exp2, fp16 P stored back to TMEM (tcgen05.st) where the
-//                        next MMA takes it as its A operand.  At the end the two (m, l, O) are merged
-//                        log-sum-exp style and O/l goes to global memory.
-// S_{j+1} is issued before P_j V_j, so the tensor pipe computes the next scores while a softmax team
-// works on the current ones, and each team has two MMA block times for one block of softmax.
+//                        memory) into one of THREE TMEM score buffers, so that the scores of blocks j+1 and
+//                        j+2 are already there while block j is in the softmax; O += P_j V_j with P read
+//                        straight from TMEM (it overwrites the first 64 columns of its own score buffer as
+//                        packed fp16 pairs) and V as MN-major B operand from shared memory, into the one
+//                        TMEM accumulator; tcgen05.commit signals the mbarriers.  Descriptors are built
+//                        once; only offsets are added per MMA.
+//   warps 2-5, 6-9       two softmax teams, one thread per row each, taking alternate KV blocks.  Per block:
+//                        tcgen05.ld of the 128-column score row, causal mask, row max; the reference max is a
+//                        single chain over all blocks, handed from team to team through shared memory (block
+//                        j continues from what the other team published for block j-1); lazy rescale of O
+//                        (only when the max grows by more than 2^4, after the previous P V has completed);
+//                        exp2; fp16 P stored back to TMEM (tcgen05.st).  Each thread keeps its own partial
+//                        row sum; the two are added at the end and O/l goes to global memory.
+// TMEM: 3 x 128 score columns + 128 accumulator columns = 512.  With three score buffers the tensor pipe is
+// never waiting for a softmax: the loop is bound by the MMAs (about 1770 cycles per block, of which the
+// S = Q K^T MMAs, which read both operands from shared memory, take about 1070).
 //
 // Every mbarrier wait is bounded: after about a second without progress the kernel raises an abort
 // flag, every role leaves its loop, outstanding copies and MMAs are drained (bounded again), TMEM is
@@ -43,18 +46,23 @@ constexpr int BM = 128, BN = 128, HD = 128;
 constexpr int SLAB = 128 * 128;                 // bytes of one 128-row x 64-element fp16 slab
 constexpr int TILE = 2 * SLAB;                  // a 128 x 128 fp16 tile = two slabs
 constexpr int OFF_Q = 0;
-constexpr int NST = 2;                          // K and V ring depth
+constexpr int NKS = 3, NVS = 2;                 // K and V ring depths
+constexpr int NSB = 3;                          // score buffers in TMEM
 constexpr int OFF_K = OFF_Q + TILE;
-constexpr int OFF_V = OFF_K + NST * TILE;
-constexpr int OFF_BAR = OFF_V + NST * TILE;
-constexpr int OFF_MX = OFF_BAR + 256;           // float2 [2 teams][128 rows]: (m, l) exchanged at the end
+constexpr int OFF_V = OFF_K + NKS * TILE;
+constexpr int OFF_BAR = OFF_V + NVS * TILE;
+constexpr int OFF_MREF = OFF_BAR + 256;         // float [2][128]: reference max published per block parity
+constexpr int OFF_MX = OFF_MREF + 1024;         // float2 [2 teams][128 rows]: (m, l) exchanged at the end
 constexpr int SMEM_BYTES = OFF_MX + 2048 + 1024;   // + slack for 1024-byte alignment
 static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 constexpr long long kWaitCycles = 2000000000LL;    // ~1 s
 constexpr long long kDrainCycles = 200000000LL;    // ~0.1 s
 constexpr float kRescaleThreshold = 4.0f;          // log2 units: P stays below 2^4 relative to the reference max
 
-enum Bar { Q_FULL = 0, K_FULL = 1, K_EMPTY = 4, V_FULL = 7, V_EMPTY = 10, S_FULL = 13, P_FULL = 15, PV_DONE = 17, DRAIN = 19, XCH = 20, ALL_DONE = 21, NBAR = 22 };
+enum Bar { Q_FULL = 0, K_FULL = 1, K_EMPTY = K_FULL + NKS, V_FULL = K_EMPTY + NKS, V_EMPTY = V_FULL + NVS, S_FULL = V_EMPTY + NVS,
+           P_FULL = S_FULL + NSB, PV_DONE = P_FULL + NSB, MREF = PV_DONE + 2, DRAIN = MREF + 2, XCH = DRAIN + 1, ALL_DONE = XCH + 1,
+           NBAR = ALL_DONE + 1 };
+static_assert(NBAR * 8 + 16 <= 256, "barrier block");
 
 #ifndef OATTN_TC_POLY
 #define OATTN_TC_POLY 0
@@ -242,19 +250,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 
     if (tid == 0) {
         mbar_init(bar(Q_FULL), 1);
-        for (int s = 0; s < NST; ++s) {
-            mbar_init(bar(K_FULL + s), 1);
-            mbar_init(bar(K_EMPTY + s), 1);
-            mbar_init(bar(V_FULL + s), 1);
-            mbar_init(bar(V_EMPTY + s), 1);
-        }
-        mbar_init(bar(S_FULL), 1);
-        mbar_init(bar(S_FULL + 1), 1);
-        mbar_init(bar(P_FULL), 4);
-        mbar_init(bar(P_FULL + 1), 4);
+        for (int s = 0; s < NKS; ++s) { mbar_init(bar(K_FULL + s), 1); mbar_init(bar(K_EMPTY + s), 1); }
+        for (int s = 0; s < NVS; ++s) { mbar_init(bar(V_FULL + s), 1); mbar_init(bar(V_EMPTY + s), 1); }
+        for (int s = 0; s < NSB; ++s) { mbar_init(bar(S_FULL + s), 1); mbar_init(bar(P_FULL + s), 4); }
+        for (int s = 0; s < 2; ++s) { mbar_init(bar(PV_DONE + s), 1); mbar_init(bar(MREF + s), 4); }
         mbar_init(bar(XCH), 256);
-        mbar_init(bar(PV_DONE), 1);
-        mbar_init(bar(PV_DONE + 1), 1);
         mbar_init(bar(DRAIN), 1);
         mbar_init(bar(ALL_DONE), 1);
         *s_abort = 0;
@@ -269,19 +269,19 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *s_tmem;
-    const uint32_t TM_S = tmem, TM_O = tmem + 256;   // S_t at TM_S + 128 t, O_t at TM_O + 128 t
+    const uint32_t TM_S = tmem, TM_O = tmem + NSB * BN;   // score buffer b at TM_S + 128 b, the accumulator behind them
 
     if (warp == 0) {
         // ---------------------------------------------------------------- TMA producer
         if (lane == 0) {
             bool ok = true;
-            int k_issued[NST] = {}, v_issued[NST] = {};
+            int k_issued[NKS] = {}, v_issued[NVS] = {};
             mbar_expect_tx(bar(Q_FULL), TILE);
             tma_load_3d(sbase + OFF_Q, &tmQ, 0, kvh * p.G, t0, bar(Q_FULL));
             tma_load_3d(sbase + OFF_Q + SLAB, &tmQ, 64, kvh * p.G, t0, bar(Q_FULL));
             auto load_k = [&](int j) {
-                const int s = j % NST;
-                if (j >= NST) ok = mbar_wait(bar(K_EMPTY + s), ((j / NST) - 1) & 1, s_abort);
+                const int s = j % NKS;
+                if (j >= NKS) ok = mbar_wait(bar(K_EMPTY + s), ((j / NKS) - 1) & 1, s_abort);
                 if (!ok) return;
                 mbar_expect_tx(bar(K_FULL + s), TILE);
                 tma_load_3d(sbase + OFF_K + s * TILE, &tmK, 0, j * BN, kvh, bar(K_FULL + s));
@@ -289,26 +289,27 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 ++k_issued[s];
             };
             auto load_v = [&](int j) {
-                const int s = j % NST;
-                if (j >= NST) ok = mbar_wait(bar(V_EMPTY + s), ((j / NST) - 1) & 1, s_abort);
+                const int s = j % NVS;
+                if (j >= NVS) ok = mbar_wait(bar(V_EMPTY + s), ((j / NVS) - 1) & 1, s_abort);
                 if (!ok) return;
                 mbar_expect_tx(bar(V_FULL + s), TILE);
                 tma_load_3d(sbase + OFF_V + s * TILE, &tmV, 0, j * BN, kvh, bar(V_FULL + s));
                 tma_load_3d(sbase + OFF_V + s * TILE + SLAB, &tmV, 64, j * BN, kvh, bar(V_FULL + s));
                 ++v_issued[s];
             };
-            load_k(0);
+            // consumption order of the MMA warp: K_0..K_2, then V_j, K_(j+3)
+            for (int j = 0; j < NSB && j < nb && ok; ++j) load_k(j);
             for (int j = 0; j < nb && ok; ++j) {
-                if (j + 1 < nb) load_k(j + 1);
-                if (ok) load_v(j);
+                load_v(j);
+                if (ok && j + NSB < nb) load_k(j + NSB);
             }
             if (*s_abort) {
                 // make sure no copy is still writing this CTA's shared memory when it exits
                 mbar_drain(bar(Q_FULL), 0);
-                for (int s = 0; s < NST; ++s) {
+                for (int s = 0; s < NKS; ++s)
                     if (k_issued[s]) mbar_drain(bar(K_FULL + s), (k_issued[s] - 1) & 1);
+                for (int s = 0; s < NVS; ++s)
                     if (v_issued[s]) mbar_drain(bar(V_FULL + s), (v_issued[s] - 1) & 1);
-                }
             }
         }
         __syncwarp();
@@ -316,40 +317,47 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         // ---------------------------------------------------------------- MMA issuer
         if (lane == 0) {
             bool ok = mbar_wait(bar(Q_FULL), 0, s_abort);
+            // Descriptors are built once; inside the loops only the (compile-time) k-step offset and the stage
+            // offset are added to the 14-bit address field (in 16-byte units; it cannot carry out of the field).
+            // The issuing lane shares its scheduler with two softmax warps, so every instruction between two MMAs
+            // delays the tensor pipe.
+            const uint64_t dQ = desc_kmajor(sbase + OFF_Q), dK = desc_kmajor(sbase + OFF_K), dV = desc_mnmajor(sbase + OFF_V);
             auto issue_s = [&](int j) {
-                const int s = j % NST, b = j & 1;
-                ok = mbar_wait(bar(K_FULL + s), (j / NST) & 1, s_abort);
+                const int s = j % NKS, b = j % NSB;
+                ok = mbar_wait(bar(K_FULL + s), (j / NKS) & 1, s_abort);
                 if (!ok) return;
                 TRACE(0, 0, j);
                 tc_fence_after();
+                const uint64_t dKs = dK + (uint64_t)((s * TILE) >> 4);
+                const uint32_t d = TM_S + b * BN;
 #pragma unroll
                 for (int kk = 0; kk < HD / 16; ++kk) {
-                    const uint32_t off = (kk >> 2) * SLAB + (kk & 3) * 32;
-                    tc_mma(TM_S + b * BN, desc_kmajor(sbase + OFF_Q + off), desc_kmajor(sbase + OFF_K + s * TILE + off), IDESC_S, kk > 0);
+                    const uint64_t off = (uint64_t)((((kk >> 2) * SLAB) + (kk & 3) * 32) >> 4);
+                    tc_mma(d, dQ + off, dKs + off, IDESC_S, kk > 0);
                 }
                 tc_commit(bar(S_FULL + b));
                 tc_commit(bar(K_EMPTY + s));
             };
-            if (ok) issue_s(0);
+            for (int j = 0; j < NSB && j < nb && ok; ++j) issue_s(j);
             for (int j = 0; j < nb && ok; ++j) {
-                if (j + 1 < nb) issue_s(j + 1);
-                if (!ok) break;
-                const int s = j & 1, sv = j % NST;
-                ok = mbar_wait(bar(P_FULL + s), (j >> 1) & 1, s_abort);
+                const int b = j % NSB, sv = j % NVS;
+                ok = mbar_wait(bar(P_FULL + b), (j / NSB) & 1, s_abort);
                 TRACE(0, 1, j);
-                if (ok) ok = mbar_wait(bar(V_FULL + sv), (j / NST) & 1, s_abort);
+                if (ok) ok = mbar_wait(bar(V_FULL + sv), (j / NVS) & 1, s_abort);
                 if (!ok) break;
                 TRACE(0, 2, j);
                 tc_fence_after();
+                const uint64_t dVs = dV + (uint64_t)((sv * TILE) >> 4);
+                const uint32_t a_t = TM_S + b * BN;
+                const uint32_t acc0 = j > 0 ? 1u : 0u;
 #pragma unroll
-                for (int kk = 0; kk < BN / 16; ++kk) {
-                    const uint32_t b_off = kk * 2048;                             // V: 16 rows of 128 B per k-step
-                    tc_mma_ts(TM_O + s * HD, TM_S + s * BN + kk * 8, desc_mnmajor(sbase + OFF_V + sv * TILE + b_off), IDESC_PV,
-                              (j > 1 || kk > 0) ? 1u : 0u);
-                }
-                tc_commit(bar(PV_DONE + s));
+                for (int kk = 0; kk < BN / 16; ++kk)                              // V: 16 rows of 128 B per k-step
+                    tc_mma_ts(TM_O, a_t + kk * 8, dVs + (uint64_t)((kk * 2048) >> 4), IDESC_PV, kk > 0 ? 1u : acc0);
+                tc_commit(bar(PV_DONE + (j & 1)));
                 tc_commit(bar(V_EMPTY + sv));
                 TRACE(0, 3, j);
+                // score buffer b is free again once P_j V_j has been issued (the tensor pipe runs in order)
+                if (j + NSB < nb) issue_s(j + NSB);
             }
             if (ok) tc_commit(bar(ALL_DONE));
             if (*s_abort) {
@@ -368,16 +376,17 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         const bool valid = tok < ntok;
         const int vis = p.n_past + tglob;                   // last visible cache row
         const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
-        const uint32_t ts = TM_S + lane_addr + team * BN;   // this team's score buffer, this thread's lane
-        const uint32_t to = TM_O + lane_addr + team * HD;   // this team's accumulator
-        float m_ref = -CUDART_INF_F, l = 0.f;
+        const uint32_t to = TM_O + lane_addr;               // the accumulator row of this thread
+        float* s_mref = reinterpret_cast<float*>(smem + OFF_MREF);
+        float m_l = -CUDART_INF_F, l = 0.f;                 // this thread's partial row sum and the reference max it is relative to
         bool ok = true;
-        int n_done = 0;                                     // blocks this team has handed to the MMA warp
 
-        for (int j = team; j < nb && ok; j += 2, ++n_done) {
+        for (int j = team; j < nb && ok; j += 2) {
+            const int b = j % NSB;
+            const uint32_t ts = TM_S + lane_addr + b * BN;  // score buffer of this block, this thread's lane
             if (tid == 64 || tid == 192) TRACE(1 + team, 0, j);
             // every give-up decision is made warp-uniform: the TMEM loads and stores below are warp-collective
-            ok = __all_sync(0xffffffffu, mbar_wait(bar(S_FULL + team), n_done & 1, s_abort));
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(S_FULL + b), (j / NSB) & 1, s_abort));
             if (!ok) break;
             if (tid == 64 || tid == 192) TRACE(1 + team, 1, j);
             tc_fence_after();
@@ -399,21 +408,32 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 for (int c = 0; c < 4; ++c) mxc[c] = max3(mxc[c], v[i + 2 * c], v[i + 2 * c + 1]);
             }
             const float mx = fmaxf(fmaxf(mxc[0], mxc[1]), fmaxf(mxc[2], mxc[3]));
-            float m_new = m_ref;
-            if (n_done == 0 || mx > m_ref + kRescaleThreshold) m_new = mx;
-            // a row that is fully masked so far keeps m_ref = -inf; use 0 as the exponent base then (all p = 0)
+            // The reference max is one chain over all blocks: block j continues from what the other team
+            // published for block j-1 (slot and barrier (j-1) & 1), and publishes its own before anything else.
+            float m_prev = -CUDART_INF_F;
+            if (j > 0) {
+                ok = __all_sync(0xffffffffu, mbar_wait(bar(MREF + ((j - 1) & 1)), ((j - 1) >> 1) & 1, s_abort));
+                if (!ok) break;
+                m_prev = s_mref[((j - 1) & 1) * 128 + row];
+            }
+            const float m_new = (m_prev == -CUDART_INF_F || mx > m_prev + kRescaleThreshold) ? fmaxf(mx, m_prev) : m_prev;
+            s_mref[(j & 1) * 128 + row] = m_new;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(MREF + (j & 1)));
+            // a row that is fully masked so far keeps -inf; use 0 as the exponent base then (all p = 0)
             const float m_use = (m_new == -CUDART_INF_F) ? 0.f : m_new;
-            const bool need = (n_done > 0) && (m_new != m_ref) && (m_ref != -CUDART_INF_F);
+            const bool need = (m_new != m_prev) && (m_prev != -CUDART_INF_F);
             if (__any_sync(0xffffffffu, need)) {
-                // O_t must be quiescent while it is rescaled: wait for this team's previous P V.  A parity wait is
-                // only meaningful for the current or the previous phase of a barrier; that holds here because
-                // the score block just received was issued after the P V two blocks back, and the tensor pipe
-                // completes in order, so PV_DONE[team] has seen at least n_done - 1 completions.
-                ok = __all_sync(0xffffffffu, mbar_wait(bar(PV_DONE + team), (n_done - 1) & 1, s_abort));
+                // O must be quiescent and complete up to block j-1.  PV_DONE alternates between two barriers by
+                // block parity; the score block just received proves that every P V up to j-3 has completed, and
+                // P_j V_j cannot start before this thread delivers P_j, so each barrier is at most one phase
+                // away from the one waited for.
+                if (j >= 2) ok = mbar_wait(bar(PV_DONE + (j & 1)), ((j - 2) >> 1) & 1, s_abort);
+                if (ok) ok = mbar_wait(bar(PV_DONE + ((j - 1) & 1)), ((j - 1) >> 1) & 1, s_abort);
+                ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_fence_after();
-                const float alpha = need ? fast_exp2(m_ref - m_new) : 1.f;
-                l *= alpha;
+                const float alpha = need ? fast_exp2(m_prev - m_new) : 1.f;
                 float o[32];
 #pragma unroll 1
                 for (int c = 0; c < 4; ++c) {
@@ -424,101 +444,63 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 }
                 asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
             }
-            m_ref = m_new;
+            if (m_l != m_new) {                             // bring this thread's partial sum to the current reference
+                l *= (m_l == -CUDART_INF_F) ? 0.f : fast_exp2(m_l - m_new);
+                m_l = m_new;
+            }
             if (tid == 64 || tid == 192) TRACE(1 + team, 3, j);
             // P (fp16 pairs) goes over the first 64 columns of this thread's own score row.
-            // The special-function unit (ex2, and the fp32->fp16 conversion) has 16 lanes per SM, which for a
-            // 128 x 128 score block is as long as the two MMAs themselves.  Every other pair of elements
-            // therefore takes its exponential from a degree-3 polynomial on the FMA pipe instead.
             uint32_t pk[64];
-#if OATTN_TC_FAST
-            // Half of the pairs take 2^x from the special-function unit, the other half from the polynomial on the
-            // FMA pipe; subtraction and row sums run as packed f32x2 instructions.
-            const f2 m2 = pack2(m_use, m_use);
-            f2 lacc[2] = {pack2(0.f, 0.f), pack2(0.f, 0.f)};
-#pragma unroll
-            for (int i = 0; i < 64; ++i) {
-                const f2 x = sub2(pack2(v[2 * i], v[2 * i + 1]), m2);
-                float p0, p1;
-                if (i & 1) {
-                    exp2_poly2(x, p0, p1);
-                } else {
-                    float x0, x1;
-                    unpack2(x, x0, x1);
-                    p0 = fast_exp2(x0);
-                    p1 = fast_exp2(x1);
-                }
-                lacc[i & 1] = add2(lacc[i & 1], pack2(p0, p1));
-                pk[i] = pack_half2(p0, p1);
-            }
-            {
-                float a0, a1, b0, b1;
-                unpack2(lacc[0], a0, a1);
-                unpack2(lacc[1], b0, b1);
-                l += (a0 + a1) + (b0 + b1);
-            }
-#else
             float l4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int i = 0; i < 64; ++i) {
                 const float x0 = v[2 * i] - m_use, x1 = v[2 * i + 1] - m_use;
                 float p0, p1;
-                if (OATTN_TC_POLY && (i & 1)) { p0 = exp2_poly(x0); p1 = exp2_poly(x1); }
-                else       { p0 = fast_exp2(x0); p1 = fast_exp2(x1); }
+                if (OATTN_TC_POLY && (i % (OATTN_TC_POLY ? OATTN_TC_POLY : 1)) == OATTN_TC_POLY - 1) { p0 = exp2_poly(x0); p1 = exp2_poly(x1); }
+                else { p0 = fast_exp2(x0); p1 = fast_exp2(x1); }
                 l4[i & 3] += p0 + p1;
                 pk[i] = pack_half2(p0, p1);
             }
             l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
-#endif
             if (tid == 64 || tid == 192) TRACE(1 + team, 4, j);
             tmem_st32(ts, reinterpret_cast<const float*>(pk));
             tmem_st32(ts + 32, reinterpret_cast<const float*>(pk + 32));
             asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar(P_FULL + team));      // one arrival per warp (the barrier counts 4)
+            if (lane == 0) mbar_arrive(bar(P_FULL + b));         // one arrival per warp (the barrier counts 4)
             if (tid == 64 || tid == 192) TRACE(1 + team, 5, j);
         }
-        // ---- merge the two teams' (m, l, O) and write the output --------------------------------------
+        // ---- add the two teams' row sums and write the output -----------------------------------------
         float2* s_x = reinterpret_cast<float2*>(smem + OFF_MX);
         if (ok) {
-            s_x[team * 128 + row] = make_float2(m_ref, l);
+            s_x[team * 128 + row] = make_float2(m_l, l);
             mbar_arrive(bar(XCH));
             ok = mbar_wait(bar(XCH), 0, s_abort);
         }
-        // both accumulators are final once every MMA of this CTA has completed (single-phase barrier, committed
-        // by the MMA warp after its last P V)
+        // the accumulator is final once every MMA of this CTA has completed (single-phase barrier, committed by
+        // the MMA warp after its last P V)
         if (ok) ok = mbar_wait(bar(ALL_DONE), 0, s_abort);
         ok = __all_sync(0xffffffffu, ok);
         if (ok) {
             tc_fence_after();
-            const float2 mine = make_float2(m_ref, l), other = s_x[(1 - team) * 128 + row];
-            const float M = fmaxf(mine.x, other.x);
-            const float w_me = (mine.x == -CUDART_INF_F) ? 0.f : fast_exp2(mine.x - M);
+            const float2 other = s_x[(1 - team) * 128 + row];
+            // the reference max never decreases, so the later block's value is the final one and O is relative to it
+            const float M = fmaxf(m_l, other.x);
+            const float w_me = (m_l == -CUDART_INF_F) ? 0.f : fast_exp2(m_l - M);
             const float w_ot = (other.x == -CUDART_INF_F) ? 0.f : fast_exp2(other.x - M);
-            const float inv = 1.f / (w_me * mine.y + w_ot * other.y);
-            const float a_me = w_me * inv, a_ot = w_ot * inv;
+            const float inv = 1.f / (w_me * l + w_ot * other.y);
             // this thread writes columns [64 team, 64 team + 64) of its row
             float* dst = p.out + ((size_t)tglob * p.n_head + kvh * p.G + hg) * HD + 64 * team;
-            const uint32_t o_me = TM_O + lane_addr + team * HD + 64 * team;
-            const uint32_t o_ot = TM_O + lane_addr + (1 - team) * HD + 64 * team;
-            // Both accumulators are read unconditionally (the loads are warp-collective); one that never received
-            // a block holds whatever TMEM held before, and is discarded below by a select on its zero weight.
 #pragma unroll 1
             for (int c = 0; c < 2; ++c) {
-                float a[32], b2[32];
-                tmem_ld32(o_me + 32 * c, a);
-                tmem_ld32(o_ot + 32 * c, b2);
+                float a[32];
+                tmem_ld32(to + 64 * team + 32 * c, a);
                 if (valid) {
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        float4 r;
-                        r.x = (w_me != 0.f ? a[4 * i] * a_me : 0.f) + (w_ot != 0.f ? b2[4 * i] * a_ot : 0.f);
-                        r.y = (w_me != 0.f ? a[4 * i + 1] * a_me : 0.f) + (w_ot != 0.f ? b2[4 * i + 1] * a_ot : 0.f);
-                        r.z = (w_me != 0.f ? a[4 * i + 2] * a_me : 0.f) + (w_ot != 0.f ? b2[4 * i + 2] * a_ot : 0.f);
-                        r.w = (w_me != 0.f ? a[4 * i + 3] * a_me : 0.f) + (w_ot != 0.f ? b2[4 * i + 3] * a_ot : 0.f);
-                        *reinterpret_cast<float4*>(dst + 32 * c + 4 * i) = r;
-                    }
+                    for (int i = 0; i < 8; ++i)
+                        *reinterpret_cast<float4*>(dst + 32 * c + 4 * i) =
+                            make_float4(a[4 * i] * inv, a[4 * i + 1] * inv, a[4 * i + 2] * inv, a[4 * i + 3] * inv);
                 }
             }
         }
