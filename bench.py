@@ -193,7 +193,7 @@ def run_b200(args, w):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
     from orin_llm_b200 import build, ops
-    from orin_llm_b200.dist import SplitKVDecoder, slice_bounds
+    from orin_llm_b200.dist import PeerSplitKVDecoder, SplitKVDecoder, slice_bounds
     build.build()
     ops.init(local_rank)
 
@@ -210,7 +210,23 @@ def run_b200(args, w):
     out = torch.zeros(layers, n_head, hd, device="cuda")
     d_len = torch.tensor([n_loc], dtype=torch.int32, device="cuda")
     d_pos = torch.tensor([n_loc - 1], dtype=torch.int32, device="cuda")
-    dec = SplitKVDecoder(n_head, n_kv, hd)
+    exchange = "none"
+    dec = None
+    if world > 1:
+        exchange = args.exchange
+        if exchange == "peer":
+            try:
+                dec = PeerSplitKVDecoder(n_head, n_kv, hd)
+            except Exception as e:      # no peer-mapped memory on this box: fall back to the NCCL all-gather
+                if rank == 0:
+                    print("peer exchange unavailable (%s); using the NCCL all-gather" % e, file=sys.stderr)
+                exchange = "nccl"
+        # every rank must take the same path
+        flag = torch.tensor([1 if exchange == "peer" else 0], device="cuda")
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 0:
+            exchange = "nccl"
+            dec = SplitKVDecoder(n_head, n_kv, hd)
 
     def step():
         if world == 1:
@@ -254,12 +270,15 @@ def run_b200(args, w):
         run_step = step
         l0 = ops.launch_count()
     else:
-        ops.profile_enable(layers)            # one event pair per layer call, recorded as graph nodes
+        # event pairs around the split kernel of the first `n_prof_graph` layer calls, recorded as graph nodes
+        # (a few, not all 36: every event node costs the graph a few microseconds)
+        n_prof_graph = int(os.environ.get("OATTN_BENCH_PROFILE_CALLS", "4"))
+        ops.profile_enable(n_prof_graph)
         l0 = ops.launch_count()
         cap_stream = torch.cuda.Stream()
         cap_stream.wait_stream(torch.cuda.current_stream())
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=cap_stream):
+        with torch.cuda.graph(graph, stream=cap_stream, capture_error_mode="thread_local"):
             step()
         launches_per_step = ops.launch_count() - l0
         graph.replay()
@@ -311,9 +330,21 @@ def run_b200(args, w):
     h2d = layers * (n_head + 2 * n_kv) * hd * 4
     d2h = layers * n_head * hd * 4
 
-    if rank != 0:
+    if exchange == "peer" and dec.status() != 0:
+        raise SystemExit("peer exchange: a bounded flag wait ran out (rank %d)" % rank)
+
+    def finish():
+        # Tearing the NCCL communicator / peer mappings down can block for minutes on some hosts; every rank has
+        # its results by now, so leave through a barrier and a hard exit instead.
         if world > 1:
-            dist.destroy_process_group()
+            dist.barrier()
+            torch.cuda.synchronize()
+            sys.stdout.flush()
+            sys.stderr.flush()
+            os._exit(0)
+
+    if rank != 0:
+        finish()
         return
 
     peaks, peak_kind = measured_peaks()
@@ -349,6 +380,8 @@ def run_b200(args, w):
         "config": {"workload": args.workload, "n_head": n_head, "n_kv": n_kv, "head_dim": hd, "layers_per_step": layers,
                    "kv_len": L, "kv_rows_per_gpu": n_loc, "parallelism": "kv-split x%d" % world,
                    "launch": "eager" if args.no_graph else "cuda graph replay of the step",
+                   "exchange": {"none": "single GPU", "peer": "records stored into peers' buffers by the merge kernel (NVLink peer stores) + flag wait",
+                                "nccl": "NCCL all-gather of the records"}[exchange],
                    "l2": "inputs larger than L2: each of the %d layer calls of a step reads its own %.0f MiB of KV" % (
                        layers, per_launch_bytes / 2**20)},
         "pct_of_8tbs": 100.0 * value / (8000.0 * world),
@@ -358,8 +391,7 @@ def run_b200(args, w):
         "gpu_launches": int(launches), "clocks": clocks,
     }
     print(json.dumps(line))
-    if world > 1:
-        dist.destroy_process_group()
+    finish()
 
 
 def prefill_flops(w):
@@ -441,6 +473,7 @@ def main():
     ap.add_argument("--workload", default="decode_3b_L1048576", choices=sorted(WORKLOADS) + sorted(PREFILL_WORKLOADS))
     ap.add_argument("--layers", type=int, default=None, help="override the layer calls per step")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"], help="multi-GPU record exchange")
     ap.add_argument("--no-graph", action="store_true", help="launch the step eagerly instead of replaying a CUDA graph")
     args = ap.parse_args()
     if args.workload in PREFILL_WORKLOADS:

@@ -147,6 +147,26 @@ int oattn_decode_partial(const float* q, const uint16_t* kc, const uint16_t* vc,
  * M = max m_r, L = sum l_r e^(m_r - M), out = sum O_r e^(m_r - M) / L. */
 int oattn_combine(const float* parts, int n_parts, float* out, int n_head, int head_dim, void* stream);
 
+/* ---- multi-GPU exchange without a collective call (no reference counterpart) ----------------------------------
+ * The record exchange of split-KV decode is 8 KB per rank: latency-bound.  Instead of all-gather + combine, the
+ * per-rank merge kernel stores its record straight into every rank's exchange buffer over NVLink (plain peer
+ * stores) and raises a per-(source rank, head) generation flag; oattn_peer_wait_combine polls the flags of its
+ * own buffer (bounded, ~2 s, then a status word is set) and merges the `world` records.
+ *   exchange buffer   oattn_peer_buffer_bytes(world, n_head, head_dim) bytes on every rank, peer-mapped (e.g. CUDA
+ *                     VMM / torch symmetric memory), zero-filled before first use; `peer_bufs_dev` is a DEVICE array
+ *                     of `world` pointers (entry r = rank r's buffer as seen from this GPU, own buffer included)
+ *   state             oattn_peer_state_bytes(n_head) bytes of ordinary device memory per rank, zero-filled once
+ * Records are double-buffered by generation parity; every rank must make the same sequence of calls.  Both calls
+ * are graph-capturable.  world <= 16. */
+size_t oattn_peer_buffer_bytes(int world, int n_head, int head_dim);
+size_t oattn_peer_state_bytes(int n_head);
+int oattn_decode_partial_push(const float* q, const uint16_t* kc, const uint16_t* vc, int n_head, int n_kv, int head_dim,
+                              int n_ctx, const int* d_len, float scale, void* workspace, size_t workspace_bytes,
+                              const void* peer_bufs_dev, int rank, int world, void* state, void* stream);
+int oattn_peer_wait_combine(const void* my_buf, int world, float* out, int n_head, int head_dim, void* state, void* stream);
+/* Blocking read of the status word (0 = every wait so far was satisfied). */
+int oattn_peer_status(const void* state, int n_head, int* status);
+
 /* ---- prefill: a chunk of `batch` query tokens, causal ------------------------------------ */
 
 /* Scratch for the prefill call (fp16 staging of the rotated, scaled queries). 256-byte aligned. */

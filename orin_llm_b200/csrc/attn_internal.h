@@ -12,6 +12,17 @@ namespace oattn {
 constexpr int DECODE_TILE = 64;        // cache rows per pipeline stage of the decode kernel
 constexpr int DECODE_MAX_SPLITS = 512; // upper bound on KV splits per kv head (combine smem)
 constexpr int PART_PAD = 4;            // floats after O in a partial record: m, l, 0, 0
+constexpr int DECODE_MAX_RANKS = 16;   // ranks of one peer exchange
+
+// Exchange buffer of one rank (the same layout on every rank): records float [2 slots][world][n_head][hd+PART_PAD],
+// then, 256-byte aligned, generation flags unsigned [world][n_head].
+__host__ __device__ inline size_t peer_flags_offset(int world, int n_head, int head_dim) {
+    const size_t rec = (size_t)2 * world * n_head * (head_dim + PART_PAD) * sizeof(float);
+    return (rec + 255) & ~(size_t)255;
+}
+__host__ __device__ inline size_t peer_buffer_bytes(int world, int n_head, int head_dim) {
+    return peer_flags_offset(world, n_head, head_dim) + (((size_t)world * n_head * sizeof(unsigned) + 255) & ~(size_t)255);
+}
 
 struct DecodeArgs {
     const float* q;        // [n_head][hd] fp32
@@ -29,6 +40,9 @@ struct DecodeArgs {
     int fuse;
     RopeArgs rope;
     int emit_partial;      // combine writes the un-normalised record instead of the normalised output
+    const unsigned long long* peer_bufs = nullptr;   // multi-GPU peer exchange: device array of `world` buffer pointers
+    int* gen_push = nullptr;                          // [n_head] generation counters (private to this rank)
+    int rank = 0, world = 1;
 };
 
 // Size of the scratch block built into the library for oattn_decode_noalloc, and its device address on the
@@ -45,6 +59,9 @@ cudaError_t launch_decode(const DecodeArgs& a, cudaStream_t stream, unsigned lon
 // Merge n_parts records [n_parts][n_head][hd+PART_PAD] -> out [n_head][hd].
 cudaError_t launch_combine_records(const float* parts, int n_parts, float* out, int n_head, int head_dim,
                                    cudaStream_t stream, unsigned long long* launches);
+
+cudaError_t launch_peer_wait_combine(const void* my_buf, int world, float* out, int n_head, int head_dim, int* gen_wait,
+                                     int* status, cudaStream_t stream, unsigned long long* launches);
 
 struct PrefillArgs {
     const float* q;        // [batch][n_head][hd] fp32

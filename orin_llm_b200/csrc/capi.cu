@@ -145,10 +145,16 @@ size_t oattn_decode_workspace_bytes(int n_head, int n_kv, int head_dim) {
     return decode_ws(n_head, n_kv, head_dim, g_dev[g_cur].sm_count).total;
 }
 
+struct PeerTarget {
+    const unsigned long long* bufs = nullptr;
+    int* gen_push = nullptr;
+    int rank = 0, world = 1;
+};
+
 static int decode_common(const float* q, const float* k_new, const float* v_new, uint16_t* kc, uint16_t* vc, float* out,
                          int n_head, int n_kv, int head_dim, int n_ctx, const int* d_pos, int pos_bias, float scale,
                          int fuse, const oattn_rope_params* rope, int emit_partial, void* workspace, size_t workspace_bytes,
-                         void* stream) {
+                         void* stream, const PeerTarget* peer = nullptr) {
     if (!device_ready()) return OATTN_ERR_DEVICE;
     int rc = check_shape(n_head, n_kv, head_dim);
     if (rc != OATTN_OK) return rc;
@@ -167,6 +173,7 @@ static int decode_common(const float* q, const float* k_new, const float* v_new,
     a.n_head = n_head; a.n_kv = n_kv; a.head_dim = head_dim; a.n_ctx = n_ctx;
     a.n_splits = w.n_splits; a.min_tiles = g_decode_min_tiles;
     a.scale = scale; a.fuse = fuse; a.emit_partial = emit_partial;
+    if (peer) { a.peer_bufs = peer->bufs; a.gen_push = peer->gen_push; a.rank = peer->rank; a.world = peer->world; }
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     if (g_prof_ev && g_prof_n < g_prof_cap) {
         ev0 = g_prof_ev[2 * g_prof_n];
@@ -210,6 +217,44 @@ int oattn_decode_partial(const float* q, const uint16_t* kc, const uint16_t* vc,
                          void* stream) {
     return decode_common(q, nullptr, nullptr, const_cast<uint16_t*>(kc), const_cast<uint16_t*>(vc), part, n_head, n_kv,
                          head_dim, n_ctx, d_len, 0, scale, OATTN_FUSE_NONE, nullptr, 1, workspace, workspace_bytes, stream);
+}
+
+size_t oattn_peer_buffer_bytes(int world, int n_head, int head_dim) {
+    if (world < 1 || world > DECODE_MAX_RANKS || n_head <= 0 || (head_dim != 64 && head_dim != 128)) return 0;
+    return peer_buffer_bytes(world, n_head, head_dim);
+}
+
+size_t oattn_peer_state_bytes(int n_head) { return n_head > 0 ? align256((size_t)(2 * n_head + 1) * sizeof(int)) : 0; }
+
+int oattn_decode_partial_push(const float* q, const uint16_t* kc, const uint16_t* vc, int n_head, int n_kv, int head_dim,
+                              int n_ctx, const int* d_len, float scale, void* workspace, size_t workspace_bytes,
+                              const void* peer_bufs_dev, int rank, int world, void* state, void* stream) {
+    if (!peer_bufs_dev || !state || world < 1 || world > DECODE_MAX_RANKS || rank < 0 || rank >= world) return OATTN_ERR_ARG;
+    PeerTarget t;
+    t.bufs = reinterpret_cast<const unsigned long long*>(peer_bufs_dev);
+    t.gen_push = reinterpret_cast<int*>(state);
+    t.rank = rank;
+    t.world = world;
+    // `out` is not written in this mode; pass the state block so that the common checks see a non-null pointer
+    return decode_common(q, nullptr, nullptr, const_cast<uint16_t*>(kc), const_cast<uint16_t*>(vc),
+                         reinterpret_cast<float*>(state), n_head, n_kv, head_dim, n_ctx, d_len, 0, scale, OATTN_FUSE_NONE, nullptr,
+                         1, workspace, workspace_bytes, stream, &t);
+}
+
+int oattn_peer_wait_combine(const void* my_buf, int world, float* out, int n_head, int head_dim, void* state, void* stream) {
+    if (!device_ready()) return OATTN_ERR_DEVICE;
+    if (!my_buf || !out || !state || n_head <= 0 || world < 1 || world > DECODE_MAX_RANKS) return OATTN_ERR_ARG;
+    if (head_dim != 64 && head_dim != 128) return OATTN_ERR_UNSUPPORTED;
+    int* st = reinterpret_cast<int*>(state);
+    cudaError_t e = launch_peer_wait_combine(my_buf, world, out, n_head, head_dim, st + n_head, st + 2 * n_head,
+                                             (cudaStream_t)stream, &g_launches);
+    return e == cudaSuccess ? OATTN_OK : cuda_fail(e, "peer wait/combine launch");
+}
+
+int oattn_peer_status(const void* state, int n_head, int* status) {
+    if (!state || !status || n_head <= 0) return OATTN_ERR_ARG;
+    cudaError_t e = cudaMemcpy(status, reinterpret_cast<const int*>(state) + 2 * n_head, sizeof(int), cudaMemcpyDeviceToHost);
+    return e == cudaSuccess ? OATTN_OK : cuda_fail(e, "peer status read");
 }
 
 int oattn_combine(const float* parts, int n_parts, float* out, int n_head, int head_dim, void* stream) {

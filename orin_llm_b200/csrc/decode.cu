@@ -356,14 +356,20 @@ struct CombineArgs {
     const int* d_pos;
     int pos_bias, n_ctx, n_splits, min_tiles;
     int emit_partial;
+    // peer exchange (multi-GPU): when peer_bufs is set the un-normalised record of head h is stored straight into
+    // every rank's exchange buffer (plain stores over NVLink), followed by a per-(source, head) generation flag
+    const unsigned long long* peer_bufs;   // device array of `world` pointers (this rank's own buffer included)
+    int* gen_push;                          // [n_head] private generation counters of this rank
+    int rank, world, n_head;
 };
 
-constexpr int kCombineThreads = 256;
+constexpr int kCombineThreads = 512;
+constexpr int kCombineWarps = kCombineThreads / 32;
 
 __global__ void __launch_bounds__(kCombineThreads) combine_kernel(const CombineArgs p) {
     __shared__ float s_w[DECODE_MAX_SPLITS];
-    __shared__ float s_red[kCombineThreads / 32];
-    __shared__ float4 s_acc[kCombineThreads / 32][32];
+    __shared__ float s_red[kCombineWarps];
+    __shared__ float4 s_acc[kCombineWarps][32];
     const int h = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int hd = p.head_dim;
 
@@ -377,44 +383,70 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(const CombineA
     const float* ml = p.ml_base + (size_t)h * p.ml_hs;
     const float* ob = p.o_base + (size_t)h * p.o_hs;
 
-    // M = max m
-    float mx = -CUDART_INF_F;
-    for (int s = tid; s < n; s += kCombineThreads) mx = fmaxf(mx, ml[(size_t)s * p.ml_ss]);
+    // The partials were written a moment ago and sit in L2; the kernel is a chain of L2 round trips, so every
+    // phase issues all of its loads before it uses any of them.  (m, l) of part tid: one load per thread
+    // (n <= DECODE_MAX_SPLITS = kCombineThreads).
+    float2 my = make_float2(-CUDART_INF_F, 0.f);
+    if (tid < n) my = make_float2(ml[(size_t)tid * p.ml_ss], ml[(size_t)tid * p.ml_ss + 1]);
+    // prefetch this warp's O rows (up to 4 parts in flight per lane) while the weights are being computed
+    constexpr int U = 4;
+    float4 pre[U];
+    const bool lane_ok = lane * 4 < hd;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        const int s = warp + u * kCombineWarps;
+        pre[u] = (lane_ok && s < n) ? *reinterpret_cast<const float4*>(ob + (size_t)s * p.o_ss + lane * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+
+    float mx = my.x;
 #pragma unroll
     for (int off = 16; off; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
     if (lane == 0) s_red[warp] = mx;
     __syncthreads();
     float M = -CUDART_INF_F;
 #pragma unroll
-    for (int w = 0; w < kCombineThreads / 32; ++w) M = fmaxf(M, s_red[w]);
+    for (int w = 0; w < kCombineWarps; ++w) M = fmaxf(M, s_red[w]);
     __syncthreads();
 
-    // weights and L
-    float lsum = 0.f;
-    for (int s = tid; s < n; s += kCombineThreads) {
-        const float m = ml[(size_t)s * p.ml_ss];
-        const float w = (m == -CUDART_INF_F) ? 0.f : __expf(m - M);
-        s_w[s] = w;
-        lsum += w * ml[(size_t)s * p.ml_ss + 1];
-    }
+    const float wgt = (my.x == -CUDART_INF_F) ? 0.f : __expf(my.x - M);
+    if (tid < n) s_w[tid] = wgt;
+    float lsum = wgt * my.y;
 #pragma unroll
     for (int off = 16; off; off >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, off);
     if (lane == 0) s_red[warp] = lsum;
     __syncthreads();
     float Lsum = 0.f;
 #pragma unroll
-    for (int w = 0; w < kCombineThreads / 32; ++w) Lsum += s_red[w];
+    for (int w = 0; w < kCombineWarps; ++w) Lsum += s_red[w];
 
-    // O: warp w takes parts w, w+8, ...; lane takes 4 consecutive dims
+    // O: warp w takes parts w, w+16, ...; lane takes 4 consecutive dims
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (lane * 4 < hd) {
-        for (int s = warp; s < n; s += kCombineThreads / 32) {
-            const float w = s_w[s];
-            const float4 v = *reinterpret_cast<const float4*>(ob + (size_t)s * p.o_ss + lane * 4);
-            acc.x = fmaf(w, v.x, acc.x);
-            acc.y = fmaf(w, v.y, acc.y);
-            acc.z = fmaf(w, v.z, acc.z);
-            acc.w = fmaf(w, v.w, acc.w);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        const int s = warp + u * kCombineWarps;
+        const float w = s < n ? s_w[s] : 0.f;
+        acc.x = fmaf(w, pre[u].x, acc.x);
+        acc.y = fmaf(w, pre[u].y, acc.y);
+        acc.z = fmaf(w, pre[u].z, acc.z);
+        acc.w = fmaf(w, pre[u].w, acc.w);
+    }
+    if (lane_ok) {
+        for (int s0 = warp + U * kCombineWarps; s0 < n; s0 += U * kCombineWarps) {
+            float4 v[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int s = s0 + u * kCombineWarps;
+                v[u] = s < n ? *reinterpret_cast<const float4*>(ob + (size_t)s * p.o_ss + lane * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int s = s0 + u * kCombineWarps;
+                const float w = s < n ? s_w[s] : 0.f;
+                acc.x = fmaf(w, v[u].x, acc.x);
+                acc.y = fmaf(w, v[u].y, acc.y);
+                acc.z = fmaf(w, v[u].z, acc.z);
+                acc.w = fmaf(w, v[u].w, acc.w);
+            }
         }
     }
     s_acc[warp][lane] = acc;
@@ -423,11 +455,26 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(const CombineA
         const int l4 = tid >> 2, e = tid & 3;
         float v = 0.f;
 #pragma unroll
-        for (int w = 0; w < kCombineThreads / 32; ++w) {
+        for (int w = 0; w < kCombineWarps; ++w) {
             const float4 a = s_acc[w][l4];
             v += (e == 0) ? a.x : (e == 1) ? a.y : (e == 2) ? a.z : a.w;
         }
-        if (p.emit_partial) {
+        if (p.emit_partial && p.peer_bufs) {
+            const int g = p.gen_push[h] + 1;          // generation of this call; only this CTA touches gen_push[h]
+            const size_t rec_sz = hd + PART_PAD;
+            for (int r = 0; r < p.world; ++r) {
+                float* rec = reinterpret_cast<float*>(p.peer_bufs[r]) +
+                             ((size_t)((g & 1) * p.world + p.rank) * p.n_head + h) * rec_sz;
+                rec[tid] = v;
+                if (tid == 0) {
+                    rec[hd + 0] = M;
+                    rec[hd + 1] = Lsum;
+                    rec[hd + 2] = 0.f;
+                    rec[hd + 3] = 0.f;
+                }
+            }
+            __threadfence_system();
+        } else if (p.emit_partial) {
             float* rec = p.out + (size_t)h * (hd + PART_PAD);
             rec[tid] = v;
             if (tid == 0) {
@@ -437,9 +484,80 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(const CombineA
                 rec[hd + 3] = 0.f;
             }
         } else {
-            p.out[(size_t)h * hd + tid] = v / Lsum;
+            p.out[(size_t)h * hd + tid] = Lsum > 0.f ? v / Lsum : 0.f;
         }
     }
+    if (p.emit_partial && p.peer_bufs) {
+        // every thread fenced its own record stores above; after the barrier one thread per destination rank
+        // publishes the generation, which the destination's wait kernel polls
+        __syncthreads();
+        const int g = p.gen_push[h] + 1;
+        if (tid < p.world) {
+            unsigned* flags = reinterpret_cast<unsigned*>(reinterpret_cast<unsigned char*>(p.peer_bufs[tid]) +
+                                                          peer_flags_offset(p.world, p.n_head, hd));
+            __threadfence_system();
+            asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(flags + (size_t)p.rank * p.n_head + h), "r"((unsigned)g) : "memory");
+        }
+        __syncthreads();
+        if (tid == 0) p.gen_push[h] = g;
+    }
+}
+
+// ---- wait for every rank's record of this generation and merge them -------------------------------------------
+// One CTA per head.  Thread r polls the flag that rank r sets after its record for this head has landed in this
+// rank's exchange buffer; the poll is bounded (about two seconds), after which a status word is raised and the
+// kernel returns without touching the output.
+struct PeerWaitArgs {
+    const unsigned char* my_buf;
+    float* out;
+    int* gen_wait;      // [n_head]
+    int* status;
+    int world, n_head, head_dim;
+};
+
+__global__ void __launch_bounds__(128) peer_wait_combine_kernel(const PeerWaitArgs p) {
+    __shared__ float s_m[DECODE_MAX_RANKS], s_l[DECODE_MAX_RANKS], s_w[DECODE_MAX_RANKS];
+    __shared__ int s_fail;
+    const int h = blockIdx.x, tid = threadIdx.x, hd = p.head_dim;
+    const int g = p.gen_wait[h] + 1;
+    if (tid == 0) s_fail = 0;
+    __syncthreads();
+    if (tid < p.world) {
+        const unsigned* flag = reinterpret_cast<const unsigned*>(p.my_buf + peer_flags_offset(p.world, p.n_head, hd)) +
+                               (size_t)tid * p.n_head + h;
+        const long long t0 = clock64();
+        unsigned val;
+        for (;;) {
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(val) : "l"(flag) : "memory");
+            if ((int)(val - (unsigned)g) >= 0) break;
+            if (clock64() - t0 > 4000000000LL) { s_fail = 1; break; }
+        }
+    }
+    __syncthreads();
+    if (s_fail) {
+        if (tid == 0 && p.status) atomicExch(p.status, 1);
+        return;
+    }
+    const size_t rec_sz = hd + PART_PAD;
+    const float* recs = reinterpret_cast<const float*>(p.my_buf) + ((size_t)(g & 1) * p.world * p.n_head + h) * rec_sz;
+    const size_t rank_stride = (size_t)p.n_head * rec_sz;
+    if (tid < p.world) {
+        s_m[tid] = __ldcg(recs + tid * rank_stride + hd);
+        s_l[tid] = __ldcg(recs + tid * rank_stride + hd + 1);
+    }
+    __syncthreads();
+    float M = -CUDART_INF_F;
+    for (int r = 0; r < p.world; ++r) M = fmaxf(M, s_m[r]);
+    if (tid < p.world) s_w[tid] = (s_m[tid] == -CUDART_INF_F) ? 0.f : __expf(s_m[tid] - M);
+    __syncthreads();
+    float L = 0.f;
+    for (int r = 0; r < p.world; ++r) L += s_w[r] * s_l[r];
+    if (tid < hd) {
+        float acc = 0.f;
+        for (int r = 0; r < p.world; ++r) acc = fmaf(s_w[r], __ldcg(recs + r * rank_stride + tid), acc);
+        p.out[(size_t)h * hd + tid] = L > 0.f ? acc / L : 0.f;
+    }
+    if (tid == 0) p.gen_wait[h] = g;
 }
 
 template <int HD, bool WIDE>
@@ -525,6 +643,11 @@ cudaError_t launch_decode(const DecodeArgs& a, cudaStream_t stream, unsigned lon
     c.n_splits = a.n_splits;
     c.min_tiles = a.min_tiles;
     c.emit_partial = a.emit_partial;
+    c.peer_bufs = a.peer_bufs;
+    c.gen_push = a.gen_push;
+    c.rank = a.rank;
+    c.world = a.world;
+    c.n_head = a.n_head;
     combine_kernel<<<a.n_head, kCombineThreads, 0, stream>>>(c);
     if (launches) *launches += 2;
     return cudaGetLastError();
@@ -549,7 +672,27 @@ cudaError_t launch_combine_records(const float* parts, int n_parts, float* out, 
     c.n_splits = 0;
     c.min_tiles = 1;
     c.emit_partial = 0;
+    c.peer_bufs = nullptr;
+    c.gen_push = nullptr;
+    c.rank = 0;
+    c.world = 1;
+    c.n_head = n_head;
     combine_kernel<<<n_head, kCombineThreads, 0, stream>>>(c);
+    if (launches) *launches += 1;
+    return cudaGetLastError();
+}
+
+cudaError_t launch_peer_wait_combine(const void* my_buf, int world, float* out, int n_head, int head_dim, int* gen_wait,
+                                     int* status, cudaStream_t stream, unsigned long long* launches) {
+    PeerWaitArgs w;
+    w.my_buf = reinterpret_cast<const unsigned char*>(my_buf);
+    w.out = out;
+    w.gen_wait = gen_wait;
+    w.status = status;
+    w.world = world;
+    w.n_head = n_head;
+    w.head_dim = head_dim;
+    peer_wait_combine_kernel<<<n_head, 128, 0, stream>>>(w);
     if (launches) *launches += 1;
     return cudaGetLastError();
 }

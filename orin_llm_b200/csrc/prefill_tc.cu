@@ -6,8 +6,9 @@
 // log2 domain and the softmax is exp2.
 //
 // One CTA = one 128-row query tile of ONE kv head; a row is a (token, head-in-group) pair, row
-// R -> token t0 + R/G, head kvh*G + R%G (G = n_head/n_kv must divide 128), so a single pass over the
-// kv head's K/V rows serves all G query heads of 128/G tokens.  The KV sequence is walked in blocks of
+// R -> token t0 + R/G, head kvh*G + R%G (G = n_head/n_kv), so a single pass over the kv head's K/V rows
+// serves all G query heads of floor(128/G) tokens (when G does not divide 128 the last few tile rows are
+// zero and unused).  The KV sequence is walked in blocks of
 // 128 rows.  320 threads in three roles:
 //   warp 0   (one lane)  TMA producer: Q tile once, then 128-row K blocks (three-stage ring) and V blocks
 //                        (two-stage ring) with cp.async.bulk.tensor, 128-byte swizzle, no multicast; rows
@@ -82,7 +83,7 @@ __device__ long long g_trace[3][8][128];
 struct TcArgs {
     float* out;
     int* status;
-    int n_head, n_kv, n_past, batch, G, TQ;
+    int n_head, n_kv, n_past, batch, G, TQ;   // TQ = floor(128 / G) tokens per tile
 };
 
 // ---- PTX wrappers ---------------------------------------------------------------------------------
@@ -261,6 +262,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     }
+    // Tile rows the TMA box does not cover (G * TQ < 128) are zeroed once; inside a slab row r is the 128 bytes at
+    // r * 128, whatever the swizzle.
+    for (int i = tid; i < (BM - p.G * p.TQ) * 16; i += kThreads) {
+        const int r = p.G * p.TQ + i / 16, c = i % 16;
+        *reinterpret_cast<uint4*>(smem + OFF_Q + (c >> 3) * SLAB + r * 128 + (c & 7) * 16) = make_uint4(0, 0, 0, 0);
+    }
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(s_tmem)), "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
@@ -276,7 +284,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         if (lane == 0) {
             bool ok = true;
             int k_issued[NKS] = {}, v_issued[NVS] = {};
-            mbar_expect_tx(bar(Q_FULL), TILE);
+            mbar_expect_tx(bar(Q_FULL), 2 * 128 * p.G * p.TQ);       // two slabs of G*TQ rows of 128 bytes
             tma_load_3d(sbase + OFF_Q, &tmQ, 0, kvh * p.G, t0, bar(Q_FULL));
             tma_load_3d(sbase + OFF_Q + SLAB, &tmQ, 64, kvh * p.G, t0, bar(Q_FULL));
             auto load_k = [&](int j) {
@@ -554,7 +562,7 @@ cudaError_t prefill_tc_set_attributes() {
 cudaError_t launch_prefill_tc(const PrefillArgs& a, int sm_count, cudaStream_t stream, unsigned long long* launches) {
     (void)sm_count;
     const int G = a.n_head / a.n_kv;
-    if (a.head_dim != HD || (128 % G) != 0 || !g_encode) return cudaErrorNotSupported;
+    if (a.head_dim != HD || G > 128 || !g_encode) return cudaErrorNotSupported;
     const int TQ = 128 / G;
     const uint64_t rows = (uint64_t)a.n_past + a.batch;          // rows past the chunk are never read (zero fill)
     CUtensorMap tmQ, tmK, tmV;

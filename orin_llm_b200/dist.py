@@ -43,6 +43,44 @@ def gather_records(local, world_buf, group=None):
     return world_buf
 
 
+class PeerSplitKVDecoder:
+    """Split-KV decode whose record exchange is done by the kernels themselves: the per-rank merge kernel stores
+    its record into every rank's exchange buffer with plain peer stores over NVLink and raises a flag, and the
+    final merge kernel waits (bounded) for the flags in its own buffer.  Two small kernels after the split kernel,
+    no collective call, graph-capturable.  The exchange buffers come from torch's symmetric memory (CUDA VMM
+    mappings of every rank's block); no multicast object is created and no library kernel ever sees a peer pointer."""
+
+    def __init__(self, n_head, n_kv, head_dim, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        from . import ops
+        self.ops = ops
+        self.n_head, self.n_kv, self.head_dim = n_head, n_kv, head_dim
+        group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        nbytes = ops.peer_buffer_bytes(self.world, n_head, head_dim)
+        if nbytes == 0:
+            raise RuntimeError("peer exchange does not cover this shape / world size")
+        self.buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=torch.device("cuda", torch.cuda.current_device()))
+        self.buf.zero_()
+        self.handle = symm_mem.rendezvous(self.buf, group)
+        self.peer_bufs_dev = int(self.handle.buffer_ptrs_dev)
+        self.state = torch.zeros(ops.peer_state_bytes(n_head), dtype=torch.uint8, device="cuda")
+        self.workspace = ops.decode_workspace(n_head, n_kv, head_dim)
+        torch.cuda.synchronize()
+        dist.barrier(group)            # every buffer is zeroed before anyone stores into it
+
+    def decode(self, q, kc_local, vc_local, n_ctx_local, d_len_local, scale, out):
+        o = self.ops
+        o.attn_decode_partial_push(q, kc_local, vc_local, self.n_head, self.n_kv, self.head_dim, n_ctx_local, d_len_local,
+                                   scale, self.peer_bufs_dev, self.rank, self.world, self.state, self.workspace)
+        o.attn_peer_wait_combine(self.buf, self.world, out, self.n_head, self.head_dim, self.state)
+        return out
+
+    def status(self):
+        return self.ops.peer_status(self.state, self.n_head)
+
+
 class SplitKVDecoder:
     """Decode attention over a KV sequence that is sharded by rows across the ranks of `group`."""
 

@@ -155,6 +155,36 @@ def attn_decode_partial(q, kc, vc, part, n_head, n_kv, head_dim, n_ctx, d_len, s
                                                _ptr(d_len), scale, _ptr(ws), ws.numel(), _stream()))
 
 
+def peer_buffer_bytes(world, n_head, head_dim):
+    return int(capi.lib().oattn_peer_buffer_bytes(world, n_head, head_dim))
+
+
+def peer_state_bytes(n_head):
+    return int(capi.lib().oattn_peer_state_bytes(n_head))
+
+
+def attn_decode_partial_push(q, kc, vc, n_head, n_kv, head_dim, n_ctx, d_len, scale, peer_bufs_dev, rank, world, state,
+                             workspace=None):
+    """Partial (m, l, O) over the local rows, stored straight into every rank's exchange buffer (peer stores).
+    peer_bufs_dev: address of a device array holding `world` buffer pointers; state: uint8 tensor of
+    peer_state_bytes(n_head), zero-filled once."""
+    ws = workspace if workspace is not None else decode_workspace(n_head, n_kv, head_dim)
+    capi.check(capi.lib().oattn_decode_partial_push(_ptr(q), _ptr(kc), _ptr(vc), n_head, n_kv, head_dim, n_ctx, _ptr(d_len),
+                                                    scale, _ptr(ws), ws.numel(), ctypes.c_void_p(int(peer_bufs_dev)), rank,
+                                                    world, _ptr(state), _stream()))
+
+
+def attn_peer_wait_combine(my_buf, world, out, n_head, head_dim, state):
+    """Wait (bounded) until every rank's record of this step has landed in `my_buf`, then merge them into out."""
+    capi.check(capi.lib().oattn_peer_wait_combine(_ptr(my_buf), world, _ptr(out), n_head, head_dim, _ptr(state), _stream()))
+
+
+def peer_status(state, n_head):
+    st = ctypes.c_int(-1)
+    capi.check(capi.lib().oattn_peer_status(_ptr(state), n_head, ctypes.byref(st)))
+    return st.value
+
+
 def attn_combine(parts, n_parts, out, n_head, head_dim):
     capi.check(capi.lib().oattn_combine(_ptr(parts), n_parts, _ptr(out), n_head, head_dim, _stream()))
 
