@@ -8,7 +8,8 @@ Default workload `decode_3b_L1048576`: Qwen2.5-3B attention shape (16 query / 2 
 36 layers), KV length 1,048,576, fp16 KV i.i.d. N(0,1).  One STEP is the attention of one decoded token:
 36 decode-attention calls, one per layer, each over that layer's own KV buffers (1 GiB per layer, 36 GiB
 in all, so every call streams from HBM, never from L2).  With N GPUs the KV rows are cut into N contiguous
-slices (strong scaling); each call is local partial -> NCCL all-gather of the (m, l, O) records -> combine.
+slices (strong scaling); each call is local partial -> exchange of the (m, l, O) records -> merge, the exchange done
+by the merge kernel itself with peer stores over NVLink (--exchange nccl: NCCL all-gather instead).
 
 The metric is KV GB/s: algorithmic KV bytes (2 * n_kv * L * head_dim * 2 B per call) per second of step time.
 Prints ONE JSON line (rank 0).
@@ -40,6 +41,8 @@ PREFILL_WORKLOADS = {
     "prefill_8b_off4096": dict(n_head=32, n_kv=8, head_dim=128, batch=512, n_past=4096, theta=5e5, layers=32),
     "prefill_8b_off8192": dict(n_head=32, n_kv=8, head_dim=128, batch=512, n_past=8192, theta=5e5, layers=32),
 }
+NCU_READ_PER_KV_BYTE = 134.258 / 134.218     # dram__bytes_read.sum / algorithmic K+V bytes of the captured launch
+NCU_WRITE_BYTES_PER_LAUNCH = 4.02e6           # dram__bytes_write.sum of the captured launch
 CPU_SAMPLE_L = 131072      # rows of ONE layer call the CPU baseline / reference arm processes per step
 
 
@@ -214,15 +217,15 @@ def run_b200(args, w):
     dec = None
     if world > 1:
         exchange = args.exchange
-        if exchange == "peer":
+        if exchange.startswith("peer"):
             try:
-                dec = PeerSplitKVDecoder(n_head, n_kv, hd)
+                dec = PeerSplitKVDecoder(n_head, n_kv, hd, fused=(exchange == "peer"))
             except Exception as e:      # no peer-mapped memory on this box: fall back to the NCCL all-gather
                 if rank == 0:
                     print("peer exchange unavailable (%s); using the NCCL all-gather" % e, file=sys.stderr)
                 exchange = "nccl"
         # every rank must take the same path
-        flag = torch.tensor([1 if exchange == "peer" else 0], device="cuda")
+        flag = torch.tensor([1 if exchange.startswith("peer") else 0], device="cuda")
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)
         if int(flag.item()) == 0:
             exchange = "nccl"
@@ -260,6 +263,14 @@ def run_b200(args, w):
     for _ in range(max(args.warmup, 3)):
         step()
     torch.cuda.synchronize()
+    if world > 1 and exchange != "nccl":
+        # the kernel-driven exchange must give what the collective gives: check one layer call on every rank
+        chk = SplitKVDecoder(n_head, n_kv, hd)
+        want = torch.empty(n_head, hd, device="cuda")
+        chk.decode(q[0], Kc[0], Vc[0], n_loc, d_len, scale, want)
+        torch.cuda.synchronize()
+        if not torch.allclose(out[0], want, rtol=1e-5, atol=1e-6):
+            raise SystemExit("peer exchange result differs from the all-gather result on rank %d" % rank)
 
     # ---- timed region: kernel path with everything resident in HBM ----
     # The step is replayed from a CUDA graph, as the reference replays its decode step
@@ -345,7 +356,7 @@ def run_b200(args, w):
     h2d = layers * (n_head + 2 * n_kv) * hd * 4
     d2h = layers * n_head * hd * 4
 
-    if exchange == "peer" and dec.status() != 0:
+    if exchange.startswith("peer") and dec.status() != 0:
         raise SystemExit("peer exchange: a bounded flag wait ran out (rank %d)" % rank)
 
     def finish():
@@ -373,14 +384,14 @@ def run_b200(args, w):
         "algorithmic_bytes_per_launch": per_launch_bytes, "peak_source": peak_kind + " (MEASURED_PEAKS.json hbm_gbs)",
         "frac_of_nominal_8tbs": (achieved / 8000.0) if achieved else None,
     }
-    ncu_traffic = os.path.join(ROOT, "profiles", "decode_split_traffic.json")
-    if os.path.exists(ncu_traffic):
-        try:
-            t = json.load(open(ncu_traffic))
-            roofline["traffic"] = t["dram_bytes_per_kv_byte"] * per_launch_bytes
-            roofline["traffic_source"] = t.get("source")
-        except Exception:
-            pass
+    # DRAM traffic of one split-kernel launch, from the ncu capture summarised in profiles/decode_split_kernel_L131072.md
+    # (16/2 heads, 131072 rows: dram__bytes_read 134.258 MB for 134.218 MB of K/V, dram__bytes_write 4.0 MB).  Reads
+    # grow with the rows streamed and are scaled by the bytes of this launch; the writes (split partials) do not
+    # depend on the length and are added as captured.
+    if per_launch_bytes:
+        roofline["traffic"] = NCU_READ_PER_KV_BYTE * per_launch_bytes + NCU_WRITE_BYTES_PER_LAUNCH
+        roofline["traffic_source"] = ("ncu capture at L=131072 (profiles/decode_split_kernel_L131072.md): reads scaled by "
+                                      "bytes streamed, writes as captured")
 
     cpu = None
     if not args.no_cpu_baseline:
@@ -395,7 +406,8 @@ def run_b200(args, w):
         "config": {"workload": args.workload, "n_head": n_head, "n_kv": n_kv, "head_dim": hd, "layers_per_step": layers,
                    "kv_len": L, "kv_rows_per_gpu": n_loc, "parallelism": "kv-split x%d" % world,
                    "launch": "eager" if args.no_graph else "cuda graph replay of the step",
-                   "exchange": {"none": "single GPU", "peer": "records stored into peers' buffers by the merge kernel (NVLink peer stores) + flag wait",
+                   "exchange": {"none": "single GPU", "peer": "merge kernel stores its record into every peer's buffer (NVLink peer stores), waits for the peers' flags and merges",
+                                "peer-split": "as peer, with the flag wait and final merge in a launch of their own",
                                 "nccl": "NCCL all-gather of the records"}[exchange],
                    "l2": "inputs larger than L2: each of the %d layer calls of a step reads its own %.0f MiB of KV" % (
                        layers, per_launch_bytes / 2**20)},
@@ -488,7 +500,7 @@ def main():
     ap.add_argument("--workload", default="decode_3b_L1048576", choices=sorted(WORKLOADS) + sorted(PREFILL_WORKLOADS))
     ap.add_argument("--layers", type=int, default=None, help="override the layer calls per step")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"], help="multi-GPU record exchange")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "peer-split", "nccl"], help="multi-GPU record exchange")
     ap.add_argument("--no-graph", action="store_true", help="launch the step eagerly instead of replaying a CUDA graph")
     args = ap.parse_args()
     if args.workload in PREFILL_WORKLOADS:

@@ -164,6 +164,13 @@ int oattn_decode_partial_push(const float* q, const uint16_t* kc, const uint16_t
                               int n_ctx, const int* d_len, float scale, void* workspace, size_t workspace_bytes,
                               const void* peer_bufs_dev, int rank, int world, void* state, void* stream);
 int oattn_peer_wait_combine(const void* my_buf, int world, float* out, int n_head, int head_dim, void* state, void* stream);
+/* Both steps in two launches instead of three: the merge launch that stores this rank's record into every exchange
+ * buffer also waits for the other ranks' records and writes the merged out [n_head][head_dim].  Every rank must be
+ * running on a GPU of its own (the launch waits for kernels of the other ranks); do not mix with the two calls above
+ * on the same state block.  No counterpart in the reference. */
+int oattn_decode_peer(const float* q, const uint16_t* kc, const uint16_t* vc, float* out, int n_head, int n_kv, int head_dim,
+                      int n_ctx, const int* d_len, float scale, void* workspace, size_t workspace_bytes,
+                      const void* peer_bufs_dev, int rank, int world, void* state, void* stream);
 /* Blocking read of the status word (0 = every wait so far was satisfied). */
 int oattn_peer_status(const void* state, int n_head, int* status);
 

@@ -43,6 +43,8 @@ struct DecodeArgs {
     const unsigned long long* peer_bufs = nullptr;   // multi-GPU peer exchange: device array of `world` buffer pointers
     int* gen_push = nullptr;                          // [n_head] generation counters (private to this rank)
     int rank = 0, world = 1;
+    int fused_wait = 0;                               // the merge launch also waits for every rank's record and writes `out`
+    int* peer_status = nullptr;                       // raised when that wait ran out
 };
 
 // Size of the scratch block built into the library for oattn_decode_noalloc, and its device address on the

@@ -361,10 +361,61 @@ struct CombineArgs {
     const unsigned long long* peer_bufs;   // device array of `world` pointers (this rank's own buffer included)
     int* gen_push;                          // [n_head] private generation counters of this rank
     int rank, world, n_head;
+    int fused_wait;                         // also wait for all ranks' records and write the final output to `out`
+    int* status;                            // raised when that wait ran out
 };
 
 constexpr int kCombineThreads = 512;
 constexpr int kCombineWarps = kCombineThreads / 32;
+
+// ---- wait for every rank's record of one generation and merge them ---------------------------------------------
+// Called by all threads of a CTA that owns head h.  Thread r polls the flag that rank r sets after its record for
+// this head has landed in this rank's exchange buffer; the poll is bounded (about two seconds), after which a status
+// word is raised and the output is left untouched.  s_a / s_b: two shared float arrays of >= DECODE_MAX_RANKS.
+__device__ __forceinline__ void peer_wait_merge(const unsigned char* my_buf, int g, int h, int world, int n_head, int hd,
+                                                float* out, int* status, float* s_a, float* s_b) {
+    __shared__ int s_fail;
+    __shared__ float s_wr[DECODE_MAX_RANKS];
+    const int tid = threadIdx.x;
+    __syncthreads();
+    if (tid == 0) s_fail = 0;
+    __syncthreads();
+    if (tid < world) {
+        const unsigned* flag = reinterpret_cast<const unsigned*>(my_buf + peer_flags_offset(world, n_head, hd)) +
+                               (size_t)tid * n_head + h;
+        const long long t0 = clock64();
+        unsigned val;
+        for (;;) {
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(val) : "l"(flag) : "memory");
+            if ((int)(val - (unsigned)g) >= 0) break;
+            if (clock64() - t0 > 4000000000LL) { s_fail = 1; break; }
+        }
+    }
+    __syncthreads();
+    if (s_fail) {
+        if (tid == 0 && status) atomicExch(status, 1);
+        return;
+    }
+    const size_t rec_sz = hd + PART_PAD;
+    const float* recs = reinterpret_cast<const float*>(my_buf) + ((size_t)(g & 1) * world * n_head + h) * rec_sz;
+    const size_t rank_stride = (size_t)n_head * rec_sz;
+    if (tid < world) {
+        s_a[tid] = __ldcg(recs + tid * rank_stride + hd);
+        s_b[tid] = __ldcg(recs + tid * rank_stride + hd + 1);
+    }
+    __syncthreads();
+    float M = -CUDART_INF_F;
+    for (int r = 0; r < world; ++r) M = fmaxf(M, s_a[r]);
+    if (tid < world) s_wr[tid] = (s_a[tid] == -CUDART_INF_F) ? 0.f : __expf(s_a[tid] - M);
+    __syncthreads();
+    float L = 0.f;
+    for (int r = 0; r < world; ++r) L += s_wr[r] * s_b[r];
+    if (tid < hd) {
+        float acc = 0.f;
+        for (int r = 0; r < world; ++r) acc = fmaf(s_wr[r], __ldcg(recs + r * rank_stride + tid), acc);
+        out[(size_t)h * hd + tid] = L > 0.f ? acc / L : 0.f;
+    }
+}
 
 __global__ void __launch_bounds__(kCombineThreads) combine_kernel(const CombineArgs p) {
     __shared__ float s_w[DECODE_MAX_SPLITS];
@@ -473,7 +524,6 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(const CombineA
                     rec[hd + 3] = 0.f;
                 }
             }
-            __threadfence_system();
         } else if (p.emit_partial) {
             float* rec = p.out + (size_t)h * (hd + PART_PAD);
             rec[tid] = v;
@@ -488,15 +538,20 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(const CombineA
         }
     }
     if (p.emit_partial && p.peer_bufs) {
-        // every thread fenced its own record stores above; after the barrier one thread per destination rank
-        // publishes the generation, which the destination's wait kernel polls
+        // the barrier orders every thread's record stores before the flag stores below; one thread per destination
+        // rank then publishes the generation with a system-scope release (cumulative over the stores the barrier
+        // made visible to it), which the destination polls with an acquire
         __syncthreads();
         const int g = p.gen_push[h] + 1;
         if (tid < p.world) {
             unsigned* flags = reinterpret_cast<unsigned*>(reinterpret_cast<unsigned char*>(p.peer_bufs[tid]) +
                                                           peer_flags_offset(p.world, p.n_head, hd));
-            __threadfence_system();
             asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(flags + (size_t)p.rank * p.n_head + h), "r"((unsigned)g) : "memory");
+        }
+        if (p.fused_wait) {
+            // same launch also waits for the other ranks' records of this generation and writes the final output
+            peer_wait_merge(reinterpret_cast<const unsigned char*>(p.peer_bufs[p.rank]), g, h, p.world, p.n_head, hd,
+                            p.out, p.status, s_w, s_red);
         }
         __syncthreads();
         if (tid == 0) p.gen_push[h] = g;
@@ -516,48 +571,12 @@ struct PeerWaitArgs {
 };
 
 __global__ void __launch_bounds__(128) peer_wait_combine_kernel(const PeerWaitArgs p) {
-    __shared__ float s_m[DECODE_MAX_RANKS], s_l[DECODE_MAX_RANKS], s_w[DECODE_MAX_RANKS];
-    __shared__ int s_fail;
-    const int h = blockIdx.x, tid = threadIdx.x, hd = p.head_dim;
+    __shared__ float s_m[DECODE_MAX_RANKS], s_l[DECODE_MAX_RANKS];
+    const int h = blockIdx.x;
     const int g = p.gen_wait[h] + 1;
-    if (tid == 0) s_fail = 0;
+    peer_wait_merge(p.my_buf, g, h, p.world, p.n_head, p.head_dim, p.out, p.status, s_m, s_l);
     __syncthreads();
-    if (tid < p.world) {
-        const unsigned* flag = reinterpret_cast<const unsigned*>(p.my_buf + peer_flags_offset(p.world, p.n_head, hd)) +
-                               (size_t)tid * p.n_head + h;
-        const long long t0 = clock64();
-        unsigned val;
-        for (;;) {
-            asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(val) : "l"(flag) : "memory");
-            if ((int)(val - (unsigned)g) >= 0) break;
-            if (clock64() - t0 > 4000000000LL) { s_fail = 1; break; }
-        }
-    }
-    __syncthreads();
-    if (s_fail) {
-        if (tid == 0 && p.status) atomicExch(p.status, 1);
-        return;
-    }
-    const size_t rec_sz = hd + PART_PAD;
-    const float* recs = reinterpret_cast<const float*>(p.my_buf) + ((size_t)(g & 1) * p.world * p.n_head + h) * rec_sz;
-    const size_t rank_stride = (size_t)p.n_head * rec_sz;
-    if (tid < p.world) {
-        s_m[tid] = __ldcg(recs + tid * rank_stride + hd);
-        s_l[tid] = __ldcg(recs + tid * rank_stride + hd + 1);
-    }
-    __syncthreads();
-    float M = -CUDART_INF_F;
-    for (int r = 0; r < p.world; ++r) M = fmaxf(M, s_m[r]);
-    if (tid < p.world) s_w[tid] = (s_m[tid] == -CUDART_INF_F) ? 0.f : __expf(s_m[tid] - M);
-    __syncthreads();
-    float L = 0.f;
-    for (int r = 0; r < p.world; ++r) L += s_w[r] * s_l[r];
-    if (tid < hd) {
-        float acc = 0.f;
-        for (int r = 0; r < p.world; ++r) acc = fmaf(s_w[r], __ldcg(recs + r * rank_stride + tid), acc);
-        p.out[(size_t)h * hd + tid] = L > 0.f ? acc / L : 0.f;
-    }
-    if (tid == 0) p.gen_wait[h] = g;
+    if (threadIdx.x == 0) p.gen_wait[h] = g;
 }
 
 template <int HD, bool WIDE>
@@ -648,6 +667,8 @@ cudaError_t launch_decode(const DecodeArgs& a, cudaStream_t stream, unsigned lon
     c.rank = a.rank;
     c.world = a.world;
     c.n_head = a.n_head;
+    c.fused_wait = a.fused_wait;
+    c.status = a.peer_status;
     combine_kernel<<<a.n_head, kCombineThreads, 0, stream>>>(c);
     if (launches) *launches += 2;
     return cudaGetLastError();
@@ -677,6 +698,8 @@ cudaError_t launch_combine_records(const float* parts, int n_parts, float* out, 
     c.rank = 0;
     c.world = 1;
     c.n_head = n_head;
+    c.fused_wait = 0;
+    c.status = nullptr;
     combine_kernel<<<n_head, kCombineThreads, 0, stream>>>(c);
     if (launches) *launches += 1;
     return cudaGetLastError();

@@ -45,15 +45,17 @@ def gather_records(local, world_buf, group=None):
 
 class PeerSplitKVDecoder:
     """Split-KV decode whose record exchange is done by the kernels themselves: the per-rank merge kernel stores
-    its record into every rank's exchange buffer with plain peer stores over NVLink and raises a flag, and the
-    final merge kernel waits (bounded) for the flags in its own buffer.  Two small kernels after the split kernel,
-    no collective call, graph-capturable.  The exchange buffers come from torch's symmetric memory (CUDA VMM
-    mappings of every rank's block); no multicast object is created and no library kernel ever sees a peer pointer."""
+    its record into every rank's exchange buffer with plain peer stores over NVLink and raises a flag, then waits
+    (bounded) for the other ranks' flags in its own buffer and writes the merged output.  One small kernel after
+    the split kernel, no collective call, graph-capturable; fused=False keeps the wait in a launch of its own.
+    The exchange buffers come from torch's symmetric memory (CUDA VMM mappings of every rank's block); no multicast
+    object is created and no library kernel ever sees a peer pointer."""
 
-    def __init__(self, n_head, n_kv, head_dim, group=None):
+    def __init__(self, n_head, n_kv, head_dim, group=None, fused=True):
         import torch.distributed._symmetric_memory as symm_mem
         from . import ops
         self.ops = ops
+        self.fused = fused
         self.n_head, self.n_kv, self.head_dim = n_head, n_kv, head_dim
         group = group if group is not None else dist.group.WORLD
         self.world = dist.get_world_size(group)
@@ -72,6 +74,10 @@ class PeerSplitKVDecoder:
 
     def decode(self, q, kc_local, vc_local, n_ctx_local, d_len_local, scale, out):
         o = self.ops
+        if self.fused:
+            o.attn_decode_peer(q, kc_local, vc_local, out, self.n_head, self.n_kv, self.head_dim, n_ctx_local, d_len_local,
+                               scale, self.peer_bufs_dev, self.rank, self.world, self.state, self.workspace)
+            return out
         o.attn_decode_partial_push(q, kc_local, vc_local, self.n_head, self.n_kv, self.head_dim, n_ctx_local, d_len_local,
                                    scale, self.peer_bufs_dev, self.rank, self.world, self.state, self.workspace)
         o.attn_peer_wait_combine(self.buf, self.world, out, self.n_head, self.head_dim, self.state)

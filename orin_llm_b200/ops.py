@@ -174,6 +174,16 @@ def attn_decode_partial_push(q, kc, vc, n_head, n_kv, head_dim, n_ctx, d_len, sc
                                                     world, _ptr(state), _stream()))
 
 
+def attn_decode_peer(q, kc, vc, out, n_head, n_kv, head_dim, n_ctx, d_len, scale, peer_bufs_dev, rank, world, state,
+                     workspace=None):
+    """Split-KV decode over this rank's rows with the record exchange and the final merge inside the merge launch
+    (every rank on a GPU of its own).  out [n_head][head_dim] is written on every rank."""
+    ws = workspace if workspace is not None else decode_workspace(n_head, n_kv, head_dim)
+    capi.check(capi.lib().oattn_decode_peer(_ptr(q), _ptr(kc), _ptr(vc), _ptr(out), n_head, n_kv, head_dim, n_ctx, _ptr(d_len),
+                                            scale, _ptr(ws), ws.numel(), ctypes.c_void_p(int(peer_bufs_dev)), rank, world,
+                                            _ptr(state), _stream()))
+
+
 def attn_peer_wait_combine(my_buf, world, out, n_head, head_dim, state):
     """Wait (bounded) until every rank's record of this step has landed in `my_buf`, then merge them into out."""
     capi.check(capi.lib().oattn_peer_wait_combine(_ptr(my_buf), world, _ptr(out), n_head, head_dim, _ptr(state), _stream()))

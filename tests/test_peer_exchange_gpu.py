@@ -48,3 +48,29 @@ def test_push_then_wait_on_one_device(ops, oracle, world):
             assert ops.peer_status(states[r], n_head) == 0
             assert_close(outs[r].cpu().numpy(), want, "step %d rank %d" % (step, r))
             assert torch.equal(outs[r], outs[0])
+
+
+def test_fused_exchange_world_one(ops, oracle):
+    """oattn_decode_peer (push, wait and merge in one launch) with a single rank: the launch waits only for its own
+    flag, so it can run alone on one GPU.  Covers the fused code path, its generation counter over repeated calls
+    (both record slots) and the status word; equal to the plain decode call."""
+    n_head, n_kv, hd, L = 16, 2, 128, 3000
+    scale = np.float32(1.0 / np.sqrt(hd))
+    buf = torch.zeros(ops.peer_buffer_bytes(1, n_head, hd), dtype=torch.uint8, device="cuda")
+    state = torch.zeros(ops.peer_state_bytes(n_head), dtype=torch.uint8, device="cuda")
+    ptrs = torch.tensor([buf.data_ptr()], dtype=torch.int64, device="cuda")
+    for step in range(3):
+        q, K, V = make_qkv(900 + step, n_head, n_kv, hd, L)
+        want = oracle.attend(q[0], K.astype(np.float32), V.astype(np.float32), L, scale)
+        dq, dK, dV = dev(q[0]), dev(K), dev(V)
+        d_len = torch.tensor([L], dtype=torch.int32, device="cuda")
+        out = torch.empty(n_head, hd, device="cuda")
+        ops.attn_decode_peer(dq, dK, dV, out, n_head, n_kv, hd, L, d_len, float(scale), ptrs.data_ptr(), 0, 1, state)
+        torch.cuda.synchronize()
+        assert ops.peer_status(state, n_head) == 0
+        assert_close(out.cpu().numpy(), want, "fused exchange step %d" % step)
+        ref = torch.empty(n_head, hd, device="cuda")
+        d_pos = torch.tensor([L - 1], dtype=torch.int32, device="cuda")
+        ops.attn_decode(dq, None, None, dK, dV, ref, n_head, n_kv, hd, L, d_pos, float(scale), fuse=ops.FUSE_NONE)
+        torch.cuda.synchronize()
+        assert torch.allclose(out, ref, rtol=1e-5, atol=1e-6)
