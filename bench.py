@@ -114,68 +114,88 @@ class ClockSampler:
 
 # ---------------------------------------------------------------------------------------------------
 # CPU side: the reference's own scalar attention (oracle/_ref) or its C restatement (oracle/)
-def cpu_attention_sample(w, threads=None):
-    """Times ONE decode-attention call of the workload's shape over CPU_SAMPLE_L rows on the host cores.
-    Returns (seconds, kind, cores, sample description)."""
-    from oracle.oracle import Oracle, RefLib
-    L = min(CPU_SAMPLE_L, w["L"])
-    n_head, n_kv, hd = w["n_head"], w["n_kv"], w["head_dim"]
-    rng = np.random.default_rng(7)
-    q = rng.standard_normal((n_head, hd), dtype=np.float32).astype(np.float16).astype(np.float32)
-    kc = rng.standard_normal((n_kv, L, hd), dtype=np.float32).astype(np.float16).astype(np.float32)
-    vc = rng.standard_normal((n_kv, L, hd), dtype=np.float32).astype(np.float16).astype(np.float32)
-    scale = np.float32(1.0 / np.sqrt(hd))
-    ncpu = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
-    threads = threads or min(n_head, ncpu)
-    if RefLib.available():
-        ref = RefLib()
-        t0 = time.perf_counter()
-        _, used = ref.attend_mt(q, kc, vc, L, scale, threads)
-        dt = time.perf_counter() - t0
-        kind = "reference"
-    else:
-        import ctypes
-        orc = Oracle()
-        out = np.empty_like(q)
-        f32p = ctypes.POINTER(ctypes.c_float)
-        fn = orc.L.oracle_attend_head
-        fn.argtypes = [f32p] * 4 + [ctypes.c_int] * 6 + [ctypes.c_float, f32p]
-        used = threads
+class CpuAttentionSample:
+    """Decode-attention calls of the workload's shape over the first CPU_SAMPLE_L KV rows on the host cores: the
+    reference's own CPU attention when it was compiled (kind "reference"), else the C restatement (kind "port").
+    The inputs are made once; run(calls) times `calls` back-to-back layer calls and returns the seconds."""
+
+    def __init__(self, w, threads=None):
+        from oracle.oracle import Oracle, RefLib
+        self.L = L = min(CPU_SAMPLE_L, w["L"])
+        self.n_head, self.n_kv, self.hd = n_head, n_kv, hd = w["n_head"], w["n_kv"], w["head_dim"]
+        rng = np.random.default_rng(7)
+        self.q = rng.standard_normal((n_head, hd), dtype=np.float32).astype(np.float16).astype(np.float32)
+        self.kc = rng.standard_normal((n_kv, L, hd), dtype=np.float32).astype(np.float16).astype(np.float32)
+        self.vc = rng.standard_normal((n_kv, L, hd), dtype=np.float32).astype(np.float16).astype(np.float32)
+        self.scale = np.float32(1.0 / np.sqrt(hd))
+        ncpu = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+        self.threads = threads or min(n_head, ncpu)
+        if RefLib.available():
+            self.ref = RefLib()
+            self.kind = "reference"
+        else:
+            import ctypes
+            self.ref = None
+            self.kind = "port"
+            self.out = np.empty_like(self.q)
+            self.f32p = ctypes.POINTER(ctypes.c_float)
+            self.fn = Oracle().L.oracle_attend_head
+            self.fn.argtypes = [self.f32p] * 4 + [ctypes.c_int] * 6 + [ctypes.c_float, self.f32p]
+        self.cores = self.threads
+
+    def _one_call(self):
+        L, n_head = self.L, self.n_head
+        if self.ref is not None:
+            _, used = self.ref.attend_mt(self.q, self.kc, self.vc, L, self.scale, self.threads)
+            self.cores = used
+            return
+        f32p, fn = self.f32p, self.fn
 
         def work(t):
             score = np.empty(L, np.float32)
-            for h in range(t, n_head, threads):
-                fn(q.ctypes.data_as(f32p), kc.ctypes.data_as(f32p), vc.ctypes.data_as(f32p), out.ctypes.data_as(f32p),
-                   h, n_head, n_kv, hd, L, L, scale, score.ctypes.data_as(f32p))
-        th = [threading.Thread(target=work, args=(t,)) for t in range(threads)]
-        t0 = time.perf_counter()
+            for h in range(t, n_head, self.threads):
+                fn(self.q.ctypes.data_as(f32p), self.kc.ctypes.data_as(f32p), self.vc.ctypes.data_as(f32p),
+                   self.out.ctypes.data_as(f32p), h, n_head, self.n_kv, self.hd, L, L, self.scale, score.ctypes.data_as(f32p))
+        th = [threading.Thread(target=work, args=(t,)) for t in range(self.threads)]
         for x in th:
             x.start()
         for x in th:
             x.join()
-        dt = time.perf_counter() - t0
-        kind = "port"
-    sample = "one layer call of the workload shape over the first %d KV rows (fp32 cache, %d host threads, one per query head)" % (L, used)
-    return dt, kind, used, sample, L
+
+    def run(self, calls):
+        t0 = time.perf_counter()
+        for _ in range(calls):
+            self._one_call()
+        return time.perf_counter() - t0
+
+    def describe(self, calls):
+        return ("%d layer calls of the workload shape, each over the first %d KV rows (fp32 cache, %d host threads, one per "
+                "query head)" % (calls, self.L, self.cores))
+
+
+REFERENCE_ARM_CALLS = 8     # layer calls per step of the reference arm (about two seconds of host work)
+CPU_BASELINE_CALLS = 48     # layer calls of the cpu_baseline leg (10 to 15 seconds of host work)
 
 
 def run_reference_arm(args, w):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    cpu = CpuAttentionSample(w)
     times = []
     for i in range(args.warmup + args.steps):
-        dt, kind, cores, sample, L = cpu_attention_sample(w)
+        dt = cpu.run(REFERENCE_ARM_CALLS)
         if i >= args.warmup:
             times.append(dt)
     ms = 1e3 * float(np.mean(times))
-    gbs = kv_bytes(w, L) / (ms * 1e-3) / 1e9
+    gbs = REFERENCE_ARM_CALLS * kv_bytes(w, cpu.L) / (ms * 1e-3) / 1e9
+    sample = cpu.describe(REFERENCE_ARM_CALLS)
     line = {
         "impl": "reference", "metric": "decode_attn_kv_gbs", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": args.workload, "sample": sample, **{k: w[k] for k in ("n_head", "n_kv", "head_dim")}},
-        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": kind, "sample": sample},
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cpu.cores, "kind": cpu.kind, "sample": sample},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line))
@@ -199,6 +219,13 @@ def run_b200(args, w):
     from orin_llm_b200.dist import PeerSplitKVDecoder, SplitKVDecoder, slice_bounds
     build.build()
     ops.init(local_rank)
+    # Launch ordering of the decode kernels (oattn_set_decode_overlap).  2: the split kernel may fetch its first K/V
+    # tiles while the previous call's merge drains.  Its precondition holds here as in the reference's decode graph:
+    # the position word is constant during a step and every layer call has its own cache.  It pays for short
+    # contexts on one GPU only, so that is where the default turns it on.
+    if args.overlap < 0:
+        args.overlap = 2 if (world == 1 and w["L"] <= 65536) else 0
+    ops.set_decode_overlap(args.overlap)
 
     n_head, n_kv, hd, layers, L = w["n_head"], w["n_kv"], w["head_dim"], w["layers"], w["L"]
     scale = 1.0 / float(np.sqrt(hd))
@@ -321,13 +348,16 @@ def run_b200(args, w):
 
     def e2e_body():
         d_in.copy_(h_in, non_blocking=True)                 # host -> device: this step's inputs
+        if world > 1 and owner:
+            # the rank that holds the newest row appends it for every layer first (the multi-GPU call has no fused
+            # append), so that no decode call directly follows a write to its own cache
+            for l in range(layers):
+                ops.kv_store_ind(Kc[l], Vc[l], dk[l], dv[l], n_kv, hd, n_loc, d_pos)
         for l in range(layers):
             if world == 1:
                 ops.attn_decode(dq[l], dk[l], dv[l], Kc[l], Vc[l], out[l], n_head, n_kv, hd, n_loc, d_pos, scale,
                                 ops.FUSE_KV_APPEND, None)
             else:
-                if owner:
-                    ops.kv_store_ind(Kc[l], Vc[l], dk[l], dv[l], n_kv, hd, n_loc, d_pos)
                 dec.decode(dq[l], Kc[l], Vc[l], n_loc, d_len, scale, out[l])
         hout.copy_(out, non_blocking=True)                  # device -> host: the step's result
 
@@ -395,9 +425,11 @@ def run_b200(args, w):
 
     cpu = None
     if not args.no_cpu_baseline:
-        dt, kind, cores, sample, Ls = cpu_attention_sample(w)
-        cpu = {"value": kv_bytes(w, Ls) / dt / 1e9, "unit": "GB/s", "cores": cores, "kind": kind, "sample": sample,
-               "seconds": dt}
+        smp = CpuAttentionSample(w)
+        smp.run(1)
+        dt = smp.run(CPU_BASELINE_CALLS)
+        cpu = {"value": CPU_BASELINE_CALLS * kv_bytes(w, smp.L) / dt / 1e9, "unit": "GB/s", "cores": smp.cores,
+               "kind": smp.kind, "sample": smp.describe(CPU_BASELINE_CALLS), "seconds": dt}
 
     line = {
         "metric": "decode_attn_kv_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
@@ -406,6 +438,8 @@ def run_b200(args, w):
         "config": {"workload": args.workload, "n_head": n_head, "n_kv": n_kv, "head_dim": hd, "layers_per_step": layers,
                    "kv_len": L, "kv_rows_per_gpu": n_loc, "parallelism": "kv-split x%d" % world,
                    "launch": "eager" if args.no_graph else "cuda graph replay of the step",
+                   "launch_order": {0: "ordinary launches", 1: "programmatic dependent launches",
+                                    2: "programmatic dependent launches, K/V prefetch ahead of the dependency wait"}[args.overlap],
                    "exchange": {"none": "single GPU", "peer": "merge kernel stores its record into every peer's buffer (NVLink peer stores), waits for the peers' flags and merges",
                                 "peer-split": "as peer, with the flag wait and final merge in a launch of their own",
                                 "nccl": "NCCL all-gather of the records"}[exchange],
@@ -501,6 +535,8 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="override the layer calls per step")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--exchange", default="peer", choices=["peer", "peer-split", "nccl"], help="multi-GPU record exchange")
+    ap.add_argument("--overlap", type=int, default=-1, choices=[-1, 0, 1, 2],
+                    help="decode launch ordering (oattn_set_decode_overlap); -1: 2 for contexts up to 65536 rows on one GPU, else 0")
     ap.add_argument("--no-graph", action="store_true", help="launch the step eagerly instead of replaying a CUDA graph")
     args = ap.parse_args()
     if args.workload in PREFILL_WORKLOADS:

@@ -197,6 +197,19 @@ int oattn_prefill_status(const void* workspace, int n_head, int head_dim, int ba
  * 1 = the warp-level mma.sync kernel kept as an in-library cross-check.  Process-wide. */
 int oattn_set_prefill_impl(int impl);
 
+/* How the decode launches are ordered against the preceding kernels of the stream (no counterpart in the reference).
+ *   0  (default) ordinary launches.
+ *   1  programmatic dependent launches: a decode kernel may be scheduled while the preceding kernel of the
+ *      stream drains, and waits for it to complete before it reads or writes anything.  Same results as 0.
+ *   2  as 1, and the split kernel reads *d_pos and starts fetching cache rows below the valid length BEFORE that wait.
+ *      The caller vouches that neither is written by the kernels launched on the stream since the previous
+ *      non-decode launch (true for the reference's decode graph, src/model_gpu.cu:295-344: the position is copied in
+ *      before the graph starts, every layer has its own cache, and other kernels run between two calls on one
+ *      cache).  Do not use for back-to-back calls that append to the same cache.  Measured on B200: about 13 % more
+ *      throughput for short contexts (1K to 4K rows) on one GPU, nothing for long ones, and a loss when the merge
+ *      kernel exchanges records with other GPUs, so leave it off there. */
+int oattn_set_decode_overlap(int mode);
+
 /* Lower bound on the 64-row tiles one decode split handles (default 2): short contexts then
  * use fewer, fuller splits.  Process-wide tuning knob; must not change between the capture and
  * the replays of a CUDA graph. */

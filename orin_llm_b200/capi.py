@@ -24,7 +24,7 @@ EXPORTS = [
     "oattn_decode_partial", "oattn_combine", "oattn_peer_buffer_bytes", "oattn_peer_state_bytes",
     "oattn_decode_partial_push", "oattn_peer_wait_combine", "oattn_decode_peer", "oattn_peer_status", "oattn_prefill_workspace_bytes", "oattn_prefill",
     "oattn_prefill_status",
-    "oattn_set_prefill_impl", "oattn_set_decode_min_tiles", "oattn_profile_enable", "oattn_profile_collect",
+    "oattn_set_prefill_impl", "oattn_set_decode_min_tiles", "oattn_set_decode_overlap", "oattn_profile_enable", "oattn_profile_collect",
     "oattn_launch_count",
 ]
 
@@ -86,6 +86,7 @@ def lib():
     L.oattn_prefill_status.argtypes = [vp, i, i, i, ctypes.POINTER(ctypes.c_int)]
     L.oattn_set_prefill_impl.argtypes = [i]
     L.oattn_set_decode_min_tiles.argtypes = [i]
+    L.oattn_set_decode_overlap.argtypes = [i]
     L.oattn_profile_enable.argtypes = [i]
     L.oattn_profile_collect.argtypes = [ctypes.POINTER(ctypes.c_float), i, ctypes.POINTER(ctypes.c_int)]
     L.oattn_launch_count.restype = ctypes.c_ulonglong

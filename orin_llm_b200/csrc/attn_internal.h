@@ -43,6 +43,7 @@ struct DecodeArgs {
     const unsigned long long* peer_bufs = nullptr;   // multi-GPU peer exchange: device array of `world` buffer pointers
     int* gen_push = nullptr;                          // [n_head] generation counters (private to this rank)
     int rank = 0, world = 1;
+    int overlap = 0;                                  // 0 plain launches, 1 dependent launches, 2 + K/V prefetch before the wait
     int fused_wait = 0;                               // the merge launch also waits for every rank's record and writes `out`
     int* peer_status = nullptr;                       // raised when that wait ran out
 };
@@ -63,7 +64,7 @@ cudaError_t launch_combine_records(const float* parts, int n_parts, float* out, 
                                    cudaStream_t stream, unsigned long long* launches);
 
 cudaError_t launch_peer_wait_combine(const void* my_buf, int world, float* out, int n_head, int head_dim, int* gen_wait,
-                                     int* status, cudaStream_t stream, unsigned long long* launches);
+                                     int* status, int overlap, cudaStream_t stream, unsigned long long* launches);
 
 struct PrefillArgs {
     const float* q;        // [batch][n_head][hd] fp32

@@ -18,6 +18,7 @@ DeviceState g_dev[kMaxDevices];
 int g_cur = -1;                       // device of the last oattn_init
 int g_prefill_impl = 0;               // 0 = tcgen05, 1 = mma.sync
 int g_decode_min_tiles = 2;
+int g_decode_overlap = 0;
 unsigned long long g_launches = 0;
 char g_cuda_err[256] = "";
 
@@ -173,7 +174,7 @@ static int decode_common(const float* q, const float* k_new, const float* v_new,
     a.ws_ml = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + w.o_bytes);
     a.d_pos = d_pos; a.pos_bias = pos_bias;
     a.n_head = n_head; a.n_kv = n_kv; a.head_dim = head_dim; a.n_ctx = n_ctx;
-    a.n_splits = w.n_splits; a.min_tiles = g_decode_min_tiles;
+    a.n_splits = w.n_splits; a.min_tiles = g_decode_min_tiles; a.overlap = g_decode_overlap;
     a.scale = scale; a.fuse = fuse; a.emit_partial = emit_partial;
     if (peer) { a.peer_bufs = peer->bufs; a.gen_push = peer->gen_push; a.rank = peer->rank; a.world = peer->world;
                 a.fused_wait = peer->fused_wait; a.peer_status = peer->status; }
@@ -265,7 +266,7 @@ int oattn_peer_wait_combine(const void* my_buf, int world, float* out, int n_hea
     if (head_dim != 64 && head_dim != 128) return OATTN_ERR_UNSUPPORTED;
     int* st = reinterpret_cast<int*>(state);
     cudaError_t e = launch_peer_wait_combine(my_buf, world, out, n_head, head_dim, st + n_head, st + 2 * n_head,
-                                             (cudaStream_t)stream, &g_launches);
+                                             g_decode_overlap, (cudaStream_t)stream, &g_launches);
     return e == cudaSuccess ? OATTN_OK : cuda_fail(e, "peer wait/combine launch");
 }
 
@@ -332,6 +333,12 @@ int oattn_prefill(const float* q, const float* k_new, const float* v_new, uint16
 int oattn_set_prefill_impl(int impl) {
     if (impl != 0 && impl != 1) return OATTN_ERR_ARG;
     g_prefill_impl = impl;
+    return OATTN_OK;
+}
+
+int oattn_set_decode_overlap(int mode) {
+    if (mode < 0 || mode > 2) return OATTN_ERR_ARG;
+    g_decode_overlap = mode;
     return OATTN_OK;
 }
 

@@ -87,6 +87,13 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+// ---- programmatic dependent launch -----------------------------------------------------------
+// A kernel launched with the programmatic-stream-serialization attribute may start while the preceding kernel of the
+// stream is still running.  pdl_wait() blocks until every preceding kernel has completed and its writes are
+// visible (a no-op for an ordinary launch); pdl_trigger() lets the next kernel of the stream begin launching.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+
 // Byte offset of (row, 16-byte chunk) inside a tile whose rows are ROW_BYTES wide, with the
 // chunk index XOR-ed by the row so that the 8 rows one ldmatrix phase touches fall in 8
 // different bank groups.

@@ -98,6 +98,12 @@ __global__ void __launch_bounds__(kThreads, 2) decode_split_kernel(const DecodeA
     const int r = lane >> 2, t = lane & 3;
     const int G = p.n_head / p.n_kv;
 
+    // The merge kernel of this call may start launching now; it waits for this grid to complete before it reads.
+    pdl_trigger();
+    // Unless the caller vouched for the position word and the cache rows below the valid length (overlap 2), nothing
+    // is read before every preceding kernel of the stream has completed.
+    if (p.overlap != 2) pdl_wait();
+
     const int npos = clamp_len(*p.d_pos + p.pos_bias, p.n_ctx);
     const SplitPlan plan = plan_splits(npos, p.n_splits, p.min_tiles);
     if (split >= plan.active) return;
@@ -137,6 +143,9 @@ __global__ void __launch_bounds__(kThreads, 2) decode_split_kernel(const DecodeA
         if (s < nt) load_tile(s, s);
         cp_async_commit();
     }
+
+    // the first tiles are in flight; q, the new K/V row and the scratch block belong to preceding kernels
+    if (p.overlap == 2) pdl_wait();
 
     // ---- prologue: RoPE table, Q -> fp16 fragments, new K/V row ------------------------------
     float* s_cos = reinterpret_cast<float*>(smem + L::CS_OFF);
@@ -424,6 +433,9 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(const CombineA
     const int h = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int hd = p.head_dim;
 
+    pdl_trigger();
+    pdl_wait();      // the split kernel's partials (or the gathered records) must be complete
+
     int n = p.n_parts;
     if (n < 0) {
         const int npos = clamp_len(*p.d_pos + p.pos_bias, p.n_ctx);
@@ -573,17 +585,34 @@ struct PeerWaitArgs {
 __global__ void __launch_bounds__(128) peer_wait_combine_kernel(const PeerWaitArgs p) {
     __shared__ float s_m[DECODE_MAX_RANKS], s_l[DECODE_MAX_RANKS];
     const int h = blockIdx.x;
+    pdl_trigger();
+    pdl_wait();
     const int g = p.gen_wait[h] + 1;
     peer_wait_merge(p.my_buf, g, h, p.world, p.n_head, p.head_dim, p.out, p.status, s_m, s_l);
     __syncthreads();
     if (threadIdx.x == 0) p.gen_wait[h] = g;
 }
 
+// Launch with (overlap != 0) or without the programmatic-stream-serialization attribute.
+template <typename Kernel, typename Args>
+cudaError_t launch_dependent(Kernel kernel, dim3 grid, int threads, size_t smem, cudaStream_t stream, int overlap, const Args& args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(threads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = overlap ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, args);
+}
+
 template <int HD, bool WIDE>
 cudaError_t launch_split(const DecodeArgs& a, cudaStream_t stream) {
-    dim3 grid(a.n_splits, a.n_kv);
-    decode_split_kernel<HD, WIDE><<<grid, kThreads, DecodeSmem<HD>::TOTAL, stream>>>(a);
-    return cudaGetLastError();
+    return launch_dependent(decode_split_kernel<HD, WIDE>, dim3(a.n_splits, a.n_kv), kThreads, DecodeSmem<HD>::TOTAL, stream,
+                            a.overlap, a);
 }
 
 } // namespace
@@ -669,9 +698,9 @@ cudaError_t launch_decode(const DecodeArgs& a, cudaStream_t stream, unsigned lon
     c.n_head = a.n_head;
     c.fused_wait = a.fused_wait;
     c.status = a.peer_status;
-    combine_kernel<<<a.n_head, kCombineThreads, 0, stream>>>(c);
+    e = launch_dependent(combine_kernel, dim3(a.n_head), kCombineThreads, 0, stream, a.overlap, c);
     if (launches) *launches += 2;
-    return cudaGetLastError();
+    return e;
 }
 
 cudaError_t launch_combine_records(const float* parts, int n_parts, float* out, int n_head, int head_dim,
@@ -706,7 +735,7 @@ cudaError_t launch_combine_records(const float* parts, int n_parts, float* out, 
 }
 
 cudaError_t launch_peer_wait_combine(const void* my_buf, int world, float* out, int n_head, int head_dim, int* gen_wait,
-                                     int* status, cudaStream_t stream, unsigned long long* launches) {
+                                     int* status, int overlap, cudaStream_t stream, unsigned long long* launches) {
     PeerWaitArgs w;
     w.my_buf = reinterpret_cast<const unsigned char*>(my_buf);
     w.out = out;
@@ -715,9 +744,9 @@ cudaError_t launch_peer_wait_combine(const void* my_buf, int world, float* out, 
     w.world = world;
     w.n_head = n_head;
     w.head_dim = head_dim;
-    peer_wait_combine_kernel<<<n_head, 128, 0, stream>>>(w);
+    cudaError_t e = launch_dependent(peer_wait_combine_kernel, dim3(n_head), 128, 0, stream, overlap, w);
     if (launches) *launches += 1;
-    return cudaGetLastError();
+    return e;
 }
 
 } // namespace oattn

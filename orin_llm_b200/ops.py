@@ -222,6 +222,12 @@ def set_prefill_impl(impl):
     capi.check(capi.lib().oattn_set_prefill_impl(impl))
 
 
+def set_decode_overlap(mode):
+    """0 ordinary launches (default), 1 dependent launches, 2 also prefetch K/V before waiting for the preceding kernel
+    (the caller vouches for the position word and the cache rows; see the C header)."""
+    capi.check(capi.lib().oattn_set_decode_overlap(mode))
+
+
 def set_decode_min_tiles(tiles):
     capi.check(capi.lib().oattn_set_decode_min_tiles(tiles))
 

@@ -257,3 +257,67 @@ def test_argument_errors(ops):
     assert L.oattn_decode(p, None, None, p, p, p, 28, 4, 128, 64, None, 0.1, 0, None, ws.data_ptr(), ws.numel(), None) == capi.ERR_ARG
     assert L.oattn_decode(p, None, None, p, p, p, 28, 4, 128, 64, p, 0.1, 7, None, ws.data_ptr(), ws.numel(), None) == capi.ERR_ARG
     assert L.oattn_prefill(p, None, None, p, p, p, 28, 4, 128, 64, 60, 8, 0.1, 0, None, ws.data_ptr(), ws.numel(), None) == capi.ERR_ARG
+
+
+@pytest.mark.parametrize("mode", [1, 2])
+def test_launch_overlap_modes_give_the_same_output(ops, oracle, mode):
+    """A chain of layer calls, each on its own cache (as a decode step runs them), captured in a CUDA graph under
+    launch-ordering modes 1 (dependent launches) and 2 (dependent launches with K/V prefetch before the wait): same
+    bits as the default mode 0, and equal to the oracle."""
+    n_head, n_kv, hd, n_ctx, layers = 16, 2, 128, 3000, 6
+    scale = np.float32(1.0 / np.sqrt(hd))
+    rope = (1, hd, 1e6, None)
+    pos = 2500
+    rng = np.random.default_rng(77)
+    caches, qs, ks, vs = [], [], [], []
+    for l in range(layers):
+        _, K, V = make_qkv(700 + l, n_head, n_kv, hd, pos, n_ctx)
+        caches.append((K, V))
+        qs.append(rng.standard_normal((n_head, hd)).astype(np.float32))
+        ks.append(rng.standard_normal((n_kv, hd)).astype(np.float32))
+        vs.append(f16_round(rng.standard_normal((n_kv, hd)).astype(np.float32)))
+    d_pos = torch.tensor([pos], dtype=torch.int32, device="cuda")
+    dq, dk, dv = dev(np.stack(qs)), dev(np.stack(ks)), dev(np.stack(vs))
+    ws = ops.decode_workspace(n_head, n_kv, hd)
+
+    def run(m):
+        ops.set_decode_overlap(m)
+        try:
+            dK = [dev(K) for K, _ in caches]
+            dV = [dev(V) for _, V in caches]
+            out = torch.zeros(layers, n_head, hd, device="cuda")
+            stream = torch.cuda.Stream()
+            stream.wait_stream(torch.cuda.current_stream())
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(stream):
+                ops.set_stream(stream)
+                try:
+                    graph.capture_begin()
+                    for l in range(layers):
+                        ops.attn_decode(dq[l], dk[l], dv[l], dK[l], dV[l], out[l], n_head, n_kv, hd, n_ctx, d_pos, float(scale),
+                                        ops.FUSE_ALL, rope, ws)
+                    graph.capture_end()
+                finally:
+                    ops.set_stream(None)
+            graph.replay()
+            torch.cuda.synchronize()
+            eager = torch.zeros_like(out)
+            dK2 = [dev(K) for K, _ in caches]
+            dV2 = [dev(V) for _, V in caches]
+            for l in range(layers):
+                ops.attn_decode(dq[l], dk[l], dv[l], dK2[l], dV2[l], eager[l], n_head, n_kv, hd, n_ctx, d_pos, float(scale),
+                                ops.FUSE_ALL, rope, ws)
+            torch.cuda.synchronize()
+            assert torch.equal(out, eager)
+            return out.cpu().numpy()
+        finally:
+            ops.set_decode_overlap(0)
+
+    base = run(0)
+    got = run(mode)
+    assert np.array_equal(got, base)
+    for l in (0, layers - 1):
+        K, V = caches[l]
+        want = oracle.attn_batch(qs[l][None].copy(), ks[l][None].copy(), vs[l][None].copy(), K.astype(np.float32),
+                                 V.astype(np.float32), pos, scale, True, 1, hd, 1e6, None)[0]
+        assert_close(got[l], want, "mode %d layer %d" % (mode, l))
