@@ -150,8 +150,9 @@ int oattn_combine(const float* parts, int n_parts, float* out, int n_head, int h
 /* ---- multi-GPU exchange without a collective call (no reference counterpart) ----------------------------------
  * The record exchange of split-KV decode is 8 KB per rank: latency-bound.  Instead of all-gather + combine, the
  * per-rank merge kernel stores its record straight into every rank's exchange buffer over NVLink (plain peer
- * stores) and raises a per-(source rank, head) generation flag; oattn_peer_wait_combine polls the flags of its
- * own buffer (bounded, ~2 s, then a status word is set) and merges the `world` records.
+ * stores).  Every fp32 value travels in one aligned 8-byte word together with the generation number of the call, so
+ * the receiver needs neither a fence nor a flag: oattn_peer_wait_combine polls the words of its own buffer until
+ * they carry the current generation (bounded, ~2 s, then a status word is set) and merges the `world` records.
  *   exchange buffer   oattn_peer_buffer_bytes(world, n_head, head_dim) bytes on every rank, peer-mapped (e.g. CUDA
  *                     VMM / torch symmetric memory), zero-filled before first use; `peer_bufs_dev` is a DEVICE array
  *                     of `world` pointers (entry r = rank r's buffer as seen from this GPU, own buffer included)

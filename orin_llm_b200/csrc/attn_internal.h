@@ -14,14 +14,12 @@ constexpr int DECODE_MAX_SPLITS = 512; // upper bound on KV splits per kv head (
 constexpr int PART_PAD = 4;            // floats after O in a partial record: m, l, 0, 0
 constexpr int DECODE_MAX_RANKS = 16;   // ranks of one peer exchange
 
-// Exchange buffer of one rank (the same layout on every rank): records float [2 slots][world][n_head][hd+PART_PAD],
-// then, 256-byte aligned, generation flags unsigned [world][n_head].
-__host__ __device__ inline size_t peer_flags_offset(int world, int n_head, int head_dim) {
-    const size_t rec = (size_t)2 * world * n_head * (head_dim + PART_PAD) * sizeof(float);
-    return (rec + 255) & ~(size_t)255;
-}
+// Exchange buffer of one rank (the same layout on every rank): 8-byte words [2 slots][world][n_head][hd+PART_PAD],
+// each word = {fp32 value, 32-bit generation tag}.  Value and tag travel in one aligned 8-byte store, so a reader
+// that sees the tag of the generation it waits for has the value too: no fence and no separate flag.
 __host__ __device__ inline size_t peer_buffer_bytes(int world, int n_head, int head_dim) {
-    return peer_flags_offset(world, n_head, head_dim) + (((size_t)world * n_head * sizeof(unsigned) + 255) & ~(size_t)255);
+    const size_t rec = (size_t)2 * world * n_head * (head_dim + PART_PAD) * sizeof(unsigned long long);
+    return (rec + 255) & ~(size_t)255;
 }
 
 struct DecodeArgs {

@@ -375,28 +375,65 @@ struct CombineArgs {
 };
 
 constexpr int kCombineThreads = 512;
+constexpr int kPeerWaitThreads = 128 + 32;   // head_dim (at most 128) value pollers + up to DECODE_MAX_RANKS (m, l) pollers
 constexpr int kCombineWarps = kCombineThreads / 32;
 
-// ---- wait for every rank's record of one generation and merge them ---------------------------------------------
-// Called by all threads of a CTA that owns head h.  Thread r polls the flag that rank r sets after its record for
-// this head has landed in this rank's exchange buffer; the poll is bounded (about two seconds), after which a status
-// word is raised and the output is left untouched.  s_a / s_b: two shared float arrays of >= DECODE_MAX_RANKS.
+// ---- record exchange between ranks: tagged 8-byte words ---------------------------------------------------------
+__device__ __forceinline__ void peer_store_word(unsigned long long* dst, float v, unsigned tag) {
+    const unsigned long long w = ((unsigned long long)tag << 32) | (unsigned long long)__float_as_uint(v);
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;\n" ::"l"(dst), "l"(w) : "memory");
+}
+__device__ __forceinline__ unsigned long long peer_load_word(const unsigned long long* src) {
+    unsigned long long w;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];\n" : "=l"(w) : "l"(src) : "memory");
+    return w;
+}
+
+// Wait for every rank's record of generation g for head h in this rank's exchange buffer and merge them.
+// Called by all threads of a CTA of at least head_dim + world threads.  Thread d < head_dim polls the words that carry
+// O[d] of every source rank (all polls of one round are independent loads); thread head_dim + r polls m and l of
+// rank r.  A word is taken once its tag equals g.  The wait is bounded (about two seconds), after which a status
+// word is raised and the output is left untouched.
 __device__ __forceinline__ void peer_wait_merge(const unsigned char* my_buf, int g, int h, int world, int n_head, int hd,
-                                                float* out, int* status, float* s_a, float* s_b) {
+                                                float* out, int* status) {
     __shared__ int s_fail;
-    __shared__ float s_wr[DECODE_MAX_RANKS];
+    __shared__ float s_m[DECODE_MAX_RANKS], s_l[DECODE_MAX_RANKS];
     const int tid = threadIdx.x;
     __syncthreads();
     if (tid == 0) s_fail = 0;
     __syncthreads();
-    if (tid < world) {
-        const unsigned* flag = reinterpret_cast<const unsigned*>(my_buf + peer_flags_offset(world, n_head, hd)) +
-                               (size_t)tid * n_head + h;
-        const long long t0 = clock64();
-        unsigned val;
+    const size_t rec_sz = hd + PART_PAD;
+    const unsigned long long* recs = reinterpret_cast<const unsigned long long*>(my_buf) +
+                                     ((size_t)(g & 1) * world * n_head + h) * rec_sz;
+    const size_t rank_stride = (size_t)n_head * rec_sz;
+    float o[DECODE_MAX_RANKS];
+    const long long t0 = clock64();
+    if (tid < hd) {
+        unsigned pending = (1u << world) - 1u;      // world <= DECODE_MAX_RANKS = 16
+        while (pending) {
+            unsigned long long w[DECODE_MAX_RANKS];
+#pragma unroll
+            for (int r = 0; r < DECODE_MAX_RANKS; ++r)
+                if (pending >> r & 1u) w[r] = peer_load_word(recs + r * rank_stride + tid);
+#pragma unroll
+            for (int r = 0; r < DECODE_MAX_RANKS; ++r) {
+                if ((pending >> r & 1u) && (unsigned)(w[r] >> 32) == (unsigned)g) {
+                    o[r] = __uint_as_float((unsigned)w[r]);
+                    pending &= ~(1u << r);
+                }
+            }
+            if (pending && clock64() - t0 > 4000000000LL) { s_fail = 1; break; }
+        }
+    } else if (tid < hd + world) {
+        const int r = tid - hd;
+        const unsigned long long* rec = recs + r * rank_stride + hd;
         for (;;) {
-            asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(val) : "l"(flag) : "memory");
-            if ((int)(val - (unsigned)g) >= 0) break;
+            const unsigned long long wm = peer_load_word(rec), wl = peer_load_word(rec + 1);
+            if ((unsigned)(wm >> 32) == (unsigned)g && (unsigned)(wl >> 32) == (unsigned)g) {
+                s_m[r] = __uint_as_float((unsigned)wm);
+                s_l[r] = __uint_as_float((unsigned)wl);
+                break;
+            }
             if (clock64() - t0 > 4000000000LL) { s_fail = 1; break; }
         }
     }
@@ -405,23 +442,18 @@ __device__ __forceinline__ void peer_wait_merge(const unsigned char* my_buf, int
         if (tid == 0 && status) atomicExch(status, 1);
         return;
     }
-    const size_t rec_sz = hd + PART_PAD;
-    const float* recs = reinterpret_cast<const float*>(my_buf) + ((size_t)(g & 1) * world * n_head + h) * rec_sz;
-    const size_t rank_stride = (size_t)n_head * rec_sz;
-    if (tid < world) {
-        s_a[tid] = __ldcg(recs + tid * rank_stride + hd);
-        s_b[tid] = __ldcg(recs + tid * rank_stride + hd + 1);
-    }
-    __syncthreads();
-    float M = -CUDART_INF_F;
-    for (int r = 0; r < world; ++r) M = fmaxf(M, s_a[r]);
-    if (tid < world) s_wr[tid] = (s_a[tid] == -CUDART_INF_F) ? 0.f : __expf(s_a[tid] - M);
-    __syncthreads();
-    float L = 0.f;
-    for (int r = 0; r < world; ++r) L += s_wr[r] * s_b[r];
     if (tid < hd) {
-        float acc = 0.f;
-        for (int r = 0; r < world; ++r) acc = fmaf(s_wr[r], __ldcg(recs + r * rank_stride + tid), acc);
+        float M = -CUDART_INF_F;
+        for (int r = 0; r < world; ++r) M = fmaxf(M, s_m[r]);
+        float L = 0.f, acc = 0.f;
+#pragma unroll
+        for (int r = 0; r < DECODE_MAX_RANKS; ++r) {
+            if (r < world) {
+                const float w = (s_m[r] == -CUDART_INF_F) ? 0.f : __expf(s_m[r] - M);
+                L = fmaf(w, s_l[r], L);
+                acc = fmaf(w, o[r], acc);
+            }
+        }
         out[(size_t)h * hd + tid] = L > 0.f ? acc / L : 0.f;
     }
 }
@@ -523,17 +555,15 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(const CombineA
             v += (e == 0) ? a.x : (e == 1) ? a.y : (e == 2) ? a.z : a.w;
         }
         if (p.emit_partial && p.peer_bufs) {
-            const int g = p.gen_push[h] + 1;          // generation of this call; only this CTA touches gen_push[h]
+            const unsigned g = (unsigned)(p.gen_push[h] + 1);   // generation of this call; only this CTA touches gen_push[h]
             const size_t rec_sz = hd + PART_PAD;
             for (int r = 0; r < p.world; ++r) {
-                float* rec = reinterpret_cast<float*>(p.peer_bufs[r]) +
-                             ((size_t)((g & 1) * p.world + p.rank) * p.n_head + h) * rec_sz;
-                rec[tid] = v;
+                unsigned long long* rec = reinterpret_cast<unsigned long long*>(p.peer_bufs[r]) +
+                                          ((size_t)((g & 1) * p.world + p.rank) * p.n_head + h) * rec_sz;
+                peer_store_word(rec + tid, v, g);
                 if (tid == 0) {
-                    rec[hd + 0] = M;
-                    rec[hd + 1] = Lsum;
-                    rec[hd + 2] = 0.f;
-                    rec[hd + 3] = 0.f;
+                    peer_store_word(rec + hd + 0, M, g);
+                    peer_store_word(rec + hd + 1, Lsum, g);
                 }
             }
         } else if (p.emit_partial) {
@@ -550,20 +580,11 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(const CombineA
         }
     }
     if (p.emit_partial && p.peer_bufs) {
-        // the barrier orders every thread's record stores before the flag stores below; one thread per destination
-        // rank then publishes the generation with a system-scope release (cumulative over the stores the barrier
-        // made visible to it), which the destination polls with an acquire
-        __syncthreads();
         const int g = p.gen_push[h] + 1;
-        if (tid < p.world) {
-            unsigned* flags = reinterpret_cast<unsigned*>(reinterpret_cast<unsigned char*>(p.peer_bufs[tid]) +
-                                                          peer_flags_offset(p.world, p.n_head, hd));
-            asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(flags + (size_t)p.rank * p.n_head + h), "r"((unsigned)g) : "memory");
-        }
         if (p.fused_wait) {
             // same launch also waits for the other ranks' records of this generation and writes the final output
             peer_wait_merge(reinterpret_cast<const unsigned char*>(p.peer_bufs[p.rank]), g, h, p.world, p.n_head, hd,
-                            p.out, p.status, s_w, s_red);
+                            p.out, p.status);
         }
         __syncthreads();
         if (tid == 0) p.gen_push[h] = g;
@@ -582,13 +603,12 @@ struct PeerWaitArgs {
     int world, n_head, head_dim;
 };
 
-__global__ void __launch_bounds__(128) peer_wait_combine_kernel(const PeerWaitArgs p) {
-    __shared__ float s_m[DECODE_MAX_RANKS], s_l[DECODE_MAX_RANKS];
+__global__ void __launch_bounds__(kPeerWaitThreads) peer_wait_combine_kernel(const PeerWaitArgs p) {
     const int h = blockIdx.x;
     pdl_trigger();
     pdl_wait();
     const int g = p.gen_wait[h] + 1;
-    peer_wait_merge(p.my_buf, g, h, p.world, p.n_head, p.head_dim, p.out, p.status, s_m, s_l);
+    peer_wait_merge(p.my_buf, g, h, p.world, p.n_head, p.head_dim, p.out, p.status);
     __syncthreads();
     if (threadIdx.x == 0) p.gen_wait[h] = g;
 }
@@ -744,7 +764,7 @@ cudaError_t launch_peer_wait_combine(const void* my_buf, int world, float* out, 
     w.world = world;
     w.n_head = n_head;
     w.head_dim = head_dim;
-    cudaError_t e = launch_dependent(peer_wait_combine_kernel, dim3(n_head), 128, 0, stream, overlap, w);
+    cudaError_t e = launch_dependent(peer_wait_combine_kernel, dim3(n_head), kPeerWaitThreads, 0, stream, overlap, w);
     if (launches) *launches += 1;
     return e;
 }
