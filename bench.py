@@ -431,6 +431,33 @@ def run_b200(args, w):
         cpu = {"value": CPU_BASELINE_CALLS * kv_bytes(w, smp.L) / dt / 1e9, "unit": "GB/s", "cores": smp.cores,
                "kind": smp.kind, "sample": smp.describe(CPU_BASELINE_CALLS), "seconds": dt}
 
+    # ---- comparison leg: the reference's own decode kernel (src/kernels.cu, recompiled unmodified for sm_100a) on
+    # one layer call of this workload, same buffers; single GPU, device 0 only, group <= 8 (its limits)
+    ref_cuda = None
+    if world == 1 and local_rank == 0 and not args.no_ref_cuda and n_head // n_kv <= 8 and n_loc % 128 == 0:
+        from oracle.oracle import RefCuda
+        if RefCuda.available():
+            rc = RefCuda()
+            r_out = torch.empty(n_head, hd, device="cuda")
+            rc.flash_attention_decode_ind(q[0], Kc[0], Vc[0], r_out, n_head, n_kv, hd, n_loc, d_pos, scale)
+            torch.cuda.synchronize()
+            reps = 3
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for i in range(reps):
+                rc.flash_attention_decode_ind(q[i % layers], Kc[i % layers], Vc[i % layers], r_out, n_head, n_kv, hd, n_loc,
+                                              d_pos, scale)
+            e1.record()
+            torch.cuda.synchronize()
+            r_ms = e0.elapsed_time(e1) / reps
+            rc.flash_attention_decode_ind(q[0], Kc[0], Vc[0], r_out, n_head, n_kv, hd, n_loc, d_pos, scale)
+            m_out = torch.empty(n_head, hd, device="cuda")
+            ops.flash_attention_decode_ind(q[0], Kc[0], Vc[0], m_out, n_head, n_kv, hd, n_loc, d_pos, scale)
+            torch.cuda.synchronize()
+            ref_cuda = {"value": per_launch_bytes / (r_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_call": r_ms,
+                        "kernel": "flash_attention_decode_ind of the reference (src/kernels.cu:1993-2000), compiled for sm_100a",
+                        "max_abs_diff_to_this_repo": float((r_out - m_out).abs().max().item())}
+
     line = {
         "metric": "decode_attn_kv_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
@@ -446,7 +473,7 @@ def run_b200(args, w):
                    "l2": "inputs larger than L2: each of the %d layer calls of a step reads its own %.0f MiB of KV" % (
                        layers, per_launch_bytes / 2**20)},
         "pct_of_8tbs": 100.0 * value / (8000.0 * world),
-        "roofline": roofline, "cpu_baseline": cpu,
+        "roofline": roofline, "cpu_baseline": cpu, "reference_cuda_kernel": ref_cuda,
         "e2e": {"value": e2e_value, "unit": "GB/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h},
         "gpu_launches": int(launches), "clocks": clocks,
@@ -507,6 +534,36 @@ def run_b200_prefill(args, w):
     tflops = flops / (ms * 1e-3) / 1e12
     peaks, peak_kind = measured_peaks()
     assert ops.prefill_status(n_head, n_kv, hd, batch) == 0
+
+    # ---- comparison leg: the reference's own prefill sequence (rope q, rope k, kv_store_batch, flash_attention;
+    # src/model_gpu.cu:379-384) with its kernels recompiled unmodified for sm_100a, on one layer's buffers
+    ref_cuda = None
+    if not args.no_ref_cuda and n_head // n_kv <= 8 and n_ctx % 128 == 0:
+        from oracle.oracle import RefCuda
+        if RefCuda.available():
+            rc = RefCuda()
+            r_out = torch.empty(batch, n_head, hd, device="cuda")
+            rK, rV = Kc[0].clone(), Vc[0].clone()
+
+            def ref_call():
+                rq, rk = q[0].clone(), k[0].clone()
+                rc.rope_batch(rq, ops.ROPE_NORMAL, batch * n_head, hd, hd, w["theta"], n_past, n_head)
+                rc.rope_batch(rk, ops.ROPE_NORMAL, batch * n_kv, hd, hd, w["theta"], n_past, n_kv)
+                rc.kv_store_batch(rK, rV, rk, v[0], n_kv, hd, n_ctx, n_past, batch)
+                rc.flash_attention(rq, rK, rV, r_out, n_head, n_kv, hd, n_ctx, n_past, batch, scale)
+            ref_call()
+            torch.cuda.synchronize()
+            reps = 5
+            e0.record()
+            for _ in range(reps):
+                ref_call()
+            e1.record()
+            torch.cuda.synchronize()
+            r_ms = e0.elapsed_time(e1) / reps
+            ref_cuda = {"value": prefill_flops(w) / (r_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_call": r_ms,
+                        "kernel": "rope_normal_batch x2 + kv_store_batch + flash_attention of the reference "
+                                  "(src/kernels.cu), compiled for sm_100a; includes two small device copies of q and k",
+                        "max_abs_diff_to_this_repo": float((r_out - out[0]).abs().max().item())}
     line = {
         "metric": "prefill_attn_tflops", "value": tflops, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
@@ -520,6 +577,7 @@ def run_b200_prefill(args, w):
                      "peak_source": peak_kind + " (MEASURED_PEAKS.json bf16_tflops, burst)",
                      "frac_of_nominal_2250": tflops / 2250.0,
                      "note": "achieved = causal algorithmic FLOPs / step time, prologue kernel included"},
+        "reference_cuda_kernel": ref_cuda,
         "gpu_launches": int(launches), "clocks": clocks,
     }
     print(json.dumps(line))
@@ -534,6 +592,7 @@ def main():
     ap.add_argument("--workload", default="decode_3b_L1048576", choices=sorted(WORKLOADS) + sorted(PREFILL_WORKLOADS))
     ap.add_argument("--layers", type=int, default=None, help="override the layer calls per step")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-ref-cuda", action="store_true", help="skip the reference-CUDA-kernel comparison leg")
     ap.add_argument("--exchange", default="peer", choices=["peer", "peer-split", "nccl"], help="multi-GPU record exchange")
     ap.add_argument("--overlap", type=int, default=-1, choices=[-1, 0, 1, 2],
                     help="decode launch ordering (oattn_set_decode_overlap); -1: 2")

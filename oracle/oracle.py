@@ -17,6 +17,7 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 ORACLE_SO = os.path.join(HERE, "liboracle_attn.so")
 REF_SO = os.path.join(HERE, "_ref", "libref_attn.so")
+REF_CUDA_SO = os.path.join(HERE, "_ref", "libref_cuda.so")
 
 _f32p = ctypes.POINTER(ctypes.c_float)
 _i = ctypes.c_int
@@ -35,6 +36,10 @@ def build(ref_root="/root/reference"):
     subprocess.check_call(["make", "-s", "-C", HERE, "all"])
     if os.path.isdir(os.path.join(ref_root, "src")):
         subprocess.check_call(["make", "-s", "-C", HERE, "ref", "REF=" + ref_root])
+        try:     # optional: the GPU-side cross-check needs nvcc and a minute of compile time
+            subprocess.check_call(["make", "-s", "-C", HERE, "refcuda", "REF=" + ref_root])
+        except (subprocess.CalledProcessError, OSError) as e:
+            print("oracle: reference CUDA kernels not built (%s)" % e)
 
 
 class Oracle:
@@ -167,3 +172,106 @@ class RefLib:
 
     def kv_shift(self, kcache, vcache, n_layer, n_kv, d, n_ctx, n_keep, shift):
         self.L.ref_kv_shift(_fp(kcache), _fp(vcache), n_layer, n_kv, d, n_ctx, n_keep, shift)
+
+
+class RefCuda:
+    """The reference's own CUDA wrappers (src/kernels.h), recompiled for sm_100a into oracle/_ref/libref_cuda.so.
+    Arguments are torch CUDA tensors on device 0 (the reference is device-0 only); calls run on torch's current
+    stream.  Test infrastructure: a second parity check and the comparison leg of the benchmark.
+
+    Limits of the reference kernels (src/kernels.cu:1117,1183-1196,1361,1430-1445): n_head / n_kv <= 8; n_ctx a
+    multiple of 128 with the cache initialised up to the next multiple of 128 past the last position."""
+
+    @staticmethod
+    def available():
+        return os.path.exists(REF_CUDA_SO)
+
+    def __init__(self):
+        import torch
+        self.torch = torch
+        L = ctypes.CDLL(REF_CUDA_SO)
+        vp, sz = ctypes.c_void_p, ctypes.c_size_t
+        L.refcuda_init.restype = _i
+        L.refcuda_set_stream.argtypes = [vp]
+        L.refcuda_scratch_size.restype = sz
+        L.refcuda_scratch_size.argtypes = [_i, _i]
+        L.refcuda_scratch_assign.argtypes = [vp, _i, _i]
+        L.refcuda_quantize_activation.argtypes = [vp, _i]
+        L.refcuda_rms_norm_rows.argtypes = [vp, vp, _i, _i, _f, vp]
+        L.refcuda_add_inplace_broadcast.argtypes = [vp, vp, _i, _i]
+        L.refcuda_rope_batch.argtypes = [vp, _i, _i, _i, _i, _f, _i, _i, vp]
+        L.refcuda_rope_ind.argtypes = [vp, _i, _i, _i, _i, _f, vp, vp]
+        L.refcuda_kv_store_batch.argtypes = [vp, vp, vp, vp, _i, _i, _i, _i, _i]
+        L.refcuda_kv_store_ind.argtypes = [vp, vp, vp, vp, _i, _i, _i, vp]
+        L.refcuda_kv_shift.argtypes = [vp, vp, _i, _i, _i, _i, _i, _i]
+        L.refcuda_flash_attention.argtypes = [vp, vp, vp, vp, _i, _i, _i, _i, _i, _i, _f]
+        L.refcuda_flash_attention_decode_ind.argtypes = [vp, vp, vp, vp, _i, _i, _i, _i, vp, _f]
+        self.L = L
+        if L.refcuda_init() != 0:
+            raise RuntimeError("reference cuda::init failed")
+
+    def _sync_stream(self):
+        self.L.refcuda_set_stream(ctypes.c_void_p(self.torch.cuda.current_stream().cuda_stream))
+
+    @staticmethod
+    def _p(t):
+        return ctypes.c_void_p(t.data_ptr()) if t is not None else None
+
+    @staticmethod
+    def check_shape(n_head, n_kv, n_ctx):
+        if n_head // n_kv > 8 or n_ctx % 128:
+            raise ValueError("outside the reference kernels' limits (group <= 8, n_ctx % 128 == 0)")
+
+    def flash_attention_decode_ind(self, q, kc, vc, out, n_head, n_kv, head_dim, n_ctx, d_pos, scale):
+        self.check_shape(n_head, n_kv, n_ctx)
+        self._sync_stream()
+        self.L.refcuda_flash_attention_decode_ind(self._p(q), self._p(kc), self._p(vc), self._p(out), n_head, n_kv, head_dim,
+                                                  n_ctx, self._p(d_pos), scale)
+
+    def flash_attention(self, q, kc, vc, out, n_head, n_kv, head_dim, n_ctx, n_past, batch, scale):
+        self.check_shape(n_head, n_kv, n_ctx)
+        self._sync_stream()
+        self.L.refcuda_flash_attention(self._p(q), self._p(kc), self._p(vc), self._p(out), n_head, n_kv, head_dim, n_ctx,
+                                       n_past, batch, scale)
+
+    def rope_batch(self, x, rope_type, rows, head_dim, n_rot, theta, n_past, heads, freq_factors=None):
+        self._sync_stream()
+        self.L.refcuda_rope_batch(self._p(x), rope_type, rows, head_dim, n_rot, theta, n_past, heads, self._p(freq_factors))
+
+    def rope_ind(self, x, rope_type, rows, head_dim, n_rot, theta, d_pos, freq_factors=None):
+        self._sync_stream()
+        self.L.refcuda_rope_ind(self._p(x), rope_type, rows, head_dim, n_rot, theta, self._p(d_pos), self._p(freq_factors))
+
+    def kv_store_batch(self, kc, vc, k, v, heads, head_dim, n_ctx, pos_base, batch):
+        self._sync_stream()
+        self.L.refcuda_kv_store_batch(self._p(kc), self._p(vc), self._p(k), self._p(v), heads, head_dim, n_ctx, pos_base, batch)
+
+    def kv_store_ind(self, kc, vc, k, v, heads, head_dim, n_ctx, d_pos):
+        self._sync_stream()
+        self.L.refcuda_kv_store_ind(self._p(kc), self._p(vc), self._p(k), self._p(v), heads, head_dim, n_ctx, self._p(d_pos))
+
+    def kv_shift(self, kc, vc, n_layer, n_kv, head_dim, n_ctx, n_keep, shift):
+        self._sync_stream()
+        self.L.refcuda_kv_shift(self._p(kc), self._p(vc), n_layer, n_kv, head_dim, n_ctx, n_keep, shift)
+
+    def rms_norm_rows(self, x, w, rows, cols, eps, y):
+        self._sync_stream()
+        self.L.refcuda_rms_norm_rows(self._p(x), self._p(w), rows, cols, eps, self._p(y))
+
+    def add_inplace_broadcast(self, a, b, stride, batch):
+        self._sync_stream()
+        self.L.refcuda_add_inplace_broadcast(self._p(a), self._p(b), stride, batch)
+
+    def quantize_activation(self, x, n_in):
+        """Returns (int8 values [n_in], fp32 scales [ceil(n_in/32)]) as the reference's GEMV kernels read them."""
+        torch = self.torch
+        self._sync_stream()
+        nbytes = int(self.L.refcuda_scratch_size(n_in, 1))
+        arena = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+        self.L.refcuda_scratch_assign(self._p(arena), n_in, 1)
+        self.L.refcuda_quantize_activation(self._p(x), n_in)
+        torch.cuda.current_stream().synchronize()
+        n_al = (n_in + 255) // 256 * 256
+        qs = arena[:n_in].view(torch.int8).clone()
+        scales = arena[n_al:n_al + 4 * ((n_in + 31) // 32)].view(torch.float32).clone()
+        return qs, scales

@@ -25,3 +25,12 @@ def ops():
     build.build()
     _ops.init(0)
     return _ops
+
+
+@pytest.fixture(scope="session")
+def refcuda(ops):
+    """The reference's own CUDA kernels recompiled for sm_100a (oracle/_ref/libref_cuda.so), when they were built."""
+    from oracle.oracle import RefCuda
+    if not RefCuda.available():
+        pytest.skip("oracle/_ref/libref_cuda.so is not built (needs the reference tree and nvcc at build time)")
+    return RefCuda()
