@@ -175,6 +175,42 @@ int oattn_decode_peer(const float* q, const uint16_t* kc, const uint16_t* vc, fl
 /* Blocking read of the status word (0 = every wait so far was satisfied). */
 int oattn_peer_status(const void* state, int n_head, int* status);
 
+/* ---- the steps on either side of attention, folded into the same launches -------------------- */
+
+/* Optional extras of oattn_decode_ex / oattn_prefill_ex.  Every pointer is a device pointer and may be NULL.
+ *   bias_q/k/v   replace add_inplace_broadcast on q, k, v (src/model_gpu.cu:372-374; src/model_cpu.cpp:258-260):
+ *                [n_head*head_dim], [n_kv*head_dim], [n_kv*head_dim], added before everything else.
+ *   norm_q/k     replace rms_norm_rows over the head rows of q and k (src/model_gpu.cu:274-275, 376-377;
+ *                src/model_cpu.cpp:266, 271): y = x / sqrt(mean(x^2) + norm_eps) * w, w of [head_dim], after the bias
+ *                and before RoPE.
+ *   out_qs, out_scales   (decode only) the output in the form the next GEMV reads, replacing
+ *                quantize_activation(d_attn_) (src/model_gpu.cu:284; quantize_q8_1_k, src/kernels.cu:136-145): per
+ *                32 consecutive values d = max|x| / 127, q = round-half-away(x / d) (0 for an all-zero group); int8
+ *                [n_head*head_dim] and fp32 [n_head*head_dim/32], laid out as scratch_assign does
+ *                (src/kernels.cu:1763-1776).  With these set, `out` may be NULL.
+ * bias_k, bias_v and norm_k act on the appended row and need OATTN_FUSE_KV_APPEND. */
+typedef struct oattn_ext {
+    const float* bias_q;
+    const float* bias_k;
+    const float* bias_v;
+    const float* norm_q;
+    const float* norm_k;
+    float norm_eps;
+    int8_t* out_qs;
+    float* out_scales;
+} oattn_ext;
+
+/* oattn_decode with the extras above (ext == NULL: identical to oattn_decode). */
+int oattn_decode_ex(const float* q, const float* k_new, const float* v_new, uint16_t* kc, uint16_t* vc, float* out,
+                    int n_head, int n_kv, int head_dim, int n_ctx, const int* d_pos, float scale, int fuse,
+                    const oattn_rope_params* rope, const oattn_ext* ext, void* workspace, size_t workspace_bytes, void* stream);
+/* oattn_prefill with bias / norm (out_qs is refused: the reference's prefill feeds a different, 128-value block
+ * format to its batched GEMM, src/kernels.cu:147-155, which is not produced here). */
+int oattn_prefill_ex(const float* q, const float* k_new, const float* v_new, uint16_t* kc, uint16_t* vc, float* out,
+                     int n_head, int n_kv, int head_dim, int n_ctx, int n_past, int batch, float scale, int fuse,
+                     const oattn_rope_params* rope, const oattn_ext* ext, void* workspace, size_t workspace_bytes,
+                     void* stream);
+
 /* ---- prefill: a chunk of `batch` query tokens, causal ------------------------------------ */
 
 /* Scratch for the prefill call (fp16 staging of the rotated, scaled queries). 256-byte aligned. */

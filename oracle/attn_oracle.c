@@ -181,3 +181,44 @@ void oracle_kv_shift(void *kcache, void *vcache, int n_layer, int n_kv, int d, i
         }
     }
 }
+
+/* src/model_cpu.cpp:13-18  rms_norm(): sum of squares in double, r = 1/sqrt(ss/n + eps) in double,
+ * y[i] = (float)(x[i] * r * w[i]) with the product formed in double, left to right.  y may alias x. */
+void oracle_rms_norm(const float *x, const float *w, int n, float eps, float *y) {
+    double ss = 0.0;
+    for (int i = 0; i < n; ++i) ss += (double)x[i] * x[i];
+    double r = 1.0 / sqrt(ss / n + eps);
+    for (int i = 0; i < n; ++i) y[i] = (float)(x[i] * r * w[i]);
+}
+
+/* src/model_cpu.cpp:258-274  what one token's q, k, v go through between the projections and RoPE:
+ * bias add on all of q, k, v (:258-260), then the per-head RMSNorm of every q head (:266) and every k head
+ * (:271) with a [d] weight.  In place; any pointer of the last five may be NULL (step absent). */
+void oracle_pre_attention(float *q, float *k, float *v, int n_head, int n_kv, int d,
+                          const float *bias_q, const float *bias_k, const float *bias_v,
+                          const float *norm_q, const float *norm_k, float eps) {
+    if (bias_q) for (int i = 0; i < n_head * d; ++i) q[i] += bias_q[i];
+    if (bias_k) for (int i = 0; i < n_kv * d; ++i) k[i] += bias_k[i];
+    if (bias_v) for (int i = 0; i < n_kv * d; ++i) v[i] += bias_v[i];
+    if (norm_q) for (int h = 0; h < n_head; ++h) oracle_rms_norm(q + h * d, norm_q, d, eps, q + h * d);
+    if (norm_k) for (int h = 0; h < n_kv; ++h) oracle_rms_norm(k + h * d, norm_k, d, eps, k + h * d);
+}
+
+/* src/kernels.cu:136-145  quantize_q8_1_k, the form in which the reference's GPU decode path hands the attention
+ * output to the next GEMV (src/model_gpu.cu:284): per group of 32 consecutive values d = max|x| / 127 and
+ * q = roundf(x / d), q = 0 when the group is all zero; a ragged last group is padded with zeros.  The reference
+ * builds this kernel with fast-math division; this restatement uses IEEE fp32 division (what the replacement
+ * kernel uses), so against the reference kernel itself a value on a rounding boundary may differ by one. */
+void oracle_quantize_q8_1(const float *x, int n, signed char *qs, float *scales) {
+    for (int g = 0; g * 32 < n; ++g) {
+        float amax = 0.0f;
+        for (int i = g * 32; i < g * 32 + 32 && i < n; ++i) {
+            float a = fabsf(x[i]);
+            if (a > amax) amax = a;
+        }
+        const float d = amax / 127.0f;
+        for (int i = g * 32; i < g * 32 + 32 && i < n; ++i)
+            qs[i] = amax == 0.0f ? 0 : (signed char)roundf(x[i] / d);
+        scales[g] = d;
+    }
+}

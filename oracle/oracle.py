@@ -56,6 +56,9 @@ class Oracle:
         L.oracle_attn_batch.argtypes = [_f32p] * 6 + [_i] * 6 + [_f, _i, _i, _i, _f, _f32p, _f32p]
         L.oracle_kv_shift.argtypes = [ctypes.c_void_p, ctypes.c_void_p] + [_i] * 7
         L.oracle_softmax.argtypes = [_f32p, _i]
+        L.oracle_rms_norm.argtypes = [_f32p, _f32p, _i, _f, _f32p]
+        L.oracle_pre_attention.argtypes = [_f32p, _f32p, _f32p, _i, _i, _i] + [_f32p] * 5 + [_f]
+        L.oracle_quantize_q8_1.argtypes = [_f32p, _i, ctypes.c_void_p, _f32p]
         self.L = L
 
     def rope(self, x, rope_type, n_rot, theta, pos, freq_factors=None):
@@ -96,6 +99,26 @@ class Oracle:
                                  _fp(freq_factors), _fp(score))
         return out
 
+    def pre_attention(self, q, k, v, bias_q=None, bias_k=None, bias_v=None, norm_q=None, norm_k=None, eps=1e-6):
+        """Bias add and per-head RMSNorm of one token's (or a batch of tokens') q, k, v, in place
+        (model_cpu.cpp:258-274).  q [..., n_head, d], k and v [..., n_kv, d]."""
+        d = q.shape[-1]
+        n_head, n_kv = q.shape[-2], k.shape[-2]
+        q2, k2, v2 = q.reshape(-1, n_head, d), k.reshape(-1, n_kv, d), v.reshape(-1, n_kv, d)
+        for t in range(q2.shape[0]):
+            self.L.oracle_pre_attention(_fp(q2[t]), _fp(k2[t]), _fp(v2[t]), n_head, n_kv, d, _fp(bias_q), _fp(bias_k),
+                                        _fp(bias_v), _fp(norm_q), _fp(norm_k), eps)
+        return q, k, v
+
+    def quantize_q8_1(self, x):
+        """(int8 values, fp32 scales) of a flat fp32 vector in the reference's q8_1 activation form
+        (kernels.cu:136-145)."""
+        x = np.ascontiguousarray(x, np.float32).reshape(-1)
+        qs = np.empty(x.size, np.int8)
+        scales = np.empty((x.size + 31) // 32, np.float32)
+        self.L.oracle_quantize_q8_1(_fp(x), x.size, qs.ctypes.data, _fp(scales))
+        return qs, scales
+
     def kv_shift(self, kcache, vcache, n_layer, n_kv, d, n_ctx, n_keep, shift):
         """In place on arrays of any element width (fp32 oracle cache or the uint16 device image)."""
         assert kcache.flags["C_CONTIGUOUS"] and vcache.flags["C_CONTIGUOUS"]
@@ -121,6 +144,8 @@ class RefLib:
         L.ref_forward_probe.argtypes = [_f32p, _i, _i, _i, _i, _i, _i, _i, _f, _f32p] + [_f32p] * 6
         L.ref_forward_probe.restype = _i
         L.ref_kv_shift.argtypes = [_f32p, _f32p] + [_i] * 6
+        L.ref_forward_probe_pre.argtypes = [_f32p, _i, _i, _i, _i, _i, _i, _i, _f, _f32p] + [_f32p] * 5 + [_f] + [_f32p] * 6
+        L.ref_forward_probe_pre.restype = _i
         self.L = L
 
     def rope(self, x, rope_type, n_rot, theta, pos, freq_factors=None):
@@ -168,6 +193,24 @@ class RefLib:
                                       _fp(k_rot), _fp(attn))
         assert rc == 0, "probe self-check failed"
         del nk
+        return dict(q_pre=q_pre, k_pre=k_pre, v_pre=v_pre, q_rot=q_rot, k_rot=k_rot, attn=attn)
+
+    def forward_probe_pre(self, x_in, n_head, n_kv, d, n_ctx, rope_type, n_rot, theta, bias_q, bias_k, bias_v, norm_q,
+                          norm_k, eps, freq_factors=None):
+        """forward_probe on a layer that also has q/k/v biases and per-head q/k norm weights."""
+        n_tok, ne = x_in.shape
+        assert ne == n_head * d
+        q_pre = np.empty((n_tok, n_head, d), np.float32)
+        k_pre = np.empty((n_tok, n_kv, d), np.float32)
+        v_pre = np.empty((n_tok, n_kv, d), np.float32)
+        q_rot = np.empty((n_tok, n_head, d), np.float32)
+        k_rot = np.empty((n_tok, n_kv, d), np.float32)
+        attn = np.empty((n_tok, n_head, d), np.float32)
+        rc = self.L.ref_forward_probe_pre(_fp(x_in), n_tok, n_head, n_kv, d, n_ctx, rope_type, n_rot, theta,
+                                          _fp(freq_factors), _fp(bias_q), _fp(bias_k), _fp(bias_v), _fp(norm_q),
+                                          _fp(norm_k), eps, _fp(q_pre), _fp(k_pre), _fp(v_pre), _fp(q_rot), _fp(k_rot),
+                                          _fp(attn))
+        assert rc == 0, "probe self-check failed"
         return dict(q_pre=q_pre, k_pre=k_pre, v_pre=v_pre, q_rot=q_rot, k_rot=k_rot, attn=attn)
 
     def kv_shift(self, kcache, vcache, n_layer, n_kv, d, n_ctx, n_keep, shift):

@@ -47,6 +47,14 @@ llm::Tensor make_f32(std::vector<float>& buf, int ne0, int ne1) {
 
 } // namespace
 
+// Runs the reference's forward() on the one-layer probe model; optional q/k/v biases and per-head q/k norm weights
+// are attached to the layer the way the loader would (Layer::bq/bk/bv/wq_norm/wk_norm, model_cpu.cpp:258-274).
+static int probe_impl(const float* x_in, int n_tok, int n_head, int n_kv, int d, int n_ctx,
+                      int rope_type, int n_rot, float theta, const float* freq_factors,
+                      const float* bias_q, const float* bias_k, const float* bias_v,
+                      const float* norm_q, const float* norm_k, float eps,
+                      float* q_pre, float* k_pre, float* v_pre, float* q_rot, float* k_rot, float* attn);
+
 extern "C" {
 
 void ref_rope(float* x, int rope_type, int n_rot, float theta, int pos, const float* freq_factors) {
@@ -123,6 +131,41 @@ int ref_attend_chunk_mt(const float* q, const float* kcache, const float* vcache
 int ref_forward_probe(const float* x_in, int n_tok, int n_head, int n_kv, int d, int n_ctx,
                       int rope_type, int n_rot, float theta, const float* freq_factors,
                       float* q_pre, float* k_pre, float* v_pre, float* q_rot, float* k_rot, float* attn) {
+    return probe_impl(x_in, n_tok, n_head, n_kv, d, n_ctx, rope_type, n_rot, theta, freq_factors,
+                      nullptr, nullptr, nullptr, nullptr, nullptr, 1e-6f, q_pre, k_pre, v_pre, q_rot, k_rot, attn);
+}
+
+// As ref_forward_probe, with q/k/v biases and per-head q/k RMSNorm weights on the layer.  q_pre/k_pre/v_pre are the
+// projections BEFORE bias and norm (what a fused prologue receives); q_rot/k_rot what forward() fed to attention.
+int ref_forward_probe_pre(const float* x_in, int n_tok, int n_head, int n_kv, int d, int n_ctx,
+                          int rope_type, int n_rot, float theta, const float* freq_factors,
+                          const float* bias_q, const float* bias_k, const float* bias_v,
+                          const float* norm_q, const float* norm_k, float eps,
+                          float* q_pre, float* k_pre, float* v_pre, float* q_rot, float* k_rot, float* attn) {
+    return probe_impl(x_in, n_tok, n_head, n_kv, d, n_ctx, rope_type, n_rot, theta, freq_factors,
+                      bias_q, bias_k, bias_v, norm_q, norm_k, eps, q_pre, k_pre, v_pre, q_rot, k_rot, attn);
+}
+
+// The reference's kv_shift on an fp32 cache (model_cpu.cpp:321-340), via its own member function.
+void ref_kv_shift(float* kcache, float* vcache, int n_layer, int n_kv, int d, int n_ctx, int n_keep, int shift) {
+    llm::HParams hp;
+    hp.n_layer = n_layer; hp.n_head_kv = n_kv; hp.head_dim = d; hp.n_ctx = n_ctx;
+    llm::Model::impl m;
+    const size_t n = (size_t)n_layer * n_kv * n_ctx * d;
+    m.k_cache_.assign(kcache, kcache + n);
+    m.v_cache_.assign(vcache, vcache + n);
+    m.kv_shift(hp, n_keep, shift);
+    memcpy(kcache, m.k_cache_.data(), n * sizeof(float));
+    memcpy(vcache, m.v_cache_.data(), n * sizeof(float));
+}
+
+} // extern "C"
+
+static int probe_impl(const float* x_in, int n_tok, int n_head, int n_kv, int d, int n_ctx,
+                      int rope_type, int n_rot, float theta, const float* freq_factors,
+                      const float* bias_q, const float* bias_k, const float* bias_v,
+                      const float* norm_q, const float* norm_k, float eps,
+                      float* q_pre, float* k_pre, float* v_pre, float* q_rot, float* k_rot, float* attn) {
     const int ne = n_head * d, nk = n_kv * d;
     ProbeModel pm;
     pm.embd.assign(x_in, x_in + (size_t)n_tok * ne);
@@ -154,7 +197,7 @@ int ref_forward_probe(const float* x_in, int n_tok, int n_head, int n_kv, int d,
     hp.arch = "probe";
     hp.n_vocab = n_tok; hp.n_embd = ne; hp.n_layer = 1; hp.n_head = n_head; hp.n_head_kv = n_kv;
     hp.head_dim = d; hp.n_ff = 1; hp.n_rot = n_rot; hp.n_ctx = n_ctx;
-    hp.rms_eps = 1e-6f; hp.rope_theta = theta; hp.rope_type = rope_type;
+    hp.rms_eps = eps; hp.rope_theta = theta; hp.rope_type = rope_type;
     hp.rope_freq_factors = freq_factors;
 
     llm::Model::impl m;
@@ -166,6 +209,13 @@ int ref_forward_probe(const float* x_in, int n_tok, int n_head, int n_kv, int d,
     L.wq = &pm.t_q; L.wk = &pm.t_k; L.wv = &pm.t_v; L.wo = &pm.t_o;
     L.ffn_gate = &pm.t_gate; L.ffn_up = &pm.t_up; L.ffn_down = &pm.t_down;
     L.attn_norm = &pm.t_n1; L.ffn_norm = &pm.t_n2;
+    std::vector<float> bq, bk, bv, nq, nkw;
+    llm::Tensor t_bq, t_bk, t_bv, t_nq, t_nk;
+    if (bias_q) { bq.assign(bias_q, bias_q + ne); t_bq = make_f32(bq, ne, 1); L.bq = &t_bq; }
+    if (bias_k) { bk.assign(bias_k, bias_k + nk); t_bk = make_f32(bk, nk, 1); L.bk = &t_bk; }
+    if (bias_v) { bv.assign(bias_v, bias_v + nk); t_bv = make_f32(bv, nk, 1); L.bv = &t_bv; }
+    if (norm_q) { nq.assign(norm_q, norm_q + d); t_nq = make_f32(nq, d, 1); L.wq_norm = &t_nq; }
+    if (norm_k) { nkw.assign(norm_k, norm_k + d); t_nk = make_f32(nkw, d, 1); L.wk_norm = &t_nk; }
     m.init_buffers(hp);
 
     std::vector<float> xn(ne);
@@ -184,22 +234,8 @@ int ref_forward_probe(const float* x_in, int n_tok, int n_head, int n_kv, int d,
         // v is stored untouched in the cache; check the probe's own claim about it
         for (int h = 0; h < n_kv; ++h)
             for (int i = 0; i < d; ++i)
-                if (m.v_cache_[((size_t)h * n_ctx + t) * d + i] != v_pre[(size_t)t * nk + h * d + i]) return -1;
+                if (m.v_cache_[((size_t)h * n_ctx + t) * d + i] !=
+                    v_pre[(size_t)t * nk + h * d + i] + (bias_v ? bias_v[h * d + i] : 0.0f)) return -1;
     }
     return 0;
 }
-
-// The reference's kv_shift on an fp32 cache (model_cpu.cpp:321-340), via its own member function.
-void ref_kv_shift(float* kcache, float* vcache, int n_layer, int n_kv, int d, int n_ctx, int n_keep, int shift) {
-    llm::HParams hp;
-    hp.n_layer = n_layer; hp.n_head_kv = n_kv; hp.head_dim = d; hp.n_ctx = n_ctx;
-    llm::Model::impl m;
-    const size_t n = (size_t)n_layer * n_kv * n_ctx * d;
-    m.k_cache_.assign(kcache, kcache + n);
-    m.v_cache_.assign(vcache, vcache + n);
-    m.kv_shift(hp, n_keep, shift);
-    memcpy(kcache, m.k_cache_.data(), n * sizeof(float));
-    memcpy(vcache, m.v_cache_.data(), n * sizeof(float));
-}
-
-} // extern "C"

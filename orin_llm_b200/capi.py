@@ -20,7 +20,7 @@ PART_PAD = 4
 EXPORTS = [
     "oattn_strerror", "oattn_last_cuda_error", "oattn_init", "oattn_sm_count", "oattn_rope",
     "oattn_kv_store", "oattn_kv_shift", "oattn_decode_workspace_bytes", "oattn_decode",
-    "oattn_decode_noalloc_max_bytes", "oattn_decode_noalloc",
+    "oattn_decode_ex", "oattn_prefill_ex", "oattn_decode_noalloc_max_bytes", "oattn_decode_noalloc",
     "oattn_decode_partial", "oattn_combine", "oattn_peer_buffer_bytes", "oattn_peer_state_bytes",
     "oattn_decode_partial_push", "oattn_peer_wait_combine", "oattn_decode_peer", "oattn_peer_status", "oattn_prefill_workspace_bytes", "oattn_prefill",
     "oattn_prefill_status",
@@ -32,6 +32,12 @@ EXPORTS = [
 class RopeParams(ctypes.Structure):
     _fields_ = [("rope_type", ctypes.c_int), ("n_rot", ctypes.c_int), ("theta", ctypes.c_float),
                 ("freq_factors", ctypes.c_void_p)]
+
+
+class Ext(ctypes.Structure):
+    _fields_ = [("bias_q", ctypes.c_void_p), ("bias_k", ctypes.c_void_p), ("bias_v", ctypes.c_void_p),
+                ("norm_q", ctypes.c_void_p), ("norm_k", ctypes.c_void_p), ("norm_eps", ctypes.c_float),
+                ("out_qs", ctypes.c_void_p), ("out_scales", ctypes.c_void_p)]
 
 
 class AttnError(RuntimeError):
@@ -67,6 +73,9 @@ def lib():
     L.oattn_decode_workspace_bytes.restype = sz
     L.oattn_decode_workspace_bytes.argtypes = [i, i, i]
     L.oattn_decode.argtypes = [vp, vp, vp, vp, vp, vp, i, i, i, i, vp, f, i, rp, vp, sz, vp]
+    ep = ctypes.POINTER(Ext)
+    L.oattn_decode_ex.argtypes = [vp, vp, vp, vp, vp, vp, i, i, i, i, vp, f, i, rp, ep, vp, sz, vp]
+    L.oattn_prefill_ex.argtypes = [vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, f, i, rp, ep, vp, sz, vp]
     L.oattn_decode_noalloc_max_bytes.restype = sz
     L.oattn_decode_noalloc_max_bytes.argtypes = []
     L.oattn_decode_noalloc.argtypes = [vp, vp, vp, vp, i, i, i, i, vp, f, vp]

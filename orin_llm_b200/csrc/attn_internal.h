@@ -38,6 +38,9 @@ struct DecodeArgs {
     int fuse;
     RopeArgs rope;
     int emit_partial;      // combine writes the un-normalised record instead of the normalised output
+    PreArgs pre;                   // optional bias / per-head RMSNorm in front of RoPE
+    int8_t* out_qs = nullptr;      // optional q8_1 form of the output: int8 [n_head*hd] ...
+    float* out_scales = nullptr;   // ... and one fp32 scale per 32 values; `out` may then be nullptr
     const unsigned long long* peer_bufs = nullptr;   // multi-GPU peer exchange: device array of `world` buffer pointers
     int* gen_push = nullptr;                          // [n_head] generation counters (private to this rank)
     int rank = 0, world = 1;
@@ -77,6 +80,7 @@ struct PrefillArgs {
     float scale;
     int fuse;
     RopeArgs rope;
+    PreArgs pre;           // optional bias / per-head RMSNorm in front of RoPE (k and v parts only with the append)
 };
 
 // Prologue shared by both prefill kernels: RoPE(q) -> q16, RoPE(k_new) + fp16 append of k_new, v_new.

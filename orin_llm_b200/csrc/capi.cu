@@ -154,19 +154,38 @@ struct PeerTarget {
     int* status = nullptr;
 };
 
+// Checks an extension block and copies it into the kernel arguments.  k/v bias and k norm act on the appended row,
+// so they need the fused append; the q8_1 output exists for the decode call only.
+static int apply_ext(const oattn_ext* ext, int fuse, bool allow_q8, int n_head, int n_kv, PreArgs& pre, int8_t** out_qs,
+                     float** out_scales) {
+    if (!ext) return OATTN_OK;
+    const bool append = (fuse & OATTN_FUSE_KV_APPEND) != 0;
+    if ((ext->bias_k || ext->bias_v || ext->norm_k) && !append) return OATTN_ERR_ARG;
+    if ((ext->norm_q || ext->norm_k) && !(ext->norm_eps >= 0.0f)) return OATTN_ERR_ARG;
+    if ((ext->out_qs != nullptr) != (ext->out_scales != nullptr)) return OATTN_ERR_ARG;
+    if (ext->out_qs && !allow_q8) return OATTN_ERR_UNSUPPORTED;
+    if ((ext->norm_q || ext->norm_k) && n_head + n_kv > 160) return OATTN_ERR_UNSUPPORTED;
+    pre.bias_q = ext->bias_q; pre.bias_k = ext->bias_k; pre.bias_v = ext->bias_v;
+    pre.norm_q = ext->norm_q; pre.norm_k = ext->norm_k; pre.eps = ext->norm_eps;
+    if (out_qs) { *out_qs = ext->out_qs; *out_scales = ext->out_scales; }
+    return OATTN_OK;
+}
+
 static int decode_common(const float* q, const float* k_new, const float* v_new, uint16_t* kc, uint16_t* vc, float* out,
                          int n_head, int n_kv, int head_dim, int n_ctx, const int* d_pos, int pos_bias, float scale,
                          int fuse, const oattn_rope_params* rope, int emit_partial, void* workspace, size_t workspace_bytes,
-                         void* stream, const PeerTarget* peer = nullptr) {
+                         void* stream, const PeerTarget* peer = nullptr, const oattn_ext* ext = nullptr) {
     if (!device_ready()) return OATTN_ERR_DEVICE;
     int rc = check_shape(n_head, n_kv, head_dim);
     if (rc != OATTN_OK) return rc;
-    if (!q || !kc || !vc || !out || !d_pos || n_ctx <= 0 || !(scale > 0.0f)) return OATTN_ERR_ARG;
+    const bool q8_only = ext && ext->out_qs && !emit_partial;     // the fp32 output is optional next to the q8_1 one
+    if (!q || !kc || !vc || (!out && !q8_only) || !d_pos || n_ctx <= 0 || !(scale > 0.0f)) return OATTN_ERR_ARG;
     if (fuse & ~OATTN_FUSE_ALL) return OATTN_ERR_ARG;
     if ((fuse & OATTN_FUSE_ROPE_K) && !(fuse & OATTN_FUSE_KV_APPEND)) return OATTN_ERR_ARG;
     if ((fuse & OATTN_FUSE_KV_APPEND) && (!k_new || !v_new)) return OATTN_ERR_ARG;
     DecodeArgs a;
     if ((rc = check_rope(fuse, rope, head_dim, a.rope)) != OATTN_OK) return rc;
+    if ((rc = apply_ext(ext, fuse, !emit_partial, n_head, n_kv, a.pre, &a.out_qs, &a.out_scales)) != OATTN_OK) return rc;
     const DecodeWs w = decode_ws(n_head, n_kv, head_dim, g_dev[g_cur].sm_count);
     if (!workspace || ((uintptr_t)workspace & 255) || workspace_bytes < w.total) return OATTN_ERR_WORKSPACE;
     a.q = q; a.k_new = k_new; a.v_new = v_new; a.kc = kc; a.vc = vc; a.out = out;
@@ -193,6 +212,13 @@ int oattn_decode(const float* q, const float* k_new, const float* v_new, uint16_
                  const oattn_rope_params* rope, void* workspace, size_t workspace_bytes, void* stream) {
     return decode_common(q, k_new, v_new, kc, vc, out, n_head, n_kv, head_dim, n_ctx, d_pos, 1, scale, fuse, rope, 0,
                          workspace, workspace_bytes, stream);
+}
+
+int oattn_decode_ex(const float* q, const float* k_new, const float* v_new, uint16_t* kc, uint16_t* vc, float* out,
+                    int n_head, int n_kv, int head_dim, int n_ctx, const int* d_pos, float scale, int fuse,
+                    const oattn_rope_params* rope, const oattn_ext* ext, void* workspace, size_t workspace_bytes, void* stream) {
+    return decode_common(q, k_new, v_new, kc, vc, out, n_head, n_kv, head_dim, n_ctx, d_pos, 1, scale, fuse, rope, 0,
+                         workspace, workspace_bytes, stream, nullptr, ext);
 }
 
 size_t oattn_decode_noalloc_max_bytes(void) { return kStaticScratchBytes; }
@@ -301,6 +327,14 @@ int oattn_prefill_status(const void* workspace, int n_head, int head_dim, int ba
 int oattn_prefill(const float* q, const float* k_new, const float* v_new, uint16_t* kc, uint16_t* vc, float* out,
                   int n_head, int n_kv, int head_dim, int n_ctx, int n_past, int batch, float scale, int fuse,
                   const oattn_rope_params* rope, void* workspace, size_t workspace_bytes, void* stream) {
+    return oattn_prefill_ex(q, k_new, v_new, kc, vc, out, n_head, n_kv, head_dim, n_ctx, n_past, batch, scale, fuse, rope,
+                            nullptr, workspace, workspace_bytes, stream);
+}
+
+int oattn_prefill_ex(const float* q, const float* k_new, const float* v_new, uint16_t* kc, uint16_t* vc, float* out,
+                     int n_head, int n_kv, int head_dim, int n_ctx, int n_past, int batch, float scale, int fuse,
+                     const oattn_rope_params* rope, const oattn_ext* ext, void* workspace, size_t workspace_bytes,
+                     void* stream) {
     if (!device_ready()) return OATTN_ERR_DEVICE;
     int rc = check_shape(n_head, n_kv, head_dim);
     if (rc != OATTN_OK) return rc;
@@ -311,6 +345,7 @@ int oattn_prefill(const float* q, const float* k_new, const float* v_new, uint16
     if ((fuse & OATTN_FUSE_KV_APPEND) && (!k_new || !v_new)) return OATTN_ERR_ARG;
     PrefillArgs a;
     if ((rc = check_rope(fuse, rope, head_dim, a.rope)) != OATTN_OK) return rc;
+    if ((rc = apply_ext(ext, fuse, false, n_head, n_kv, a.pre, nullptr, nullptr)) != OATTN_OK) return rc;
     const size_t need = oattn_prefill_workspace_bytes(n_head, n_kv, head_dim, batch);
     if (!workspace || ((uintptr_t)workspace & 255) || workspace_bytes < need) return OATTN_ERR_WORKSPACE;
     a.q = q; a.k_new = k_new; a.v_new = v_new; a.kc = kc; a.vc = vc; a.out = out;

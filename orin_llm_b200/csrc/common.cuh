@@ -17,6 +17,38 @@ struct RopeArgs {
     const float* freq_factors;  // device, n_rot/2 floats or nullptr
 };
 
+// Optional step in front of RoPE (src/model_cpu.cpp:258-274, src/model_gpu.cu:372-377): bias add on q/k/v, then a
+// per-head RMSNorm of q and k rows with a [head_dim] weight.  All pointers device, any of them may be nullptr.
+struct PreArgs {
+    const float* bias_q = nullptr;   // [n_head * head_dim]
+    const float* bias_k = nullptr;   // [n_kv * head_dim]
+    const float* bias_v = nullptr;   // [n_kv * head_dim]
+    const float* norm_q = nullptr;   // [head_dim]
+    const float* norm_k = nullptr;   // [head_dim]
+    float eps = 0.f;
+};
+
+// 1 / sqrt(mean((x + bias)^2) + eps) of one head row, computed by a full warp (rms_norm, src/model_cpu.cpp:13-18;
+// fp32 here, the CPU code accumulates in double).
+__device__ __forceinline__ float warp_row_rnorm(const float* x, const float* bias, int hd, float eps, int lane) {
+    float ss = 0.f;
+    for (int i = lane; i < hd; i += 32) {
+        const float v = x[i] + (bias ? bias[i] : 0.f);
+        ss = fmaf(v, v, ss);
+    }
+#pragma unroll
+    for (int off = 16; off; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+    return 1.0f / sqrtf(ss / (float)hd + eps);
+}
+
+// Element i of a head row after bias and norm: (x[i] + bias[i]) * r * w[i].
+__device__ __forceinline__ float pre_value(const float* x, const float* bias, const float* w, float r, int i) {
+    float v = x[i];
+    if (bias) v += bias[i];
+    if (w) v = v * r * w[i];
+    return v;
+}
+
 // ---- RoPE arithmetic -----------------------------------------------------------------------
 // Frequency of pair i exactly as the reference's CPU backend evaluates it
 // (src/model_cpu.cpp:182-183, 195-196): exponent -2i/n_rot rounded to fp32, theta^e rounded to
@@ -93,6 +125,20 @@ __device__ __forceinline__ float fast_exp2(float x) {
 // visible (a no-op for an ordinary launch); pdl_trigger() lets the next kernel of the stream begin launching.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+
+// ---- q8_1 activation form of the attention output --------------------------------------------------------
+// What the reference's quantize_q8_1_k (src/kernels.cu:136-145) makes of a vector: per group of 32 consecutive
+// values d = max|x| / 127 and q = round-half-away(x / d), q = 0 for an all-zero group; int8 values in `qs`, one fp32
+// d per group in `scales` (the layout its GEMV kernels read, src/kernels.cu:1763-1776).  Called by a full warp whose
+// lanes hold the 32 values of one group; `flat` is the value's index in the whole vector.  IEEE division.
+__device__ __forceinline__ void store_q8_group(float x, size_t flat, int8_t* qs, float* scales) {
+    float amax = fabsf(x);
+#pragma unroll
+    for (int off = 16; off; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+    const float d = __fdiv_rn(amax, 127.0f);
+    qs[flat] = amax == 0.0f ? (int8_t)0 : (int8_t)roundf(__fdiv_rn(x, d));
+    if ((threadIdx.x & 31) == 0) scales[flat >> 5] = d;
+}
 
 // Byte offset of (row, 16-byte chunk) inside a tile whose rows are ROW_BYTES wide, with the
 // chunk index XOR-ed by the row so that the 8 rows one ldmatrix phase touches fall in 8

@@ -63,26 +63,28 @@ __host__ __device__ inline SplitPlan plan_splits(int npos, int n_splits, int min
 
 __device__ __forceinline__ int clamp_len(int v, int n_ctx) { return v < 0 ? 0 : (v > n_ctx ? n_ctx : v); }
 
-// Rotates (optionally) one fp32 head row and writes it as fp16 through `store(elem, value)`.
+// Rotates (optionally) one fp32 head row and writes it as fp16 through `store(elem, value)`.  Before the rotation
+// the row gets its bias and per-head RMSNorm (`bias`, `nw` may be nullptr; `rn` is the row's 1/rms from
+// warp_row_rnorm when nw is set).
 template <typename Store>
-__device__ __forceinline__ void rope_row_to_half(const float* src, int hd, bool rotate, const RopeArgs& r,
-                                                 const float* s_cos, const float* s_sin, int lane_id, int lanes,
-                                                 Store store) {
+__device__ __forceinline__ void rope_row_to_half(const float* src, const float* bias, const float* nw, float rn, int hd,
+                                                 bool rotate, const RopeArgs& r, const float* s_cos, const float* s_sin,
+                                                 int lane_id, int lanes, Store store) {
     const int n_rot = rotate ? r.n_rot : 0;
     for (int pp = lane_id; pp < hd / 2; pp += lanes) {
         int i0, i1;
         float x0, x1;
         if (pp < n_rot / 2) {
             rope_pair_index(r.rope_type, pp, n_rot, i0, i1);
-            const float a = src[i0], b = src[i1];
+            const float a = pre_value(src, bias, nw, rn, i0), b = pre_value(src, bias, nw, rn, i1);
             const float c = s_cos[pp], s = s_sin[pp];
             x0 = a * c - b * s;
             x1 = a * s + b * c;
         } else {
             i0 = n_rot + 2 * (pp - n_rot / 2);
             i1 = i0 + 1;
-            x0 = src[i0];
-            x1 = src[i1];
+            x0 = pre_value(src, bias, nw, rn, i0);
+            x1 = pre_value(src, bias, nw, rn, i1);
         }
         store(i0, x0);
         store(i1, x1);
@@ -167,7 +169,9 @@ __global__ void __launch_bounds__(kThreads, 2) decode_split_kernel(const DecodeA
         // one warp per head row, round-robin
         for (int h = warp; h < G; h += kThreads / 32) {
             const float* src = p.q + (size_t)(kvh * G + h) * HD;
-            rope_row_to_half(src, HD, rope_q, p.rope, s_cos, s_sin, lane, 32, [&](int e, float v) {
+            const float* bq = p.pre.bias_q ? p.pre.bias_q + (size_t)(kvh * G + h) * HD : nullptr;
+            const float rn = p.pre.norm_q ? warp_row_rnorm(src, bq, HD, p.pre.eps, lane) : 1.f;
+            rope_row_to_half(src, bq, p.pre.norm_q, rn, HD, rope_q, p.rope, s_cos, s_sin, lane, 32, [&](int e, float v) {
                 *reinterpret_cast<__half*>(smem + L::Q_OFF + swz<L::ROWB>(h, e >> 3) + (e & 7) * 2) = __float2half_rn(v);
             });
         }
@@ -175,10 +179,15 @@ __global__ void __launch_bounds__(kThreads, 2) decode_split_kernel(const DecodeA
             __half* s_k = reinterpret_cast<__half*>(smem + L::KNEW_OFF);
             __half* s_v = reinterpret_cast<__half*>(smem + L::VNEW_OFF);
             if (warp == 0) {
-                rope_row_to_half(p.k_new + (size_t)kvh * HD, HD, rope_k, p.rope, s_cos, s_sin, lane, 32,
+                const float* src = p.k_new + (size_t)kvh * HD;
+                const float* bk = p.pre.bias_k ? p.pre.bias_k + (size_t)kvh * HD : nullptr;
+                const float rn = p.pre.norm_k ? warp_row_rnorm(src, bk, HD, p.pre.eps, lane) : 1.f;
+                rope_row_to_half(src, bk, p.pre.norm_k, rn, HD, rope_k, p.rope, s_cos, s_sin, lane, 32,
                                  [&](int e, float v) { s_k[e] = __float2half_rn(v); });
             } else if (warp == 1) {
-                for (int e = lane; e < HD; e += 32) s_v[e] = __float2half_rn(p.v_new[(size_t)kvh * HD + e]);
+                const float* bv = p.pre.bias_v ? p.pre.bias_v + (size_t)kvh * HD : nullptr;
+                for (int e = lane; e < HD; e += 32)
+                    s_v[e] = __float2half_rn(pre_value(p.v_new + (size_t)kvh * HD, bv, nullptr, 1.f, e));
             }
         }
     }
@@ -340,7 +349,9 @@ __global__ void __launch_bounds__(kThreads, 2) decode_split_kernel(const DecodeA
         }
         const int head = kvh * G + row;
         if (direct) {
-            p.out[(size_t)head * HD + d] = O / Lsum;
+            const float val = O / Lsum;
+            if (p.out) p.out[(size_t)head * HD + d] = val;
+            if (p.out_qs) store_q8_group(val, (size_t)head * HD + d, p.out_qs, p.out_scales);
         } else {
             p.ws_o[((size_t)head * p.n_splits + split) * HD + d] = O;
             if (d == 0) {
@@ -370,6 +381,8 @@ struct CombineArgs {
     const unsigned long long* peer_bufs;   // device array of `world` pointers (this rank's own buffer included)
     int* gen_push;                          // [n_head] private generation counters of this rank
     int rank, world, n_head;
+    int8_t* out_qs;                         // optional q8_1 form of the final output (see store_q8_group)
+    float* out_scales;
     int fused_wait;                         // also wait for all ranks' records and write the final output to `out`
     int* status;                            // raised when that wait ran out
 };
@@ -576,7 +589,9 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(const CombineA
                 rec[hd + 3] = 0.f;
             }
         } else {
-            p.out[(size_t)h * hd + tid] = Lsum > 0.f ? v / Lsum : 0.f;
+            const float val = Lsum > 0.f ? v / Lsum : 0.f;
+            if (p.out) p.out[(size_t)h * hd + tid] = val;
+            if (p.out_qs) store_q8_group(val, (size_t)h * hd + tid, p.out_qs, p.out_scales);
         }
     }
     if (p.emit_partial && p.peer_bufs) {
@@ -718,6 +733,8 @@ cudaError_t launch_decode(const DecodeArgs& a, cudaStream_t stream, unsigned lon
     c.n_head = a.n_head;
     c.fused_wait = a.fused_wait;
     c.status = a.peer_status;
+    c.out_qs = a.out_qs;
+    c.out_scales = a.out_scales;
     e = launch_dependent(combine_kernel, dim3(a.n_head), kCombineThreads, 0, stream, a.overlap, c);
     if (launches) *launches += 2;
     return e;
@@ -749,6 +766,8 @@ cudaError_t launch_combine_records(const float* parts, int n_parts, float* out, 
     c.n_head = n_head;
     c.fused_wait = 0;
     c.status = nullptr;
+    c.out_qs = nullptr;
+    c.out_scales = nullptr;
     combine_kernel<<<n_head, kCombineThreads, 0, stream>>>(c);
     if (launches) *launches += 1;
     return cudaGetLastError();

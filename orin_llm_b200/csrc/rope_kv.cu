@@ -99,6 +99,7 @@ __global__ void __launch_bounds__(kShiftThreads) kv_shift_kernel(uint16_t* kc, u
 // This is rope_*_batch(q), rope_*_batch(k), kv_store_batch of src/model_gpu.cu:379-383 plus the
 // fp16 conversion of Q that the reference does inside its attention kernel (src/kernels.cu:1393-1410).
 constexpr int kPrologueThreads = 256;
+constexpr int kPrologueMaxRows = 160;     // q and k head rows of one token whose 1/rms the norm step keeps in shared memory
 
 __global__ void __launch_bounds__(kPrologueThreads) prefill_prologue_kernel(const PrefillArgs p) {
     __shared__ float s_cos[64], s_sin[64];
@@ -113,6 +114,22 @@ __global__ void __launch_bounds__(kPrologueThreads) prefill_prologue_kernel(cons
         }
         __syncthreads();
     }
+    // bias and per-head RMSNorm in front of the rotation (src/model_gpu.cu:372-377): 1/rms of every q and k head row
+    __shared__ float s_rn[kPrologueMaxRows];
+    if (p.pre.norm_q || p.pre.norm_k) {
+        const int warp = tid >> 5, lane = tid & 31;
+        const int rows = p.n_head + (append ? p.n_kv : 0);
+        for (int row = warp; row < rows; row += kPrologueThreads / 32) {
+            const bool is_q = row < p.n_head;
+            const int head = is_q ? row : row - p.n_head;
+            const float* src = is_q ? p.q + ((size_t)b * p.n_head + head) * hd : p.k_new + ((size_t)b * p.n_kv + head) * hd;
+            const float* bias = is_q ? p.pre.bias_q : p.pre.bias_k;
+            const float* nw = is_q ? p.pre.norm_q : p.pre.norm_k;
+            const float rn = nw ? warp_row_rnorm(src, bias ? bias + (size_t)head * hd : nullptr, hd, p.pre.eps, lane) : 1.f;
+            if (lane == 0) s_rn[row] = rn;
+        }
+        __syncthreads();
+    }
     const float qs = p.scale * LOG2E;
     const int half = hd / 2;
     const int q_items = p.n_head * half;
@@ -124,18 +141,22 @@ __global__ void __launch_bounds__(kPrologueThreads) prefill_prologue_kernel(cons
         const bool rot = is_q ? rope_q : rope_k;
         const int n_rot = rot ? p.rope.n_rot : 0;
         const float* src = is_q ? p.q + ((size_t)b * p.n_head + head) * hd : p.k_new + ((size_t)b * p.n_kv + head) * hd;
+        const float* bias0 = is_q ? p.pre.bias_q : p.pre.bias_k;
+        const float* bias = bias0 ? bias0 + (size_t)head * hd : nullptr;
+        const float* nw = is_q ? p.pre.norm_q : p.pre.norm_k;
+        const float rn = nw ? s_rn[is_q ? head : p.n_head + head] : 1.f;
         int i0, i1;
         float x0, x1;
         if (pp < n_rot / 2) {
             rope_pair_index(p.rope.rope_type, pp, n_rot, i0, i1);
-            const float a = src[i0], c2 = src[i1];
+            const float a = pre_value(src, bias, nw, rn, i0), c2 = pre_value(src, bias, nw, rn, i1);
             x0 = a * s_cos[pp] - c2 * s_sin[pp];
             x1 = a * s_sin[pp] + c2 * s_cos[pp];
         } else {
             i0 = n_rot + 2 * (pp - n_rot / 2);
             i1 = i0 + 1;
-            x0 = src[i0];
-            x1 = src[i1];
+            x0 = pre_value(src, bias, nw, rn, i0);
+            x1 = pre_value(src, bias, nw, rn, i1);
         }
         if (is_q) {
             __half* dst = p.q16 + ((size_t)b * p.n_head + head) * hd;
@@ -150,8 +171,9 @@ __global__ void __launch_bounds__(kPrologueThreads) prefill_prologue_kernel(cons
     if (append) {
         for (int idx = tid; idx < p.n_kv * hd; idx += kPrologueThreads) {
             const int head = idx / hd, i = idx % hd;
+            const float* bv = p.pre.bias_v ? p.pre.bias_v + (size_t)head * hd : nullptr;
             p.vc[((size_t)head * p.n_ctx + pos) * hd + i] =
-                __half_as_ushort(__float2half_rn(p.v_new[((size_t)b * p.n_kv + head) * hd + i]));
+                __half_as_ushort(__float2half_rn(pre_value(p.v_new + ((size_t)b * p.n_kv + head) * hd, bv, nullptr, 1.f, i)));
         }
     }
 }

@@ -138,13 +138,37 @@ def flash_attention_decode_ind(q, kc, vc, out, n_head, n_kv, head_dim, n_ctx, d_
     attn_decode(q, None, None, kc, vc, out, n_head, n_kv, head_dim, n_ctx, d_pos, scale, FUSE_NONE, None, workspace)
 
 
+def _ext_params(ext):
+    """ext: dict with any of bias_q, bias_k, bias_v, norm_q, norm_k (fp32 CUDA tensors), norm_eps (float), out_qs (int8
+    tensor), out_scales (fp32 tensor) -> (pointer to capi.Ext or None, object to keep alive)."""
+    if not ext:
+        return None, None
+    unknown = set(ext) - {"bias_q", "bias_k", "bias_v", "norm_q", "norm_k", "norm_eps", "out_qs", "out_scales"}
+    if unknown:
+        raise ValueError("unknown extension keys: %s" % sorted(unknown))
+    e = capi.Ext()
+    for name in ("bias_q", "bias_k", "bias_v", "norm_q", "norm_k", "out_qs", "out_scales"):
+        t = ext.get(name)
+        setattr(e, name, t.data_ptr() if t is not None else None)
+    e.norm_eps = float(ext.get("norm_eps", 0.0))
+    return ctypes.byref(e), e
+
+
 def attn_decode(q, k_new, v_new, kc, vc, out, n_head, n_kv, head_dim, n_ctx, d_pos, scale, fuse=FUSE_ALL, rope=None,
-                workspace=None):
-    """Fused decode step of one layer (src/model_gpu.cu:277-282).  rope = (rope_type, n_rot, theta, freq_factors)."""
+                workspace=None, ext=None):
+    """Fused decode step of one layer (src/model_gpu.cu:277-282).  rope = (rope_type, n_rot, theta, freq_factors);
+    ext: optional bias / per-head norm in front and q8_1 output behind (see _ext_params)."""
     ws = workspace if workspace is not None else decode_workspace(n_head, n_kv, head_dim)
     ref, keep = _rope_params(rope)
-    capi.check(capi.lib().oattn_decode(_ptr(q), _ptr(k_new), _ptr(v_new), _ptr(kc), _ptr(vc), _ptr(out), n_head, n_kv,
-                                       head_dim, n_ctx, _ptr(d_pos), scale, fuse, ref, _ptr(ws), ws.numel(), _stream()))
+    if ext:
+        eref, ekeep = _ext_params(ext)
+        capi.check(capi.lib().oattn_decode_ex(_ptr(q), _ptr(k_new), _ptr(v_new), _ptr(kc), _ptr(vc), _ptr(out), n_head, n_kv,
+                                              head_dim, n_ctx, _ptr(d_pos), scale, fuse, ref, eref, _ptr(ws), ws.numel(),
+                                              _stream()))
+        del ekeep
+    else:
+        capi.check(capi.lib().oattn_decode(_ptr(q), _ptr(k_new), _ptr(v_new), _ptr(kc), _ptr(vc), _ptr(out), n_head, n_kv,
+                                           head_dim, n_ctx, _ptr(d_pos), scale, fuse, ref, _ptr(ws), ws.numel(), _stream()))
     del keep
 
 
@@ -200,14 +224,15 @@ def attn_combine(parts, n_parts, out, n_head, head_dim):
 
 
 def attn_prefill(q, k_new, v_new, kc, vc, out, n_head, n_kv, head_dim, n_ctx, n_past, batch, scale, fuse=FUSE_ALL,
-                 rope=None, workspace=None):
-    """Fused prefill step of one layer (src/model_gpu.cu:379-384)."""
+                 rope=None, workspace=None, ext=None):
+    """Fused prefill step of one layer (src/model_gpu.cu:372-384).  ext: optional bias / per-head norm (_ext_params)."""
     ws = workspace if workspace is not None else prefill_workspace(n_head, n_kv, head_dim, batch)
     ref, keep = _rope_params(rope)
-    capi.check(capi.lib().oattn_prefill(_ptr(q), _ptr(k_new), _ptr(v_new), _ptr(kc), _ptr(vc), _ptr(out), n_head, n_kv,
-                                        head_dim, n_ctx, n_past, batch, scale, fuse, ref, _ptr(ws), ws.numel(),
-                                        _stream()))
-    del keep
+    eref, ekeep = _ext_params(ext)
+    capi.check(capi.lib().oattn_prefill_ex(_ptr(q), _ptr(k_new), _ptr(v_new), _ptr(kc), _ptr(vc), _ptr(out), n_head, n_kv,
+                                           head_dim, n_ctx, n_past, batch, scale, fuse, ref, eref, _ptr(ws), ws.numel(),
+                                           _stream()))
+    del keep, ekeep
 
 
 def prefill_status(n_head, n_kv, head_dim, batch, workspace=None):
