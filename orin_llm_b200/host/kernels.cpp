@@ -106,4 +106,28 @@ void attention_prefill_fused(const float* q, const float* k, const float* v, uin
                         g_prefill_ws, g_prefill_ws_bytes, s_stream), "attention_prefill_fused");
 }
 
+static oattn_ext to_ext(const AttnExtras& x) {
+    oattn_ext e;
+    e.bias_q = x.bq; e.bias_k = x.bk; e.bias_v = x.bv;
+    e.norm_q = x.q_norm; e.norm_k = x.k_norm; e.norm_eps = x.rms_eps;
+    e.out_qs = x.q8; e.out_scales = x.q8_scale;
+    return e;
+}
+void attention_decode_fused(const float* q, const float* k, const float* v, uint16_t* kc, uint16_t* vc, float* out,
+                            int n_head, int n_kv, int head_dim, int n_ctx, const int* d_pos, float scale, int rope_type,
+                            int n_rot, float theta, const float* freq_factors, const AttnExtras& extras) {
+    const oattn_rope_params rp = {rope_type, n_rot, theta, freq_factors};
+    const oattn_ext ext = to_ext(extras);
+    check(oattn_decode_ex(q, k, v, kc, vc, out, n_head, n_kv, head_dim, n_ctx, d_pos, scale, OATTN_FUSE_ALL, &rp, &ext,
+                          g_decode_ws, g_decode_ws_bytes, s_stream), "attention_decode_fused");
+}
+void attention_prefill_fused(const float* q, const float* k, const float* v, uint16_t* kc, uint16_t* vc, float* out,
+                             int n_head, int n_kv, int head_dim, int n_ctx, int n_past, int batch, float scale,
+                             int rope_type, int n_rot, float theta, const float* freq_factors, const AttnExtras& extras) {
+    const oattn_rope_params rp = {rope_type, n_rot, theta, freq_factors};
+    const oattn_ext ext = to_ext(extras);
+    check(oattn_prefill_ex(q, k, v, kc, vc, out, n_head, n_kv, head_dim, n_ctx, n_past, batch, scale, OATTN_FUSE_ALL, &rp, &ext,
+                           g_prefill_ws, g_prefill_ws_bytes, s_stream), "attention_prefill_fused");
+}
+
 } // namespace llm::cuda

@@ -13,6 +13,9 @@
 //     of the caller's arena, handed over once.
 //   - attention_decode_fused()/attention_prefill_fused(): one call for the sequences
 //     rope(q), rope(k), kv_store, flash_attention* at src/model_gpu.cu:277-282 and 379-384.
+//   - AttnExtras: the steps on either side of attention that the fused calls can absorb -- q/k/v bias add and
+//     per-head q/k RMSNorm (src/model_gpu.cu:372-377, 274-275) in front, the q8_1 activation form that
+//     quantize_activation(d_attn_) produces for the Wo GEMV (src/model_gpu.cu:284) behind (decode only).
 // Error convention as in the reference (src/common.h:10-22): a failed call prints and aborts.
 #pragma once
 
@@ -56,5 +59,23 @@ void attention_decode_fused(const float* q, const float* k, const float* v, uint
 void attention_prefill_fused(const float* q, const float* k, const float* v, uint16_t* kc, uint16_t* vc, float* out,
                              int n_head, int n_kv, int head_dim, int n_ctx, int n_past, int batch, float scale,
                              int rope_type, int n_rot, float theta, const float* freq_factors = nullptr);
+
+// Optional extras of the fused calls; device pointers, nullptr = step absent.
+struct AttnExtras {
+    const float* bq = nullptr;        // [n_head*head_dim]   Layer::bq
+    const float* bk = nullptr;        // [n_kv*head_dim]     Layer::bk
+    const float* bv = nullptr;        // [n_kv*head_dim]     Layer::bv
+    const float* q_norm = nullptr;    // [head_dim]          Layer::wq_norm
+    const float* k_norm = nullptr;    // [head_dim]          Layer::wk_norm
+    float rms_eps = 0.0f;             // HParams::rms_eps
+    int8_t* q8 = nullptr;             // decode only: int8 [n_head*head_dim], as g_q8 (src/kernels.cu:1748)
+    float* q8_scale = nullptr;        //              fp32 [n_head*head_dim/32], as g_q8_scale (src/kernels.cu:1749)
+};
+void attention_decode_fused(const float* q, const float* k, const float* v, uint16_t* kc, uint16_t* vc, float* out,
+                            int n_head, int n_kv, int head_dim, int n_ctx, const int* d_pos, float scale,
+                            int rope_type, int n_rot, float theta, const float* freq_factors, const AttnExtras& extras);
+void attention_prefill_fused(const float* q, const float* k, const float* v, uint16_t* kc, uint16_t* vc, float* out,
+                             int n_head, int n_kv, int head_dim, int n_ctx, int n_past, int batch, float scale,
+                             int rope_type, int n_rot, float theta, const float* freq_factors, const AttnExtras& extras);
 
 } // namespace llm::cuda

@@ -39,6 +39,15 @@ void shim_prefill_layer_fused(const float* q, const float* k, const float* v, ui
                               int n_rot, float theta) {
     cuda::attention_prefill_fused(q, k, v, kc, vc, out, n_head, n_kv, hd, n_ctx, n_past, batch, scale, rope_type, n_rot, theta, nullptr);
 }
+// Fused decode call of a layer with biases, q/k norm and the q8_1 output (src/model_gpu.cu:268-284 in one call).
+void shim_decode_layer_fused_extras(const float* q, const float* k, const float* v, uint16_t* kc, uint16_t* vc, float* out,
+                                    int n_head, int n_kv, int hd, int n_ctx, const int* d_pos, float scale, int rope_type,
+                                    int n_rot, float theta, const float* bq, const float* bk, const float* bv,
+                                    const float* q_norm, const float* k_norm, float eps, int8_t* q8, float* q8_scale) {
+    cuda::AttnExtras x;
+    x.bq = bq; x.bk = bk; x.bv = bv; x.q_norm = q_norm; x.k_norm = k_norm; x.rms_eps = eps; x.q8 = q8; x.q8_scale = q8_scale;
+    cuda::attention_decode_fused(q, k, v, kc, vc, out, n_head, n_kv, hd, n_ctx, d_pos, scale, rope_type, n_rot, theta, nullptr, x);
+}
 void shim_kv_shift(uint16_t* kc, uint16_t* vc, int n_layer, int n_kv, int hd, int n_ctx, int n_keep, int shift) {
     cuda::kv_shift(kc, vc, n_layer, n_kv, hd, n_ctx, n_keep, shift);
 }

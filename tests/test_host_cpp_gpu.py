@@ -34,6 +34,7 @@ def shim(ops):
         getattr(L, name).argtypes = [vp] * 6 + [i] * 4 + [vp, f, i, i, f]
     for name in ("shim_prefill_layer_unfused", "shim_prefill_layer_fused"):
         getattr(L, name).argtypes = [vp] * 6 + [i] * 6 + [f, i, i, f]
+    L.shim_decode_layer_fused_extras.argtypes = [vp] * 6 + [i] * 4 + [vp, f, i, i, f] + [vp] * 5 + [f, vp, vp]
     assert L.shim_init(0) == 0
     return L
 
@@ -75,3 +76,45 @@ def test_reference_call_sequences(shim, oracle, rope_type, n_head, n_kv, theta):
                n_kv, hd, n_ctx, d_pos.data_ptr(), float(scale), rope_type, hd, theta)
         torch.cuda.synchronize()
         assert_close(out.cpu().numpy(), want, "C++ wrappers, fused=%s" % fused)
+
+
+def test_fused_decode_with_extras_through_the_cpp_wrapper(shim, oracle):
+    """attention_decode_fused with AttnExtras: biases, q/k norm and the q8_1 output in one call."""
+    n_head, n_kv, hd, n_ctx, pos = 16, 2, 128, 512, 300
+    scale = np.float32(1.0 / np.sqrt(hd))
+    rng = np.random.default_rng(95)
+    K = rng.standard_normal((n_kv, n_ctx, hd)).astype(np.float16)
+    V = rng.standard_normal((n_kv, n_ctx, hd)).astype(np.float16)
+    K[:, pos:] = 0
+    V[:, pos:] = 0
+    q = rng.standard_normal((1, n_head, hd)).astype(np.float32)
+    k = rng.standard_normal((1, n_kv, hd)).astype(np.float32)
+    v = rng.standard_normal((1, n_kv, hd)).astype(np.float32)
+    opt = dict(bias_q=(0.3 * rng.standard_normal(n_head * hd)).astype(np.float32),
+               bias_k=(0.3 * rng.standard_normal(n_kv * hd)).astype(np.float32),
+               bias_v=(0.3 * rng.standard_normal(n_kv * hd)).astype(np.float32),
+               norm_q=(1 + 0.2 * rng.standard_normal(hd)).astype(np.float32),
+               norm_k=(1 + 0.2 * rng.standard_normal(hd)).astype(np.float32))
+    qo, ko, vo = q.copy(), k.copy(), v.copy()
+    oracle.pre_attention(qo, ko, vo, eps=1e-6, **opt)
+    vo = vo.astype(np.float16).astype(np.float32)
+    want = oracle.attn_batch(qo, ko, vo, K.astype(np.float32), V.astype(np.float32), pos, scale, True, 1, hd, 1e6, None)[0]
+
+    nbytes = shim.shim_scratch_size(n_head, n_kv, hd, 1)
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    shim.shim_scratch_assign(scratch.data_ptr(), n_head, n_kv, hd, 1)
+    shim.shim_set_stream(torch.cuda.current_stream().cuda_stream)
+    dK, dV = dev(K), dev(V)
+    d = {name: dev(a) for name, a in opt.items()}
+    out = torch.empty(n_head, hd, device="cuda")
+    qs = torch.empty(n_head * hd, dtype=torch.int8, device="cuda")
+    sc = torch.empty(n_head * hd // 32, device="cuda")
+    d_pos = torch.tensor([pos], dtype=torch.int32, device="cuda")
+    shim.shim_decode_layer_fused_extras(dev(q[0]).data_ptr(), dev(k[0]).data_ptr(), dev(v[0]).data_ptr(), dK.data_ptr(),
+                                        dV.data_ptr(), out.data_ptr(), n_head, n_kv, hd, n_ctx, d_pos.data_ptr(), float(scale),
+                                        1, hd, 1e6, d["bias_q"].data_ptr(), d["bias_k"].data_ptr(), d["bias_v"].data_ptr(),
+                                        d["norm_q"].data_ptr(), d["norm_k"].data_ptr(), 1e-6, qs.data_ptr(), sc.data_ptr())
+    torch.cuda.synchronize()
+    assert_close(out.cpu().numpy(), want, "C++ wrapper with extras")
+    want_q, want_s = oracle.quantize_q8_1(out.cpu().numpy())
+    assert np.array_equal(qs.cpu().numpy(), want_q) and np.array_equal(sc.cpu().numpy(), want_s)
