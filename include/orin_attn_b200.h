@@ -69,7 +69,10 @@ const char* oattn_last_cuda_error(void);
 /* Replaces cuda::init (src/kernels.cu:1730-1737), generalised from device 0 to `device`:
  * makes it current, checks for compute capability 10.x, raises the shared-memory limits of the
  * kernels once (the reference does that on every launch, src/kernels.cu:1968,1988). */
-int oattn_init(int device);
+int oattn_init(int device);      /* device < 0: the calling thread's current device */
+/* Convenience for hosts without an arena of their own: `bytes` of device memory on the current device (cudaMalloc),
+ * never freed by the library.  The one allocating entry point; nothing else in this interface calls it. */
+int oattn_scratch_alloc(size_t bytes, void** ptr);
 /* Number of SMs of the initialised device (0 before oattn_init). */
 int oattn_sm_count(void);
 
@@ -123,8 +126,8 @@ int oattn_decode(const float* q, const float* k_new, const float* v_new, uint16_
  * of oattn_decode_noalloc_max_bytes() (2 MiB) that is part of the library image in device memory; every GPU that
  * loads the library holds that block until the process ends.  Shapes whose partials do not fit
  * (n_head * splits * (head_dim + 2) * 4 bytes, splits = 2 * SMs / n_kv) are refused with OATTN_ERR_WORKSPACE and a
- * message in oattn_last_cuda_error(); nothing is allocated or freed, here or later.  The first call on each device
- * looks up the block's device address (device must be current, as after oattn_init); make that first call outside
+ * message in oattn_last_cuda_error(); nothing is allocated or freed, here or later.  The block's device address is
+ * looked up by oattn_init (if a device was never initialised the first call does it; make that first call outside
  * any stream capture.  All calls on a device share the one block and it keeps what the previous call wrote: nothing
  * in it has to start at zero (each call overwrites the slots it later reads), but two calls that run on the GPU at
  * the same time -- different streams, or a graph replay overlapping an eager call -- would overwrite each other's

@@ -18,7 +18,7 @@ PART_PAD = 4
 
 # Every symbol include/orin_attn_b200.h declares.
 EXPORTS = [
-    "oattn_strerror", "oattn_last_cuda_error", "oattn_init", "oattn_sm_count", "oattn_rope",
+    "oattn_strerror", "oattn_last_cuda_error", "oattn_init", "oattn_scratch_alloc", "oattn_sm_count", "oattn_rope",
     "oattn_kv_store", "oattn_kv_shift", "oattn_decode_workspace_bytes", "oattn_decode",
     "oattn_decode_ex", "oattn_prefill_ex", "oattn_decode_noalloc_max_bytes", "oattn_decode_noalloc",
     "oattn_decode_partial", "oattn_combine", "oattn_peer_buffer_bytes", "oattn_peer_state_bytes",
@@ -67,6 +67,7 @@ def lib():
     L.oattn_last_cuda_error.argtypes = []
     L.oattn_init.argtypes = [i]
     L.oattn_sm_count.argtypes = []
+    L.oattn_scratch_alloc.argtypes = [sz, ctypes.POINTER(ctypes.c_void_p)]
     L.oattn_rope.argtypes = [vp, i, i, i, i, f, i, i, vp, vp, vp]
     L.oattn_kv_store.argtypes = [vp, vp, vp, vp, i, i, i, i, i, vp, vp]
     L.oattn_kv_shift.argtypes = [vp, vp, i, i, i, i, i, i, vp]

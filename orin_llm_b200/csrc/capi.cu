@@ -89,8 +89,12 @@ const char* oattn_strerror(int code) {
 const char* oattn_last_cuda_error(void) { return g_cuda_err; }
 
 int oattn_init(int device) {
-    if (device < 0 || device >= kMaxDevices) return OATTN_ERR_ARG;
-    cudaError_t e = cudaSetDevice(device);
+    cudaError_t e;
+    if (device < 0) {       // the calling thread's current device
+        if ((e = cudaGetDevice(&device)) != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+    }
+    if (device >= kMaxDevices) return OATTN_ERR_ARG;
+    e = cudaSetDevice(device);
     if (e != cudaSuccess) return cuda_fail(e, "cudaSetDevice");
     int major = 0, sms = 0;
     if ((e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device)) != cudaSuccess) return cuda_fail(e, "cudaDeviceGetAttribute");
@@ -100,11 +104,20 @@ int oattn_init(int device) {
         if ((e = decode_set_attributes()) != cudaSuccess) return cuda_fail(e, "decode attributes");
         if ((e = prefill_mma_set_attributes()) != cudaSuccess) return cuda_fail(e, "prefill (mma) attributes");
         if ((e = prefill_tc_set_attributes()) != cudaSuccess) return cuda_fail(e, "prefill (tcgen05) attributes");
+        void* scratch = nullptr;      // look the built-in scratch block up now, so that oattn_decode_noalloc never has to
+        if ((e = decode_static_scratch(&scratch)) != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(built-in scratch)");
         g_dev[device].sm_count = sms;
         g_dev[device].ready = true;
     }
     g_cur = device;
     return OATTN_OK;
+}
+
+int oattn_scratch_alloc(size_t bytes, void** ptr) {
+    if (!ptr || bytes == 0) return OATTN_ERR_ARG;
+    if (!device_ready()) return OATTN_ERR_DEVICE;
+    cudaError_t e = cudaMalloc(ptr, bytes);
+    return e == cudaSuccess ? OATTN_OK : cuda_fail(e, "cudaMalloc(scratch)");
 }
 
 int oattn_sm_count(void) { return device_ready() ? g_dev[g_cur].sm_count : 0; }

@@ -19,6 +19,38 @@ size_t g_prefill_ws_bytes = 0;
 
 inline size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
+bool g_ready = false;                // a device was initialised through this library
+
+void check(int rc, const char* what);
+
+// Hosts that never call init()/attn_scratch_assign() (the reference's model_gpu.cu linked as it is) still work: the
+// first wrapper call initialises the current device; prefill scratch is allocated on demand (prefill is never
+// captured in a graph); decode falls back to the library's built-in scratch block.
+void ensure_ready() {
+    if (g_ready) return;
+    check(oattn_init(-1), "init (on first use)");
+    g_ready = true;
+}
+
+void ensure_prefill_scratch(int n_head, int n_kv, int head_dim, int batch) {
+    const size_t need = oattn_prefill_workspace_bytes(n_head, n_kv, head_dim, batch);
+    if (g_prefill_ws && g_prefill_ws_bytes >= need) return;
+    void* p = nullptr;
+    check(oattn_scratch_alloc(need, &p), "prefill scratch");
+    g_prefill_ws = p;            // a smaller block handed over earlier stays with its owner
+    g_prefill_ws_bytes = need;
+}
+
+// Fused decode needs a real workspace (the built-in block serves the unfused call only).
+void ensure_decode_scratch(int n_head, int n_kv, int head_dim) {
+    if (g_decode_ws) return;
+    const size_t need = oattn_decode_workspace_bytes(n_head, n_kv, head_dim);
+    void* p = nullptr;
+    check(oattn_scratch_alloc(need, &p), "decode scratch");
+    g_decode_ws = p;
+    g_decode_ws_bytes = need;
+}
+
 void check(int rc, const char* what) {
     if (rc == OATTN_OK) return;
     fprintf(stderr, "[cuda::%s] %s%s%s\n", what, oattn_strerror(rc), rc == OATTN_ERR_CUDA ? ": " : "",
@@ -36,10 +68,12 @@ int init_device(int device) {
         fprintf(stderr, "[cuda::init] %s %s\n", oattn_strerror(rc), oattn_last_cuda_error());
         return -1;
     }
+    g_ready = true;
     return 0;
 }
 
 void set_stream(void* stream) { s_stream = stream; }
+void attn_set_stream(void* stream) { s_stream = stream; }
 
 size_t attn_scratch_size(int n_head, int n_kv, int head_dim, int max_batch) {
     return align256(oattn_decode_workspace_bytes(n_head, n_kv, head_dim)) +
@@ -54,38 +88,53 @@ void attn_scratch_assign(void* base, int n_head, int n_kv, int head_dim, int max
 }
 
 void rope_neox_batch(float* x, int rows, int head_dim, int n_rot, float theta, int n_past, int heads, const float* ff) {
+    ensure_ready();
     check(oattn_rope(x, rows, head_dim, OATTN_ROPE_NEOX, n_rot, theta, n_past, heads, nullptr, ff, s_stream), "rope_neox_batch");
 }
 void rope_normal_batch(float* x, int rows, int head_dim, int n_rot, float theta, int n_past, int heads, const float* ff) {
+    ensure_ready();
     check(oattn_rope(x, rows, head_dim, OATTN_ROPE_NORMAL, n_rot, theta, n_past, heads, nullptr, ff, s_stream), "rope_normal_batch");
 }
 void rope_neox_ind(float* x, int rows, int head_dim, int n_rot, float theta, const int* d_pos, const float* ff) {
+    ensure_ready();
     check(oattn_rope(x, rows, head_dim, OATTN_ROPE_NEOX, n_rot, theta, 0, 1, d_pos, ff, s_stream), "rope_neox_ind");
 }
 void rope_normal_ind(float* x, int rows, int head_dim, int n_rot, float theta, const int* d_pos, const float* ff) {
+    ensure_ready();
     check(oattn_rope(x, rows, head_dim, OATTN_ROPE_NORMAL, n_rot, theta, 0, 1, d_pos, ff, s_stream), "rope_normal_ind");
 }
 
 void kv_store_batch(uint16_t* kc, uint16_t* vc, const float* k, const float* v, int heads, int head_dim, int n_ctx,
                     int pos_base, int batch) {
+    ensure_ready();
     check(oattn_kv_store(kc, vc, k, v, heads, head_dim, n_ctx, pos_base, batch, nullptr, s_stream), "kv_store_batch");
 }
 void kv_store_ind(uint16_t* kc, uint16_t* vc, const float* k, const float* v, int heads, int head_dim, int n_ctx,
                   const int* d_pos) {
+    ensure_ready();
     check(oattn_kv_store(kc, vc, k, v, heads, head_dim, n_ctx, 0, 1, d_pos, s_stream), "kv_store_ind");
 }
 void kv_shift(uint16_t* kc, uint16_t* vc, int n_layer, int n_kv, int head_dim, int n_ctx, int n_keep, int shift) {
+    ensure_ready();
     check(oattn_kv_shift(kc, vc, n_layer, n_kv, head_dim, n_ctx, n_keep, shift, s_stream), "kv_shift");
 }
 
 void flash_attention(const float* q, const uint16_t* kc, const uint16_t* vc, float* out, int n_head, int n_kv,
                      int head_dim, int n_ctx, int n_past, int batch, float scale) {
+    ensure_ready();
+    ensure_prefill_scratch(n_head, n_kv, head_dim, batch);
     check(oattn_prefill(q, nullptr, nullptr, const_cast<uint16_t*>(kc), const_cast<uint16_t*>(vc), out, n_head, n_kv,
                         head_dim, n_ctx, n_past, batch, scale, OATTN_FUSE_NONE, nullptr, g_prefill_ws, g_prefill_ws_bytes,
                         s_stream), "flash_attention");
 }
 void flash_attention_decode_ind(const float* q, const uint16_t* kc, const uint16_t* vc, float* out, int n_head, int n_kv,
                                 int head_dim, int n_ctx, const int* d_pos, float scale) {
+    ensure_ready();
+    if (!g_decode_ws) {      // no scratch was handed over: the built-in block (graph-capturable, no allocation)
+        check(oattn_decode_noalloc(q, kc, vc, out, n_head, n_kv, head_dim, n_ctx, d_pos, scale, s_stream),
+              "flash_attention_decode_ind");
+        return;
+    }
     check(oattn_decode(q, nullptr, nullptr, const_cast<uint16_t*>(kc), const_cast<uint16_t*>(vc), out, n_head, n_kv,
                        head_dim, n_ctx, d_pos, scale, OATTN_FUSE_NONE, nullptr, g_decode_ws, g_decode_ws_bytes, s_stream),
           "flash_attention_decode_ind");
@@ -95,6 +144,8 @@ void attention_decode_fused(const float* q, const float* k, const float* v, uint
                             int n_head, int n_kv, int head_dim, int n_ctx, const int* d_pos, float scale, int rope_type,
                             int n_rot, float theta, const float* freq_factors) {
     const oattn_rope_params rp = {rope_type, n_rot, theta, freq_factors};
+    ensure_ready();
+    ensure_decode_scratch(n_head, n_kv, head_dim);
     check(oattn_decode(q, k, v, kc, vc, out, n_head, n_kv, head_dim, n_ctx, d_pos, scale, OATTN_FUSE_ALL, &rp, g_decode_ws,
                        g_decode_ws_bytes, s_stream), "attention_decode_fused");
 }
@@ -102,6 +153,8 @@ void attention_prefill_fused(const float* q, const float* k, const float* v, uin
                              int n_head, int n_kv, int head_dim, int n_ctx, int n_past, int batch, float scale,
                              int rope_type, int n_rot, float theta, const float* freq_factors) {
     const oattn_rope_params rp = {rope_type, n_rot, theta, freq_factors};
+    ensure_ready();
+    ensure_prefill_scratch(n_head, n_kv, head_dim, batch);
     check(oattn_prefill(q, k, v, kc, vc, out, n_head, n_kv, head_dim, n_ctx, n_past, batch, scale, OATTN_FUSE_ALL, &rp,
                         g_prefill_ws, g_prefill_ws_bytes, s_stream), "attention_prefill_fused");
 }
@@ -118,6 +171,8 @@ void attention_decode_fused(const float* q, const float* k, const float* v, uint
                             int n_rot, float theta, const float* freq_factors, const AttnExtras& extras) {
     const oattn_rope_params rp = {rope_type, n_rot, theta, freq_factors};
     const oattn_ext ext = to_ext(extras);
+    ensure_ready();
+    ensure_decode_scratch(n_head, n_kv, head_dim);
     check(oattn_decode_ex(q, k, v, kc, vc, out, n_head, n_kv, head_dim, n_ctx, d_pos, scale, OATTN_FUSE_ALL, &rp, &ext,
                           g_decode_ws, g_decode_ws_bytes, s_stream), "attention_decode_fused");
 }
@@ -126,6 +181,8 @@ void attention_prefill_fused(const float* q, const float* k, const float* v, uin
                              int rope_type, int n_rot, float theta, const float* freq_factors, const AttnExtras& extras) {
     const oattn_rope_params rp = {rope_type, n_rot, theta, freq_factors};
     const oattn_ext ext = to_ext(extras);
+    ensure_ready();
+    ensure_prefill_scratch(n_head, n_kv, head_dim, batch);
     check(oattn_prefill_ex(q, k, v, kc, vc, out, n_head, n_kv, head_dim, n_ctx, n_past, batch, scale, OATTN_FUSE_ALL, &rp, &ext,
                            g_prefill_ws, g_prefill_ws_bytes, s_stream), "attention_prefill_fused");
 }

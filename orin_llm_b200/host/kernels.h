@@ -27,7 +27,12 @@ namespace llm::cuda {
 int init();                       // src/kernels.cu:1730-1737 (device 0)
 int init_device(int device);      // same, for one process per GPU
 void set_stream(void* stream);    // src/kernels.cu:1726-1728
+// Same effect under a name of its own, for a host that links this library NEXT TO the reference's kernels.cu (whose own
+// set_stream then keeps serving its GEMV kernels): call both, or wrap the reference's at link time.
+void attn_set_stream(void* stream);
 
+// Optional.  Without them the first wrapper call initialises the current device, prefill scratch is allocated on
+// demand and decode uses the library's built-in scratch block (oattn_decode_noalloc).
 size_t attn_scratch_size(int n_head, int n_kv, int head_dim, int max_batch);
 void attn_scratch_assign(void* base, int n_head, int n_kv, int head_dim, int max_batch);
 
