@@ -1,0 +1,110 @@
+"""End-to-end drop-in check and timing: the reference's own model code on a synthetic model, linked three ways.
+
+TEST INFRASTRUCTURE (see oracle/e2e/driver.cpp, oracle/Makefile target e2e).  Needs the binaries under oracle/_ref/
+(built where the reference tree is present) and a B200.
+
+    python oracle/e2e/run_e2e.py --arch qwen2-1.5b --prompt 45 --gen 128 --ctx 4096 --batch 512 [--cpu] [--zerocopy]
+
+Runs e2e_ref (the reference's GPU path, weights in device memory) greedily, then e2e_b200 (this repository's
+attention kernels dropped into the same model code) on the same token sequence, and reports for each build TTFT and
+TPOT, and between builds the step-by-step top-1 agreement and the largest logit difference after the prompt and after
+the last step.  --cpu adds the reference's CPU build as the fp32 oracle of the whole model (slow: use --arch tiny);
+--zerocopy adds the reference's GPU path exactly as it is (weights read through a host mapping).
+Prints one JSON object.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+REFDIR = os.path.join(os.path.dirname(HERE), "_ref")
+sys.path.insert(0, HERE)
+import make_gguf  # noqa: E402
+
+
+def binaries():
+    return {n: os.path.join(REFDIR, n) for n in ("e2e_cpu", "e2e_ref", "e2e_ref_zerocopy", "e2e_b200")}
+
+
+def available():
+    b = binaries()
+    return all(os.path.exists(b[n]) for n in ("e2e_ref", "e2e_b200"))
+
+
+def run_build(exe, model, tmp, tag, args, force=None):
+    tok, lg = os.path.join(tmp, tag + "_tok.bin"), os.path.join(tmp, tag + "_logits.bin")
+    cmd = [exe, "--model", model, "--prompt", str(args.prompt), "--gen", str(args.gen), "--ctx", str(args.ctx),
+           "--batch", str(args.batch), "--seed", str(args.seed), "--tokens-out", tok, "--logits-out", lg]
+    if force:
+        cmd += ["--force", force]
+    p = subprocess.run(cmd, capture_output=True, text=True, timeout=args.timeout)
+    if p.returncode != 0:
+        raise RuntimeError("%s failed (%d): %s" % (tag, p.returncode, (p.stderr or p.stdout)[-800:]))
+    line = [x for x in p.stdout.splitlines() if x.startswith("{")][-1]
+    r = json.loads(line)
+    r["tokens"] = np.fromfile(tok, np.int32)
+    r["logits"] = np.fromfile(lg, np.float32).reshape(2, -1)
+    return r
+
+
+def compare(a, b):
+    n = min(len(a["tokens"]), len(b["tokens"]))
+    d = np.abs(a["logits"] - b["logits"])
+    return {"top1_agreement": float((a["tokens"][:n] == b["tokens"][:n]).mean()), "steps_compared": int(n),
+            "max_logit_diff_after_prompt": float(d[0].max()), "max_logit_diff_after_last_step": float(d[1].max()),
+            "logit_scale": float(np.abs(a["logits"]).max())}
+
+
+def timing(r):
+    return {k: r[k] for k in ("ttft_ms", "tpot_ms", "tpot_ms_after_first", "n_ctx")}
+
+
+def run(args):
+    exe = binaries()
+    out = {"arch": args.arch, "layers": args.layers, "prompt": args.prompt, "gen": args.gen, "batch": args.batch}
+    with tempfile.TemporaryDirectory() as tmp:
+        model = os.path.join(tmp, "model.gguf")
+        cfg = dict(make_gguf.ARCHS[args.arch])
+        if args.layers:
+            cfg["n_layer"] = args.layers
+        make_gguf.write_model(model, cfg, seed=args.model_seed)
+        ref = run_build(exe["e2e_ref"], model, tmp, "ref", args)
+        forced = os.path.join(tmp, "forced.bin")
+        ref["tokens"][:args.gen].astype(np.int32).tofile(forced)
+        b200 = run_build(exe["e2e_b200"], model, tmp, "b200", args, forced)
+        out["reference_gpu"] = timing(ref)
+        out["b200_dropin"] = timing(b200)
+        out["b200_vs_reference_gpu"] = compare(b200, ref)
+        if args.zerocopy and os.path.exists(exe["e2e_ref_zerocopy"]):
+            out["reference_gpu_zerocopy"] = timing(run_build(exe["e2e_ref_zerocopy"], model, tmp, "zc", args, forced))
+        if args.cpu and os.path.exists(exe["e2e_cpu"]):
+            cpu = run_build(exe["e2e_cpu"], model, tmp, "cpu", args, forced)
+            out["reference_cpu"] = timing(cpu)
+            out["b200_vs_reference_cpu"] = compare(b200, cpu)
+            out["reference_gpu_vs_reference_cpu"] = compare(ref, cpu)
+    return out
+
+
+def parser():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--arch", default="tiny", choices=sorted(make_gguf.ARCHS))
+    ap.add_argument("--layers", type=int, default=None)
+    ap.add_argument("--prompt", type=int, default=45)
+    ap.add_argument("--gen", type=int, default=32)
+    ap.add_argument("--ctx", type=int, default=4096)
+    ap.add_argument("--batch", type=int, default=512)
+    ap.add_argument("--seed", type=int, default=7)
+    ap.add_argument("--model-seed", type=int, default=1234)
+    ap.add_argument("--cpu", action="store_true")
+    ap.add_argument("--zerocopy", action="store_true")
+    ap.add_argument("--timeout", type=int, default=900)
+    return ap
+
+
+if __name__ == "__main__":
+    print(json.dumps(run(parser().parse_args())))
