@@ -7,7 +7,7 @@
 // Protocol: prompt of P seeded token ids through forward_batch in chunks of `batch` (src/engine.cpp does the same),
 // then G single-token steps.  With --force FILE the token fed at each step comes from FILE (teacher forcing), so that
 // several builds can be compared step by step even after their greedy choices diverge; the build's own argmax is
-// still recorded.
+// still recorded.  --warmup runs an untimed pass first, so that one-time costs stay out of TTFT and TPOT.
 #include <chrono>
 #include <cstdint>
 #include <cstdio>
@@ -34,6 +34,7 @@ int main(int argc, char** argv) {
     std::string path, force, tokens_out, logits_out;
     int n_prompt = 45, n_gen = 16, n_ctx = 4096, batch = 512;
     uint64_t seed = 7;
+    bool warmup = false;
     for (int i = 1; i < argc; ++i) {
         std::string a = argv[i];
         auto next = [&]() { return std::string(i + 1 < argc ? argv[++i] : ""); };
@@ -44,6 +45,7 @@ int main(int argc, char** argv) {
         else if (a == "--batch") batch = atoi(next().c_str());
         else if (a == "--seed") seed = strtoull(next().c_str(), nullptr, 10);
         else if (a == "--force") force = next();
+        else if (a == "--warmup") warmup = true;
         else if (a == "--tokens-out") tokens_out = next();
         else if (a == "--logits-out") logits_out = next();
         else { fprintf(stderr, "unknown argument %s\n", a.c_str()); return 2; }
@@ -70,6 +72,15 @@ int main(int argc, char** argv) {
         int32_t t;
         while (fread(&t, sizeof(t), 1, f) == 1) forced.push_back(t);
         fclose(f);
+    }
+
+    // Untimed pass over the first chunk and one single-token step: module loading, first-use initialisation and (GPU
+    // builds) the capture of the decode graph happen here, for every build alike.  The timed run starts again at
+    // position 0 and overwrites what this wrote.
+    if (warmup) {
+        const int n = std::min(batch, n_prompt);
+        if (n > 1) model.forward_batch(prompt.data(), n, 0);
+        model.forward(prompt[0], n > 1 ? n : 0);
     }
 
     // prefill
