@@ -6,7 +6,8 @@ TEST INFRASTRUCTURE (see oracle/e2e/driver.cpp, oracle/Makefile target e2e).  Ne
     python oracle/e2e/run_e2e.py --arch qwen2-1.5b --prompt 45 --gen 128 --ctx 4096 --batch 512 [--cpu] [--zerocopy]
 
 Runs e2e_ref (the reference's GPU path, weights in device memory) greedily, then e2e_b200 (this repository's
-attention kernels dropped into the same model code) on the same token sequence, and reports for each build TTFT and
+attention kernels dropped into the same model code; once call by call, once with OATTN_FUSE_CALL_SEQUENCE=1) on the
+same token sequence, and reports for each build TTFT and
 TPOT, and between builds the step-by-step top-1 agreement and the largest logit difference after the prompt and after
 the last step.  --cpu adds the reference's CPU build as the fp32 oracle of the whole model (slow: use --arch tiny);
 --zerocopy adds the reference's GPU path exactly as it is (weights read through a host mapping).
@@ -36,7 +37,7 @@ def available():
     return all(os.path.exists(b[n]) for n in ("e2e_ref", "e2e_b200"))
 
 
-def run_build(exe, model, tmp, tag, args, force=None):
+def run_build(exe, model, tmp, tag, args, force=None, env=None):
     tok, lg = os.path.join(tmp, tag + "_tok.bin"), os.path.join(tmp, tag + "_logits.bin")
     cmd = [exe, "--model", model, "--prompt", str(args.prompt), "--gen", str(args.gen), "--ctx", str(args.ctx),
            "--batch", str(args.batch), "--seed", str(args.seed), "--tokens-out", tok, "--logits-out", lg]
@@ -44,7 +45,7 @@ def run_build(exe, model, tmp, tag, args, force=None):
         cmd.append("--warmup")
     if force:
         cmd += ["--force", force]
-    p = subprocess.run(cmd, capture_output=True, text=True, timeout=args.timeout)
+    p = subprocess.run(cmd, capture_output=True, text=True, timeout=args.timeout, env=dict(os.environ, **(env or {})))
     if p.returncode != 0:
         raise RuntimeError("%s failed (%d): %s" % (tag, p.returncode, (p.stderr or p.stdout)[-800:]))
     line = [x for x in p.stdout.splitlines() if x.startswith("{")][-1]
@@ -79,9 +80,13 @@ def run(args):
         forced = os.path.join(tmp, "forced.bin")
         ref["tokens"][:args.gen].astype(np.int32).tofile(forced)
         b200 = run_build(exe["e2e_b200"], model, tmp, "b200", args, forced)
+        # the same binary with call-sequence fusion on: the four calls per layer run as the fused launches
+        fused = run_build(exe["e2e_b200"], model, tmp, "b200f", args, forced, env={"OATTN_FUSE_CALL_SEQUENCE": "1"})
         out["reference_gpu"] = timing(ref)
         out["b200_dropin"] = timing(b200)
+        out["b200_dropin_fused_sequence"] = timing(fused)
         out["b200_vs_reference_gpu"] = compare(b200, ref)
+        out["b200_fused_sequence_vs_reference_gpu"] = compare(fused, ref)
         if args.zerocopy and os.path.exists(exe["e2e_ref_zerocopy"]):
             try:
                 out["reference_gpu_zerocopy"] = timing(run_build(exe["e2e_ref_zerocopy"], model, tmp, "zc", args, forced))

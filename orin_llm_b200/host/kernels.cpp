@@ -58,6 +58,77 @@ void check(int rc, const char* what) {
     abort();
 }
 
+// ---- call-sequence fusion (opt-in) ------------------------------------------------------------------------------
+// The reference issues rope(q), rope(k), kv_store, attention as four calls (src/model_gpu.cu:277-282, 379-384).  With
+// fusion on, the first three are only recorded; when the attention call that follows is their consumer (same q, the k
+// that was rotated is the k that was stored, same cache, same position), all four become the one fused launch.  Any
+// other call first issues what is pending, in order, so that the wrappers keep their meaning call by call.  What
+// changes for the host: q and k are no longer rotated in place (nothing in the reference reads them afterwards).
+struct PendingRope {
+    float* x; int rows, head_dim, rope_type, n_rot; float theta; int n_past, heads; const int* d_pos; const float* ff;
+};
+struct PendingStore {
+    uint16_t* kc; uint16_t* vc; const float* k; const float* v; int heads, head_dim, n_ctx, pos_base, batch; const int* d_pos;
+};
+int g_fuse_sequence = -1;            // -1: not decided yet (environment OATTN_FUSE_CALL_SEQUENCE), 0 off, 1 on
+PendingRope g_rope[2];
+int g_n_rope = 0;
+PendingStore g_store;
+bool g_store_on = false;
+
+bool fuse_sequence() {
+    if (g_fuse_sequence < 0) {
+        const char* e = getenv("OATTN_FUSE_CALL_SEQUENCE");
+        g_fuse_sequence = (e && e[0] == '1') ? 1 : 0;
+    }
+    return g_fuse_sequence == 1;
+}
+
+void issue_rope(const PendingRope& r) {
+    check(oattn_rope(r.x, r.rows, r.head_dim, r.rope_type, r.n_rot, r.theta, r.n_past, r.heads, r.d_pos, r.ff, s_stream), "rope");
+}
+void issue_store(const PendingStore& t) {
+    check(oattn_kv_store(t.kc, t.vc, t.k, t.v, t.heads, t.head_dim, t.n_ctx, t.pos_base, t.batch, t.d_pos, s_stream), "kv_store");
+}
+
+// Issue whatever is recorded, in the order it was called.
+void flush_pending() {
+    for (int i = 0; i < g_n_rope; ++i) issue_rope(g_rope[i]);
+    g_n_rope = 0;
+    if (g_store_on) issue_store(g_store);
+    g_store_on = false;
+}
+
+void rope_call(const PendingRope& r) {
+    ensure_ready();
+    if (!fuse_sequence()) { issue_rope(r); return; }
+    if (g_store_on || g_n_rope == 2) flush_pending();
+    g_rope[g_n_rope++] = r;
+}
+void store_call(const PendingStore& t) {
+    ensure_ready();
+    if (!fuse_sequence()) { issue_store(t); return; }
+    if (g_store_on) flush_pending();
+    g_store = t;
+    g_store_on = true;
+}
+
+// Are the recorded calls exactly the producers of this attention call?
+bool sequence_matches(const float* q, const uint16_t* kc, const uint16_t* vc, int n_head, int n_kv, int head_dim, int n_ctx,
+                      int n_past, int batch, const int* d_pos) {
+    if (g_n_rope != 2 || !g_store_on) return false;
+    const PendingRope& a = g_rope[0];
+    const PendingRope& b = g_rope[1];
+    const PendingStore& t = g_store;
+    return a.x == q && a.rows == batch * n_head && a.head_dim == head_dim && a.d_pos == d_pos && a.n_past == n_past &&
+           (d_pos || a.heads == n_head) &&
+           b.x == t.k && b.rows == batch * n_kv && b.head_dim == head_dim && b.d_pos == d_pos && b.n_past == n_past &&
+           (d_pos || b.heads == n_kv) &&
+           a.rope_type == b.rope_type && a.n_rot == b.n_rot && a.theta == b.theta && a.ff == b.ff &&
+           t.kc == kc && t.vc == vc && t.heads == n_kv && t.head_dim == head_dim && t.n_ctx == n_ctx && t.d_pos == d_pos &&
+           t.batch == batch && (d_pos || t.pos_base == n_past);
+}
+
 } // namespace
 
 int init() { return init_device(0); }
@@ -72,8 +143,9 @@ int init_device(int device) {
     return 0;
 }
 
-void set_stream(void* stream) { s_stream = stream; }
-void attn_set_stream(void* stream) { s_stream = stream; }
+void set_stream(void* stream) { flush_pending(); s_stream = stream; }
+void attn_set_stream(void* stream) { flush_pending(); s_stream = stream; }
+void attn_fuse_call_sequence(bool on) { flush_pending(); g_fuse_sequence = on ? 1 : 0; }
 
 size_t attn_scratch_size(int n_head, int n_kv, int head_dim, int max_batch) {
     return align256(oattn_decode_workspace_bytes(n_head, n_kv, head_dim)) +
@@ -81,6 +153,7 @@ size_t attn_scratch_size(int n_head, int n_kv, int head_dim, int max_batch) {
 }
 
 void attn_scratch_assign(void* base, int n_head, int n_kv, int head_dim, int max_batch) {
+    flush_pending();
     g_decode_ws = base;
     g_decode_ws_bytes = oattn_decode_workspace_bytes(n_head, n_kv, head_dim);
     g_prefill_ws = static_cast<uint8_t*>(base) + align256(g_decode_ws_bytes);
@@ -88,34 +161,29 @@ void attn_scratch_assign(void* base, int n_head, int n_kv, int head_dim, int max
 }
 
 void rope_neox_batch(float* x, int rows, int head_dim, int n_rot, float theta, int n_past, int heads, const float* ff) {
-    ensure_ready();
-    check(oattn_rope(x, rows, head_dim, OATTN_ROPE_NEOX, n_rot, theta, n_past, heads, nullptr, ff, s_stream), "rope_neox_batch");
+    rope_call({x, rows, head_dim, OATTN_ROPE_NEOX, n_rot, theta, n_past, heads, nullptr, ff});
 }
 void rope_normal_batch(float* x, int rows, int head_dim, int n_rot, float theta, int n_past, int heads, const float* ff) {
-    ensure_ready();
-    check(oattn_rope(x, rows, head_dim, OATTN_ROPE_NORMAL, n_rot, theta, n_past, heads, nullptr, ff, s_stream), "rope_normal_batch");
+    rope_call({x, rows, head_dim, OATTN_ROPE_NORMAL, n_rot, theta, n_past, heads, nullptr, ff});
 }
 void rope_neox_ind(float* x, int rows, int head_dim, int n_rot, float theta, const int* d_pos, const float* ff) {
-    ensure_ready();
-    check(oattn_rope(x, rows, head_dim, OATTN_ROPE_NEOX, n_rot, theta, 0, 1, d_pos, ff, s_stream), "rope_neox_ind");
+    rope_call({x, rows, head_dim, OATTN_ROPE_NEOX, n_rot, theta, 0, 1, d_pos, ff});
 }
 void rope_normal_ind(float* x, int rows, int head_dim, int n_rot, float theta, const int* d_pos, const float* ff) {
-    ensure_ready();
-    check(oattn_rope(x, rows, head_dim, OATTN_ROPE_NORMAL, n_rot, theta, 0, 1, d_pos, ff, s_stream), "rope_normal_ind");
+    rope_call({x, rows, head_dim, OATTN_ROPE_NORMAL, n_rot, theta, 0, 1, d_pos, ff});
 }
 
 void kv_store_batch(uint16_t* kc, uint16_t* vc, const float* k, const float* v, int heads, int head_dim, int n_ctx,
                     int pos_base, int batch) {
-    ensure_ready();
-    check(oattn_kv_store(kc, vc, k, v, heads, head_dim, n_ctx, pos_base, batch, nullptr, s_stream), "kv_store_batch");
+    store_call({kc, vc, k, v, heads, head_dim, n_ctx, pos_base, batch, nullptr});
 }
 void kv_store_ind(uint16_t* kc, uint16_t* vc, const float* k, const float* v, int heads, int head_dim, int n_ctx,
                   const int* d_pos) {
-    ensure_ready();
-    check(oattn_kv_store(kc, vc, k, v, heads, head_dim, n_ctx, 0, 1, d_pos, s_stream), "kv_store_ind");
+    store_call({kc, vc, k, v, heads, head_dim, n_ctx, 0, 1, d_pos});
 }
 void kv_shift(uint16_t* kc, uint16_t* vc, int n_layer, int n_kv, int head_dim, int n_ctx, int n_keep, int shift) {
     ensure_ready();
+    flush_pending();
     check(oattn_kv_shift(kc, vc, n_layer, n_kv, head_dim, n_ctx, n_keep, shift, s_stream), "kv_shift");
 }
 
@@ -123,6 +191,19 @@ void flash_attention(const float* q, const uint16_t* kc, const uint16_t* vc, flo
                      int head_dim, int n_ctx, int n_past, int batch, float scale) {
     ensure_ready();
     ensure_prefill_scratch(n_head, n_kv, head_dim, batch);
+    if (fuse_sequence()) {
+        ensure_decode_scratch(n_head, n_kv, head_dim);       // prefill is never captured: a safe place to allocate it
+        if (sequence_matches(q, kc, vc, n_head, n_kv, head_dim, n_ctx, n_past, batch, nullptr)) {
+            const oattn_rope_params rp = {g_rope[0].rope_type, g_rope[0].n_rot, g_rope[0].theta, g_rope[0].ff};
+            const PendingStore t = g_store;
+            g_n_rope = 0;
+            g_store_on = false;
+            check(oattn_prefill(q, t.k, t.v, t.kc, t.vc, out, n_head, n_kv, head_dim, n_ctx, n_past, batch, scale, OATTN_FUSE_ALL,
+                                &rp, g_prefill_ws, g_prefill_ws_bytes, s_stream), "flash_attention (fused sequence)");
+            return;
+        }
+        flush_pending();
+    }
     check(oattn_prefill(q, nullptr, nullptr, const_cast<uint16_t*>(kc), const_cast<uint16_t*>(vc), out, n_head, n_kv,
                         head_dim, n_ctx, n_past, batch, scale, OATTN_FUSE_NONE, nullptr, g_prefill_ws, g_prefill_ws_bytes,
                         s_stream), "flash_attention");
@@ -130,6 +211,18 @@ void flash_attention(const float* q, const uint16_t* kc, const uint16_t* vc, flo
 void flash_attention_decode_ind(const float* q, const uint16_t* kc, const uint16_t* vc, float* out, int n_head, int n_kv,
                                 int head_dim, int n_ctx, const int* d_pos, float scale) {
     ensure_ready();
+    if (fuse_sequence()) {
+        if (g_decode_ws && sequence_matches(q, kc, vc, n_head, n_kv, head_dim, n_ctx, 0, 1, d_pos)) {
+            const oattn_rope_params rp = {g_rope[0].rope_type, g_rope[0].n_rot, g_rope[0].theta, g_rope[0].ff};
+            const PendingStore t = g_store;
+            g_n_rope = 0;
+            g_store_on = false;
+            check(oattn_decode(q, t.k, t.v, t.kc, t.vc, out, n_head, n_kv, head_dim, n_ctx, d_pos, scale, OATTN_FUSE_ALL, &rp,
+                               g_decode_ws, g_decode_ws_bytes, s_stream), "flash_attention_decode_ind (fused sequence)");
+            return;
+        }
+        flush_pending();
+    }
     if (!g_decode_ws) {      // no scratch was handed over: the built-in block (graph-capturable, no allocation)
         check(oattn_decode_noalloc(q, kc, vc, out, n_head, n_kv, head_dim, n_ctx, d_pos, scale, s_stream),
               "flash_attention_decode_ind");
@@ -145,6 +238,7 @@ void attention_decode_fused(const float* q, const float* k, const float* v, uint
                             int n_rot, float theta, const float* freq_factors) {
     const oattn_rope_params rp = {rope_type, n_rot, theta, freq_factors};
     ensure_ready();
+    flush_pending();
     ensure_decode_scratch(n_head, n_kv, head_dim);
     check(oattn_decode(q, k, v, kc, vc, out, n_head, n_kv, head_dim, n_ctx, d_pos, scale, OATTN_FUSE_ALL, &rp, g_decode_ws,
                        g_decode_ws_bytes, s_stream), "attention_decode_fused");
@@ -154,6 +248,7 @@ void attention_prefill_fused(const float* q, const float* k, const float* v, uin
                              int rope_type, int n_rot, float theta, const float* freq_factors) {
     const oattn_rope_params rp = {rope_type, n_rot, theta, freq_factors};
     ensure_ready();
+    flush_pending();
     ensure_prefill_scratch(n_head, n_kv, head_dim, batch);
     check(oattn_prefill(q, k, v, kc, vc, out, n_head, n_kv, head_dim, n_ctx, n_past, batch, scale, OATTN_FUSE_ALL, &rp,
                         g_prefill_ws, g_prefill_ws_bytes, s_stream), "attention_prefill_fused");
@@ -172,6 +267,7 @@ void attention_decode_fused(const float* q, const float* k, const float* v, uint
     const oattn_rope_params rp = {rope_type, n_rot, theta, freq_factors};
     const oattn_ext ext = to_ext(extras);
     ensure_ready();
+    flush_pending();
     ensure_decode_scratch(n_head, n_kv, head_dim);
     check(oattn_decode_ex(q, k, v, kc, vc, out, n_head, n_kv, head_dim, n_ctx, d_pos, scale, OATTN_FUSE_ALL, &rp, &ext,
                           g_decode_ws, g_decode_ws_bytes, s_stream), "attention_decode_fused");
@@ -182,6 +278,7 @@ void attention_prefill_fused(const float* q, const float* k, const float* v, uin
     const oattn_rope_params rp = {rope_type, n_rot, theta, freq_factors};
     const oattn_ext ext = to_ext(extras);
     ensure_ready();
+    flush_pending();
     ensure_prefill_scratch(n_head, n_kv, head_dim, batch);
     check(oattn_prefill_ex(q, k, v, kc, vc, out, n_head, n_kv, head_dim, n_ctx, n_past, batch, scale, OATTN_FUSE_ALL, &rp, &ext,
                            g_prefill_ws, g_prefill_ws_bytes, s_stream), "attention_prefill_fused");

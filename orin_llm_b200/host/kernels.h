@@ -31,6 +31,14 @@ void set_stream(void* stream);    // src/kernels.cu:1726-1728
 // set_stream then keeps serving its GEMV kernels): call both, or wrap the reference's at link time.
 void attn_set_stream(void* stream);
 
+// Call-sequence fusion, off by default (on with attn_fuse_call_sequence(true) or OATTN_FUSE_CALL_SEQUENCE=1 in the
+// environment): rope(q), rope(k), kv_store are recorded instead of launched, and when the attention call that follows
+// consumes exactly them, the four become the one fused launch -- the reference's unmodified call sites
+// (src/model_gpu.cu:277-282, 379-384) then cost what attention_*_fused costs.  Any other call first issues what is
+// recorded, in order.  Visible difference: q and k are not rotated in place any more; turn it on only for a host that,
+// like the reference, does not read them after attention.
+void attn_fuse_call_sequence(bool on);
+
 // Optional.  Without them the first wrapper call initialises the current device, prefill scratch is allocated on
 // demand and decode uses the library's built-in scratch block (oattn_decode_noalloc).
 size_t attn_scratch_size(int n_head, int n_kv, int head_dim, int max_batch);

@@ -48,6 +48,17 @@ void shim_decode_layer_fused_extras(const float* q, const float* k, const float*
     x.bq = bq; x.bk = bk; x.bv = bv; x.q_norm = q_norm; x.k_norm = k_norm; x.rms_eps = eps; x.q8 = q8; x.q8_scale = q8_scale;
     cuda::attention_decode_fused(q, k, v, kc, vc, out, n_head, n_kv, hd, n_ctx, d_pos, scale, rope_type, n_rot, theta, nullptr, x);
 }
+// A decode sequence that must NOT fuse: the k that is stored is not the k that was rotated.
+void shim_decode_layer_mismatched(float* q, float* k, const float* k_stored, const float* v, uint16_t* kc, uint16_t* vc,
+                                  float* out, int n_head, int n_kv, int hd, int n_ctx, const int* d_pos, float scale,
+                                  int rope_type, int n_rot, float theta) {
+    auto rope_ind = rope_type == 1 ? cuda::rope_neox_ind : cuda::rope_normal_ind;
+    rope_ind(q, n_head, hd, n_rot, theta, d_pos, nullptr);
+    rope_ind(k, n_kv, hd, n_rot, theta, d_pos, nullptr);
+    cuda::kv_store_ind(kc, vc, k_stored, v, n_kv, hd, n_ctx, d_pos);
+    cuda::flash_attention_decode_ind(q, kc, vc, out, n_head, n_kv, hd, n_ctx, d_pos, scale);
+}
+void shim_fuse_call_sequence(int on) { cuda::attn_fuse_call_sequence(on != 0); }
 void shim_kv_shift(uint16_t* kc, uint16_t* vc, int n_layer, int n_kv, int hd, int n_ctx, int n_keep, int shift) {
     cuda::kv_shift(kc, vc, n_layer, n_kv, hd, n_ctx, n_keep, shift);
 }

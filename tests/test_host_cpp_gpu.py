@@ -34,6 +34,8 @@ def shim(ops):
         getattr(L, name).argtypes = [vp] * 6 + [i] * 4 + [vp, f, i, i, f]
     for name in ("shim_prefill_layer_unfused", "shim_prefill_layer_fused"):
         getattr(L, name).argtypes = [vp] * 6 + [i] * 6 + [f, i, i, f]
+    L.shim_fuse_call_sequence.argtypes = [i]
+    L.shim_decode_layer_mismatched.argtypes = [vp] * 7 + [i] * 4 + [vp, f, i, i, f]
     L.shim_decode_layer_fused_extras.argtypes = [vp] * 6 + [i] * 4 + [vp, f, i, i, f] + [vp] * 5 + [f, vp, vp]
     assert L.shim_init(0) == 0
     return L
@@ -118,3 +120,59 @@ def test_fused_decode_with_extras_through_the_cpp_wrapper(shim, oracle):
     assert_close(out.cpu().numpy(), want, "C++ wrapper with extras")
     want_q, want_s = oracle.quantize_q8_1(out.cpu().numpy())
     assert np.array_equal(qs.cpu().numpy(), want_q) and np.array_equal(sc.cpu().numpy(), want_s)
+
+
+def test_call_sequence_fusion(shim, ops, oracle):
+    """With call-sequence fusion on, the reference's four-call sequences run as the fused launches: same results as
+    the oracle, two launches per decode layer (split + merge) and two per prefill chunk (prologue + attention) instead
+    of five, q left unrotated; a sequence that does not match (another k buffer stored) is issued call by call."""
+    rope_type, n_head, n_kv, theta = 1, 12, 2, 1e6
+    hd, n_ctx, n_prompt, n_dec = 128, 512, 45, 3
+    scale = np.float32(1.0 / np.sqrt(hd))
+    rng = np.random.default_rng(97)
+    n_tok = n_prompt + n_dec
+    q = rng.standard_normal((n_tok, n_head, hd), dtype=np.float32)
+    k = rng.standard_normal((n_tok, n_kv, hd), dtype=np.float32)
+    v = rng.standard_normal((n_tok, n_kv, hd), dtype=np.float32).astype(np.float16).astype(np.float32)
+    kc32 = np.zeros((n_kv, n_ctx, hd), np.float32); vc32 = np.zeros_like(kc32)
+    want = oracle.attn_batch(q.copy(), k.copy(), v.copy(), kc32, vc32, 0, scale, True, rope_type, hd, theta, None)
+
+    nbytes = shim.shim_scratch_size(n_head, n_kv, hd, n_prompt)
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    shim.shim_scratch_assign(scratch.data_ptr(), n_head, n_kv, hd, n_prompt)
+    shim.shim_set_stream(torch.cuda.current_stream().cuda_stream)
+    shim.shim_fuse_call_sequence(1)
+    try:
+        kc = torch.zeros(n_kv, n_ctx, hd, dtype=torch.float16, device="cuda"); vc = torch.zeros_like(kc)
+        out = torch.empty(n_tok, n_head, hd, device="cuda")
+        dq, dk, dv = dev(q), dev(k), dev(v)
+        l0 = ops.launch_count()
+        shim.shim_prefill_layer_unfused(dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), kc.data_ptr(), vc.data_ptr(), out.data_ptr(),
+                                        n_head, n_kv, hd, n_ctx, 0, n_prompt, float(scale), rope_type, hd, theta)
+        assert ops.launch_count() - l0 == 2
+        d_pos = torch.zeros(1, dtype=torch.int32, device="cuda")
+        for t in range(n_prompt, n_tok):
+            d_pos.fill_(t)
+            l0 = ops.launch_count()
+            shim.shim_decode_layer_unfused(dq[t].data_ptr(), dk[t].data_ptr(), dv[t].data_ptr(), kc.data_ptr(), vc.data_ptr(),
+                                           out[t].data_ptr(), n_head, n_kv, hd, n_ctx, d_pos.data_ptr(), float(scale), rope_type,
+                                           hd, theta)
+            assert ops.launch_count() - l0 == 2
+        torch.cuda.synchronize()
+        assert_close(out.cpu().numpy(), want, "call-sequence fusion")
+        assert torch.equal(dq.cpu(), torch.from_numpy(q)), "q must be left as it was"
+        # a sequence whose stored k is not the k that was rotated does not fuse: five launches, q rotated in place
+        q0, k0, k_other = dev(q[0]), dev(k[0]), dev(k[1])
+        kc2 = torch.zeros_like(kc); vc2 = torch.zeros_like(kc)
+        o0 = torch.empty(n_head, hd, device="cuda")
+        d_pos.fill_(7)
+        l0 = ops.launch_count()
+        shim.shim_decode_layer_mismatched(q0.data_ptr(), k0.data_ptr(), k_other.data_ptr(), dv[0].data_ptr(), kc2.data_ptr(),
+                                          vc2.data_ptr(), o0.data_ptr(), n_head, n_kv, hd, n_ctx, d_pos.data_ptr(), float(scale),
+                                          rope_type, hd, theta)
+        torch.cuda.synchronize()
+        assert ops.launch_count() - l0 == 5
+        assert not torch.equal(q0.cpu(), torch.from_numpy(q[0]))
+        assert torch.equal(kc2[:, 7].cpu(), torch.from_numpy(k[1]).half())      # the unrotated other k, as asked
+    finally:
+        shim.shim_fuse_call_sequence(0)
