@@ -38,8 +38,10 @@ def build(ref_root="/root/reference"):
         subprocess.check_call(["make", "-s", "-C", HERE, "ref", "REF=" + ref_root])
         try:     # optional: the GPU-side cross-check needs nvcc and a minute of compile time
             subprocess.check_call(["make", "-s", "-C", HERE, "refcuda", "REF=" + ref_root])
+            if os.path.exists(os.path.join(os.path.dirname(HERE), "orin_llm_b200", "lib", "liborin_attn_host.so")):
+                subprocess.check_call(["make", "-s", "-C", HERE, "e2e", "REF=" + ref_root])
         except (subprocess.CalledProcessError, OSError) as e:
-            print("oracle: reference CUDA kernels not built (%s)" % e)
+            print("oracle: reference CUDA kernels / end-to-end binaries not built (%s)" % e)
 
 
 class Oracle:

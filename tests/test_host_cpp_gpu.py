@@ -112,7 +112,8 @@ def test_fused_decode_with_extras_through_the_cpp_wrapper(shim, oracle):
     qs = torch.empty(n_head * hd, dtype=torch.int8, device="cuda")
     sc = torch.empty(n_head * hd // 32, device="cuda")
     d_pos = torch.tensor([pos], dtype=torch.int32, device="cuda")
-    shim.shim_decode_layer_fused_extras(dev(q[0]).data_ptr(), dev(k[0]).data_ptr(), dev(v[0]).data_ptr(), dK.data_ptr(),
+    dq0, dk0, dv0 = dev(q[0]), dev(k[0]), dev(v[0])      # named, so that they outlive the call
+    shim.shim_decode_layer_fused_extras(dq0.data_ptr(), dk0.data_ptr(), dv0.data_ptr(), dK.data_ptr(),
                                         dV.data_ptr(), out.data_ptr(), n_head, n_kv, hd, n_ctx, d_pos.data_ptr(), float(scale),
                                         1, hd, 1e6, d["bias_q"].data_ptr(), d["bias_k"].data_ptr(), d["bias_v"].data_ptr(),
                                         d["norm_q"].data_ptr(), d["norm_k"].data_ptr(), 1e-6, qs.data_ptr(), sc.data_ptr())
