@@ -4,7 +4,6 @@ this repository's attention kernels, against the reference's GPU path and its CP
 The binaries are test infrastructure built from the reference tree by `make -C oracle e2e` (oracle/e2e/driver.cpp); the
 test is skipped where they were not built.  All builds are fed the same token sequence (teacher forcing), so the
 step-by-step top-1 agreement is meaningful even though random-init logits are nearly tied."""
-import argparse
 import os
 import sys
 
@@ -32,4 +31,3 @@ def test_reference_model_on_dropped_in_attention():
     assert r["b200_vs_reference_cpu"]["max_logit_diff_after_last_step"] <= 1.5 * floor + 1e-3
     for name in ("reference_gpu", "b200_dropin", "b200_dropin_fused_sequence"):
         assert 0 < r[name]["tpot_ms_after_first"] < 50 and r[name]["ttft_ms"] > 0
-    del argparse
