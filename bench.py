@@ -348,8 +348,9 @@ def run_b200(args, w):
 
     def e2e_body():
         d_in.copy_(h_in, non_blocking=True)                 # host -> device: this step's inputs
-        if world > 1 and owner:
-            # the rank that holds the newest row appends it for every layer first (the multi-GPU call has no fused
+        fused_peer = world > 1 and exchange == "peer"
+        if world > 1 and owner and not fused_peer:
+            # the rank that holds the newest row appends it for every layer first (these exchanges have no fused
             # append), so that no decode call directly follows a write to its own cache
             for l in range(layers):
                 ops.kv_store_ind(Kc[l], Vc[l], dk[l], dv[l], n_kv, hd, n_loc, d_pos)
@@ -357,6 +358,10 @@ def run_b200(args, w):
             if world == 1:
                 ops.attn_decode(dq[l], dk[l], dv[l], Kc[l], Vc[l], out[l], n_head, n_kv, hd, n_loc, d_pos, scale,
                                 ops.FUSE_KV_APPEND, None)
+            elif fused_peer:
+                # the owner of the newest row appends it inside its split kernel, as the single-GPU call does
+                dec.decode_fused(dq[l], dk[l] if owner else None, dv[l] if owner else None, Kc[l], Vc[l], n_loc, d_len, None,
+                                 scale, None, out[l], fuse=ops.FUSE_KV_APPEND if owner else ops.FUSE_NONE)
             else:
                 dec.decode(dq[l], Kc[l], Vc[l], n_loc, d_len, scale, out[l])
         hout.copy_(out, non_blocking=True)                  # device -> host: the step's result

@@ -175,6 +175,15 @@ int oattn_peer_wait_combine(const void* my_buf, int world, float* out, int n_hea
 int oattn_decode_peer(const float* q, const uint16_t* kc, const uint16_t* vc, float* out, int n_head, int n_kv, int head_dim,
                       int n_ctx, const int* d_len, float scale, void* workspace, size_t workspace_bytes,
                       const void* peer_bufs_dev, int rank, int world, void* state, void* stream);
+/* The same with the decode step's fused prologue, for a cache that is sharded by rows: every rank passes the unrotated q
+ * with OATTN_FUSE_ROPE_Q; the rank whose slice receives the new token passes k_new, v_new and OATTN_FUSE_ALL as well.
+ * `d_len` is the number of valid local rows INCLUDING the row being appended (it lands in local row *d_len - 1);
+ * `d_rope_pos` is the token's position in the whole sequence, which sets the rotation angle (device scalars, so the
+ * call replays from a graph).  No counterpart in the reference. */
+int oattn_decode_peer_fused(const float* q, const float* k_new, const float* v_new, uint16_t* kc, uint16_t* vc, float* out,
+                            int n_head, int n_kv, int head_dim, int n_ctx, const int* d_len, const int* d_rope_pos, float scale,
+                            int fuse, const oattn_rope_params* rope, void* workspace, size_t workspace_bytes,
+                            const void* peer_bufs_dev, int rank, int world, void* state, void* stream);
 /* Blocking read of the status word (0 = every wait so far was satisfied). */
 int oattn_peer_status(const void* state, int n_head, int* status);
 

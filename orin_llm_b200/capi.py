@@ -22,7 +22,7 @@ EXPORTS = [
     "oattn_kv_store", "oattn_kv_shift", "oattn_decode_workspace_bytes", "oattn_decode",
     "oattn_decode_ex", "oattn_prefill_ex", "oattn_decode_noalloc_max_bytes", "oattn_decode_noalloc",
     "oattn_decode_partial", "oattn_combine", "oattn_peer_buffer_bytes", "oattn_peer_state_bytes",
-    "oattn_decode_partial_push", "oattn_peer_wait_combine", "oattn_decode_peer", "oattn_peer_status", "oattn_prefill_workspace_bytes", "oattn_prefill",
+    "oattn_decode_partial_push", "oattn_peer_wait_combine", "oattn_decode_peer", "oattn_decode_peer_fused", "oattn_peer_status", "oattn_prefill_workspace_bytes", "oattn_prefill",
     "oattn_prefill_status",
     "oattn_set_prefill_impl", "oattn_set_decode_min_tiles", "oattn_set_decode_overlap", "oattn_profile_enable", "oattn_profile_collect",
     "oattn_launch_count",
@@ -89,6 +89,7 @@ def lib():
     L.oattn_decode_partial_push.argtypes = [vp, vp, vp, i, i, i, i, vp, f, vp, sz, vp, i, i, vp, vp]
     L.oattn_peer_wait_combine.argtypes = [vp, i, vp, i, i, vp, vp]
     L.oattn_decode_peer.argtypes = [vp, vp, vp, vp, i, i, i, i, vp, f, vp, sz, vp, i, i, vp, vp]
+    L.oattn_decode_peer_fused.argtypes = [vp, vp, vp, vp, vp, vp, i, i, i, i, vp, vp, f, i, rp, vp, sz, vp, i, i, vp, vp]
     L.oattn_peer_status.argtypes = [vp, i, ctypes.POINTER(ctypes.c_int)]
     L.oattn_prefill_workspace_bytes.restype = sz
     L.oattn_prefill_workspace_bytes.argtypes = [i, i, i, i]

@@ -39,6 +39,7 @@ struct DecodeArgs {
     RopeArgs rope;
     int emit_partial;      // combine writes the un-normalised record instead of the normalised output
     PreArgs pre;                   // optional bias / per-head RMSNorm in front of RoPE
+    const int* d_rope_pos = nullptr;   // position used for RoPE when it is not the local row index (sharded cache)
     int8_t* out_qs = nullptr;      // optional q8_1 form of the output: int8 [n_head*hd] ...
     float* out_scales = nullptr;   // ... and one fp32 scale per 32 values; `out` may then be nullptr
     const unsigned long long* peer_bufs = nullptr;   // multi-GPU peer exchange: device array of `world` buffer pointers

@@ -165,6 +165,7 @@ struct PeerTarget {
     int rank = 0, world = 1;
     int fused_wait = 0;
     int* status = nullptr;
+    const int* rope_pos = nullptr;
 };
 
 // Checks an extension block and copies it into the kernel arguments.  k/v bias and k norm act on the appended row,
@@ -209,7 +210,7 @@ static int decode_common(const float* q, const float* k_new, const float* v_new,
     a.n_splits = w.n_splits; a.min_tiles = g_decode_min_tiles; a.overlap = g_decode_overlap;
     a.scale = scale; a.fuse = fuse; a.emit_partial = emit_partial;
     if (peer) { a.peer_bufs = peer->bufs; a.gen_push = peer->gen_push; a.rank = peer->rank; a.world = peer->world;
-                a.fused_wait = peer->fused_wait; a.peer_status = peer->status; }
+                a.fused_wait = peer->fused_wait; a.peer_status = peer->status; a.d_rope_pos = peer->rope_pos; }
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     if (g_prof_ev && g_prof_n < g_prof_cap) {
         ev0 = g_prof_ev[2 * g_prof_n];
@@ -297,6 +298,24 @@ int oattn_decode_peer(const float* q, const uint16_t* kc, const uint16_t* vc, fl
     t.status = reinterpret_cast<int*>(state) + 2 * n_head;
     return decode_common(q, nullptr, nullptr, const_cast<uint16_t*>(kc), const_cast<uint16_t*>(vc), out, n_head, n_kv,
                          head_dim, n_ctx, d_len, 0, scale, OATTN_FUSE_NONE, nullptr, 1, workspace, workspace_bytes, stream, &t);
+}
+
+int oattn_decode_peer_fused(const float* q, const float* k_new, const float* v_new, uint16_t* kc, uint16_t* vc, float* out,
+                            int n_head, int n_kv, int head_dim, int n_ctx, const int* d_len, const int* d_rope_pos, float scale,
+                            int fuse, const oattn_rope_params* rope, void* workspace, size_t workspace_bytes,
+                            const void* peer_bufs_dev, int rank, int world, void* state, void* stream) {
+    if (!peer_bufs_dev || !state || !out || world < 1 || world > DECODE_MAX_RANKS || rank < 0 || rank >= world) return OATTN_ERR_ARG;
+    if ((fuse & (OATTN_FUSE_ROPE_Q | OATTN_FUSE_ROPE_K)) && !d_rope_pos) return OATTN_ERR_ARG;
+    PeerTarget t;
+    t.bufs = reinterpret_cast<const unsigned long long*>(peer_bufs_dev);
+    t.gen_push = reinterpret_cast<int*>(state);
+    t.rank = rank;
+    t.world = world;
+    t.fused_wait = 1;
+    t.status = reinterpret_cast<int*>(state) + 2 * n_head;
+    t.rope_pos = d_rope_pos;
+    return decode_common(q, k_new, v_new, kc, vc, out, n_head, n_kv, head_dim, n_ctx, d_len, 0, scale, fuse, rope, 1,
+                         workspace, workspace_bytes, stream, &t);
 }
 
 int oattn_peer_wait_combine(const void* my_buf, int world, float* out, int n_head, int head_dim, void* state, void* stream) {

@@ -156,7 +156,9 @@ __global__ void __launch_bounds__(kThreads, 2) decode_split_kernel(const DecodeA
     if (rope_q || (rope_k && owner)) {
         for (int i = tid; i < p.rope.n_rot / 2; i += kThreads) {
             const float f = rope_freq(i, p.rope.n_rot, p.rope.theta, p.rope.freq_factors);
-            rope_cs(new_pos, f, s_cos[i], s_sin[i]);
+            // the rotation angle follows the token's position in the whole sequence, which differs from the local row
+            // index when the cache holds only a slice of the sequence
+            rope_cs(p.d_rope_pos ? *p.d_rope_pos : new_pos, f, s_cos[i], s_sin[i]);
         }
         __syncthreads();
     }

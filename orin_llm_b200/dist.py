@@ -83,6 +83,18 @@ class PeerSplitKVDecoder:
         o.attn_peer_wait_combine(self.buf, self.world, out, self.n_head, self.head_dim, self.state)
         return out
 
+    def decode_fused(self, q, k_new, v_new, kc_local, vc_local, n_ctx_local, d_len_local, d_pos, scale, rope, out, fuse=None):
+        """Decode step with the fused prologue: q unrotated on every rank; the rank that holds the newest rows (the
+        last one) passes k_new / v_new, which are rotated at the global position *d_pos and appended at local row
+        *d_len_local - 1; the other ranks pass None."""
+        o = self.ops
+        if fuse is None:
+            fuse = o.FUSE_ALL if k_new is not None else o.FUSE_ROPE_Q
+        o.attn_decode_peer_fused(q, k_new, v_new, kc_local, vc_local, out, self.n_head, self.n_kv, self.head_dim, n_ctx_local,
+                                 d_len_local, d_pos, scale, fuse, rope, self.peer_bufs_dev, self.rank, self.world, self.state,
+                                 self.workspace)
+        return out
+
     def status(self):
         return self.ops.peer_status(self.state, self.n_head)
 

@@ -208,6 +208,19 @@ def attn_decode_peer(q, kc, vc, out, n_head, n_kv, head_dim, n_ctx, d_len, scale
                                             _ptr(state), _stream()))
 
 
+def attn_decode_peer_fused(q, k_new, v_new, kc, vc, out, n_head, n_kv, head_dim, n_ctx, d_len, d_rope_pos, scale, fuse, rope,
+                           peer_bufs_dev, rank, world, state, workspace=None):
+    """attn_decode_peer with the fused prologue on a row-sharded cache: RoPE(q) on every rank at the global position
+    *d_rope_pos; the rank that receives the new token also rotates and appends k_new / v_new (local row *d_len - 1)."""
+    ws = workspace if workspace is not None else decode_workspace(n_head, n_kv, head_dim)
+    ref, keep = _rope_params(rope)
+    capi.check(capi.lib().oattn_decode_peer_fused(_ptr(q), _ptr(k_new), _ptr(v_new), _ptr(kc), _ptr(vc), _ptr(out), n_head, n_kv,
+                                                  head_dim, n_ctx, _ptr(d_len), _ptr(d_rope_pos), scale, fuse, ref, _ptr(ws),
+                                                  ws.numel(), ctypes.c_void_p(int(peer_bufs_dev)), rank, world, _ptr(state),
+                                                  _stream()))
+    del keep
+
+
 def attn_peer_wait_combine(my_buf, world, out, n_head, head_dim, state):
     """Wait (bounded) until every rank's record of this step has landed in `my_buf`, then merge them into out."""
     capi.check(capi.lib().oattn_peer_wait_combine(_ptr(my_buf), world, _ptr(out), n_head, head_dim, _ptr(state), _stream()))

@@ -9,7 +9,7 @@ import numpy as np
 import pytest
 import torch
 
-from helpers import assert_close, make_qkv
+from helpers import assert_close, assert_f16_rows_match, make_qkv
 
 pytestmark = pytest.mark.gpu
 
@@ -74,3 +74,53 @@ def test_fused_exchange_world_one(ops, oracle):
         ops.attn_decode(dq, None, None, dK, dV, ref, n_head, n_kv, hd, L, d_pos, float(scale), fuse=ops.FUSE_NONE)
         torch.cuda.synchronize()
         assert torch.allclose(out, ref, rtol=1e-5, atol=1e-6)
+
+
+def test_fused_prologue_on_a_sharded_cache(ops, oracle):
+    """oattn_decode_peer_fused on the rank that owns the newest rows of a longer sequence: its local cache holds rows
+    [lo, pos) of the sequence as local rows 0..pos-lo-1, the new token is rotated at its GLOBAL position `pos` and
+    appended at local row pos-lo.  One rank (waits only for itself), checked against the oracle run on the slice."""
+    n_head, n_kv, hd, lo, pos = 16, 2, 128, 1000, 3000
+    n_loc = pos - lo
+    n_ctx = n_loc + 64
+    scale = np.float32(1.0 / np.sqrt(hd))
+    rng = np.random.default_rng(123)
+    _, K, V = make_qkv(124, n_head, n_kv, hd, n_loc, n_ctx)
+    q = rng.standard_normal((n_head, hd)).astype(np.float32)
+    k = rng.standard_normal((n_kv, hd)).astype(np.float32)
+    v = rng.standard_normal((n_kv, hd)).astype(np.float16).astype(np.float32)
+    # oracle: rotate at the global position, append at the local row, attend over the slice
+    qo, ko = q.copy(), k.copy()
+    for h in range(n_head):
+        oracle.rope(qo[h], 1, hd, 1e6, pos)
+    for h in range(n_kv):
+        oracle.rope(ko[h], 1, hd, 1e6, pos)
+    kc32, vc32 = K.astype(np.float32), V.astype(np.float32)
+    kc32[:, n_loc] = ko
+    vc32[:, n_loc] = v
+    want = oracle.attend(qo, kc32, vc32, n_loc + 1, scale)
+
+    buf = torch.zeros(ops.peer_buffer_bytes(1, n_head, hd), dtype=torch.uint8, device="cuda")
+    state = torch.zeros(ops.peer_state_bytes(n_head), dtype=torch.uint8, device="cuda")
+    ptrs = torch.tensor([buf.data_ptr()], dtype=torch.int64, device="cuda")
+    dK, dV = dev(K), dev(V)
+    out = torch.empty(n_head, hd, device="cuda")
+    d_len = torch.tensor([n_loc + 1], dtype=torch.int32, device="cuda")
+    d_rope = torch.tensor([pos], dtype=torch.int32, device="cuda")
+    ops.attn_decode_peer_fused(dev(q), dev(k), dev(v), dK, dV, out, n_head, n_kv, hd, n_ctx, d_len, d_rope, float(scale),
+                               ops.FUSE_ALL, (1, hd, 1e6, None), ptrs.data_ptr(), 0, 1, state)
+    torch.cuda.synchronize()
+    assert ops.peer_status(state, n_head) == 0
+    assert_close(out.cpu().numpy(), want, "fused prologue on a slice")
+    assert_f16_rows_match(dK[:, n_loc].cpu().numpy(), ko, "appended K row at the local index")
+    assert np.array_equal(dV[:, n_loc].cpu().numpy(), v.astype(np.float16))
+    # a rank that does not receive the token only rotates q: same q rotation, cache untouched
+    dK2, dV2 = dev(K), dev(V)
+    out2 = torch.empty(n_head, hd, device="cuda")
+    d_len2 = torch.tensor([n_loc], dtype=torch.int32, device="cuda")
+    ops.attn_decode_peer_fused(dev(q), None, None, dK2, dV2, out2, n_head, n_kv, hd, n_ctx, d_len2, d_rope, float(scale),
+                               ops.FUSE_ROPE_Q, (1, hd, 1e6, None), ptrs.data_ptr(), 0, 1, state)
+    torch.cuda.synchronize()
+    want2 = oracle.attend(qo, K.astype(np.float32), V.astype(np.float32), n_loc, scale)
+    assert_close(out2.cpu().numpy(), want2, "q-only rotation on a slice")
+    assert torch.equal(dK2.view(torch.int16), dev(K).view(torch.int16))
