@@ -176,33 +176,6 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
     asm("max.f32 %0, %1, %2, %3;\n" : "=f"(d) : "f"(a), "f"(b), "f"(c));
     return d;
 }
-// Packed pairs of fp32 (sm_100 f32x2 arithmetic): one instruction for two lanes of work.
-struct f2 { uint64_t u; };
-__device__ __forceinline__ f2 pack2(float a, float b) { f2 r; asm("mov.b64 %0, {%1, %2};\n" : "=l"(r.u) : "f"(a), "f"(b)); return r; }
-__device__ __forceinline__ void unpack2(f2 x, float& a, float& b) { asm("mov.b64 {%0, %1}, %2;\n" : "=f"(a), "=f"(b) : "l"(x.u)); }
-__device__ __forceinline__ f2 add2(f2 a, f2 b) { f2 r; asm("add.f32x2 %0, %1, %2;\n" : "=l"(r.u) : "l"(a.u), "l"(b.u)); return r; }
-__device__ __forceinline__ f2 sub2(f2 a, f2 b) { f2 r; asm("sub.f32x2 %0, %1, %2;\n" : "=l"(r.u) : "l"(a.u), "l"(b.u)); return r; }
-__device__ __forceinline__ f2 fma2(f2 a, f2 b, f2 c) { f2 r; asm("fma.rn.f32x2 %0, %1, %2, %3;\n" : "=l"(r.u) : "l"(a.u), "l"(b.u), "l"(c.u)); return r; }
-
-// (2^x0, 2^x1) on the FMA pipe (see exp2_poly): the float steps are packed, the exponent insertion is one integer
-// multiply-add per element (n * 2^23 + bits).
-__device__ __forceinline__ void exp2_poly2(f2 x, float& p0, float& p1) {
-    float x0, x1;
-    unpack2(x, x0, x1);
-    const f2 xc = pack2(fmaxf(x0, -125.f), fmaxf(x1, -125.f));
-    const f2 magic = pack2(12582912.f, 12582912.f);
-    const f2 fi = add2(xc, magic);
-    const f2 f = sub2(xc, sub2(fi, magic));
-    f2 q = fma2(pack2(0.05508868f, 0.05508868f), f, pack2(0.24260405f, 0.24260405f));
-    q = fma2(q, f, pack2(0.69327624f, 0.69327624f));
-    q = fma2(q, f, pack2(0.99992894f, 0.99992894f));
-    float q0, q1, n0, n1;
-    unpack2(q, q0, q1);
-    unpack2(fi, n0, n1);
-    p0 = __int_as_float(__float_as_int(n0) * 8388608 + __float_as_int(q0));
-    p1 = __int_as_float(__float_as_int(n1) * 8388608 + __float_as_int(q1));
-}
-
 // 2^x without the special-function unit: x = n + f with n = round(x), f in [-0.5, 0.5]; 2^f from a
 // degree-3 polynomial (relative error 7.7e-5, well below the fp16 rounding of P); 2^n by adding n to the
 // exponent field.  Inputs below -125 (including -inf for masked scores) give ~2^-125, which becomes 0 in fp16.
