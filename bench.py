@@ -41,8 +41,8 @@ PREFILL_WORKLOADS = {
     "prefill_8b_off4096": dict(n_head=32, n_kv=8, head_dim=128, batch=512, n_past=4096, theta=5e5, layers=32),
     "prefill_8b_off8192": dict(n_head=32, n_kv=8, head_dim=128, batch=512, n_past=8192, theta=5e5, layers=32),
 }
-NCU_READ_PER_KV_BYTE = 134.258 / 134.218     # dram__bytes_read.sum / algorithmic K+V bytes of the captured launch
-NCU_WRITE_BYTES_PER_LAUNCH = 4.02e6           # dram__bytes_write.sum of the captured launch
+NCU_READ_PER_KV_BYTE = 134.272 / 134.218     # dram__bytes_read.sum / algorithmic K+V bytes of the captured launch
+NCU_WRITE_BYTES_PER_LAUNCH = 4.46e6           # dram__bytes_write.sum of the captured launch
 CPU_SAMPLE_L = 131072      # rows of ONE layer call the CPU baseline / reference arm processes per step
 
 
@@ -420,7 +420,7 @@ def run_b200(args, w):
         "frac_of_nominal_8tbs": (achieved / 8000.0) if achieved else None,
     }
     # DRAM traffic of one split-kernel launch, from the ncu capture summarised in profiles/decode_split_kernel_L131072.md
-    # (16/2 heads, 131072 rows: dram__bytes_read 134.258 MB for 134.218 MB of K/V, dram__bytes_write 4.0 MB).  Reads
+    # (16/2 heads, 131072 rows: dram__bytes_read 134.272 MB for 134.218 MB of K/V, dram__bytes_write 4.2-4.7 MB).  Reads
     # grow with the rows streamed and are scaled by the bytes of this launch; the writes (split partials) do not
     # depend on the length and are added as captured.
     if per_launch_bytes:
