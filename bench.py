@@ -392,7 +392,7 @@ def run_b200(args, w):
     d2h = layers * n_head * hd * 4
 
     if exchange.startswith("peer") and dec.status() != 0:
-        raise SystemExit("peer exchange: a bounded flag wait ran out (rank %d)" % rank)
+        raise SystemExit("peer exchange: a bounded wait for the peers' records ran out (rank %d)" % rank)
 
     def finish():
         # Tearing the NCCL communicator / peer mappings down can block for minutes on some hosts; every rank has
@@ -472,8 +472,8 @@ def run_b200(args, w):
                    "launch": "eager" if args.no_graph else "cuda graph replay of the step",
                    "launch_order": {0: "ordinary launches", 1: "programmatic dependent launches",
                                     2: "programmatic dependent launches, K/V prefetch ahead of the dependency wait"}[args.overlap],
-                   "exchange": {"none": "single GPU", "peer": "merge kernel stores its record into every peer's buffer (NVLink peer stores), waits for the peers' flags and merges",
-                                "peer-split": "as peer, with the flag wait and final merge in a launch of their own",
+                   "exchange": {"none": "single GPU", "peer": "merge kernel stores its record into every peer's buffer (NVLink peer stores), waits for the peers' records (generation-tagged words) and merges",
+                                "peer-split": "as peer, with the wait and final merge in a launch of their own",
                                 "nccl": "NCCL all-gather of the records"}[exchange],
                    "l2": "inputs larger than L2: each of the %d layer calls of a step reads its own %.0f MiB of KV" % (
                        layers, per_launch_bytes / 2**20)},

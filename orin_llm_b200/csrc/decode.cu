@@ -379,7 +379,7 @@ struct CombineArgs {
     int pos_bias, n_ctx, n_splits, min_tiles;
     int emit_partial;
     // peer exchange (multi-GPU): when peer_bufs is set the un-normalised record of head h is stored straight into
-    // every rank's exchange buffer (plain stores over NVLink), followed by a per-(source, head) generation flag
+    // every rank's exchange buffer (plain stores over NVLink), each value tagged with the generation of the call
     const unsigned long long* peer_bufs;   // device array of `world` pointers (this rank's own buffer included)
     int* gen_push;                          // [n_head] private generation counters of this rank
     int rank, world, n_head;
@@ -609,9 +609,8 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(const CombineA
 }
 
 // ---- wait for every rank's record of this generation and merge them -------------------------------------------
-// One CTA per head.  Thread r polls the flag that rank r sets after its record for this head has landed in this
-// rank's exchange buffer; the poll is bounded (about two seconds), after which a status word is raised and the
-// kernel returns without touching the output.
+// One CTA per head, in a launch of its own (the form that can run after all pushes on a single GPU); the work is
+// peer_wait_merge above.
 struct PeerWaitArgs {
     const unsigned char* my_buf;
     float* out;

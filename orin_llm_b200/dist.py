@@ -45,8 +45,9 @@ def gather_records(local, world_buf, group=None):
 
 class PeerSplitKVDecoder:
     """Split-KV decode whose record exchange is done by the kernels themselves: the per-rank merge kernel stores
-    its record into every rank's exchange buffer with plain peer stores over NVLink and raises a flag, then waits
-    (bounded) for the other ranks' flags in its own buffer and writes the merged output.  One small kernel after
+    its record into every rank's exchange buffer with plain peer stores over NVLink (every value tagged with the call's
+    generation number), then waits (bounded) until the other ranks' values of this generation have arrived in its own
+    buffer and writes the merged output.  One small kernel after
     the split kernel, no collective call, graph-capturable; fused=False keeps the wait in a launch of its own.
     The exchange buffers come from torch's symmetric memory (CUDA VMM mappings of every rank's block); no multicast
     object is created and no library kernel ever sees a peer pointer."""
