@@ -63,34 +63,6 @@ __host__ __device__ inline SplitPlan plan_splits(int npos, int n_splits, int min
 
 __device__ __forceinline__ int clamp_len(int v, int n_ctx) { return v < 0 ? 0 : (v > n_ctx ? n_ctx : v); }
 
-// Rotates (optionally) one fp32 head row and writes it as fp16 through `store(elem, value)`.  Before the rotation
-// the row gets its bias and per-head RMSNorm (`bias`, `nw` may be nullptr; `rn` is the row's 1/rms from
-// warp_row_rnorm when nw is set).
-template <typename Store>
-__device__ __forceinline__ void rope_row_to_half(const float* src, const float* bias, const float* nw, float rn, int hd,
-                                                 bool rotate, const RopeArgs& r, const float* s_cos, const float* s_sin,
-                                                 int lane_id, int lanes, Store store) {
-    const int n_rot = rotate ? r.n_rot : 0;
-    for (int pp = lane_id; pp < hd / 2; pp += lanes) {
-        int i0, i1;
-        float x0, x1;
-        if (pp < n_rot / 2) {
-            rope_pair_index(r.rope_type, pp, n_rot, i0, i1);
-            const float a = pre_value(src, bias, nw, rn, i0), b = pre_value(src, bias, nw, rn, i1);
-            const float c = s_cos[pp], s = s_sin[pp];
-            x0 = a * c - b * s;
-            x1 = a * s + b * c;
-        } else {
-            i0 = n_rot + 2 * (pp - n_rot / 2);
-            i1 = i0 + 1;
-            x0 = pre_value(src, bias, nw, rn, i0);
-            x1 = pre_value(src, bias, nw, rn, i1);
-        }
-        store(i0, x0);
-        store(i1, x1);
-    }
-}
-
 template <int HD, bool WIDE>
 __global__ void __launch_bounds__(kThreads, 2) decode_split_kernel(const DecodeArgs p) {
     using L = DecodeSmem<HD>;

@@ -130,50 +130,35 @@ __global__ void __launch_bounds__(kPrologueThreads) prefill_prologue_kernel(cons
         }
         __syncthreads();
     }
+    // One warp per head row (q rows first, then the k rows when they are appended): the lanes walk the row's rotation
+    // pairs, so consecutive lanes touch consecutive addresses and no index arithmetic beyond the pair index is needed.
     const float qs = p.scale * LOG2E;
-    const int half = hd / 2;
-    const int q_items = p.n_head * half;
-    const int k_items = append ? p.n_kv * half : 0;
-    for (int idx = tid; idx < q_items + k_items; idx += kPrologueThreads) {
-        const bool is_q = idx < q_items;
-        const int li = is_q ? idx : idx - q_items;
-        const int head = li / half, pp = li % half;
-        const bool rot = is_q ? rope_q : rope_k;
-        const int n_rot = rot ? p.rope.n_rot : 0;
+    const int warp = tid >> 5, lane = tid & 31;
+    const int rows = p.n_head + (append ? p.n_kv : 0);
+    for (int row = warp; row < rows; row += kPrologueThreads / 32) {
+        const bool is_q = row < p.n_head;
+        const int head = is_q ? row : row - p.n_head;
         const float* src = is_q ? p.q + ((size_t)b * p.n_head + head) * hd : p.k_new + ((size_t)b * p.n_kv + head) * hd;
         const float* bias0 = is_q ? p.pre.bias_q : p.pre.bias_k;
         const float* bias = bias0 ? bias0 + (size_t)head * hd : nullptr;
         const float* nw = is_q ? p.pre.norm_q : p.pre.norm_k;
-        const float rn = nw ? s_rn[is_q ? head : p.n_head + head] : 1.f;
-        int i0, i1;
-        float x0, x1;
-        if (pp < n_rot / 2) {
-            rope_pair_index(p.rope.rope_type, pp, n_rot, i0, i1);
-            const float a = pre_value(src, bias, nw, rn, i0), c2 = pre_value(src, bias, nw, rn, i1);
-            x0 = a * s_cos[pp] - c2 * s_sin[pp];
-            x1 = a * s_sin[pp] + c2 * s_cos[pp];
-        } else {
-            i0 = n_rot + 2 * (pp - n_rot / 2);
-            i1 = i0 + 1;
-            x0 = pre_value(src, bias, nw, rn, i0);
-            x1 = pre_value(src, bias, nw, rn, i1);
-        }
+        const float rn = nw ? s_rn[row] : 1.f;
         if (is_q) {
             __half* dst = p.q16 + ((size_t)b * p.n_head + head) * hd;
-            dst[i0] = __float2half_rn(x0 * qs);
-            dst[i1] = __float2half_rn(x1 * qs);
+            rope_row_to_half(src, bias, nw, rn, hd, rope_q, p.rope, s_cos, s_sin, lane, 32,
+                             [&](int e, float v) { dst[e] = __float2half_rn(v * qs); });
         } else {
             uint16_t* dst = p.kc + ((size_t)head * p.n_ctx + pos) * hd;
-            dst[i0] = __half_as_ushort(__float2half_rn(x0));
-            dst[i1] = __half_as_ushort(__float2half_rn(x1));
+            rope_row_to_half(src, bias, nw, rn, hd, rope_k, p.rope, s_cos, s_sin, lane, 32,
+                             [&](int e, float v) { dst[e] = __half_as_ushort(__float2half_rn(v)); });
         }
     }
     if (append) {
-        for (int idx = tid; idx < p.n_kv * hd; idx += kPrologueThreads) {
-            const int head = idx / hd, i = idx % hd;
+        for (int head = warp; head < p.n_kv; head += kPrologueThreads / 32) {
+            const float* src = p.v_new + ((size_t)b * p.n_kv + head) * hd;
             const float* bv = p.pre.bias_v ? p.pre.bias_v + (size_t)head * hd : nullptr;
-            p.vc[((size_t)head * p.n_ctx + pos) * hd + i] =
-                __half_as_ushort(__float2half_rn(pre_value(p.v_new + ((size_t)b * p.n_kv + head) * hd, bv, nullptr, 1.f, i)));
+            uint16_t* dst = p.vc + ((size_t)head * p.n_ctx + pos) * hd;
+            for (int i = lane; i < hd; i += 32) dst[i] = __half_as_ushort(__float2half_rn(pre_value(src, bv, nullptr, 1.f, i)));
         }
     }
 }
