@@ -68,6 +68,22 @@ cudaError_t launch_combine_records(const float* parts, int n_parts, float* out, 
 cudaError_t launch_peer_wait_combine(const void* my_buf, int world, float* out, int n_head, int head_dim, int* gen_wait,
                                      int* status, int overlap, cudaStream_t stream, unsigned long long* launches);
 
+// Launch with (overlap != 0) or without the programmatic-stream-serialization attribute.
+template <typename Kernel, typename... Args>
+inline cudaError_t launch_dependent(Kernel kernel, dim3 grid, int threads, size_t smem, cudaStream_t stream, int overlap, const Args&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(threads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = overlap ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
 struct PrefillArgs {
     const float* q;        // [batch][n_head][hd] fp32
     const float* k_new;    // [batch][n_kv][hd] fp32 or nullptr

@@ -601,22 +601,6 @@ __global__ void __launch_bounds__(kPeerWaitThreads) peer_wait_combine_kernel(con
     if (threadIdx.x == 0) p.gen_wait[h] = g;
 }
 
-// Launch with (overlap != 0) or without the programmatic-stream-serialization attribute.
-template <typename Kernel, typename Args>
-cudaError_t launch_dependent(Kernel kernel, dim3 grid, int threads, size_t smem, cudaStream_t stream, int overlap, const Args& args) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
-    cfg.blockDim = dim3(threads);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = overlap ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, kernel, args);
-}
-
 template <int HD, bool WIDE>
 cudaError_t launch_split(const DecodeArgs& a, cudaStream_t stream) {
     return launch_dependent(decode_split_kernel<HD, WIDE>, dim3(a.n_splits, a.n_kv), kThreads, DecodeSmem<HD>::TOTAL, stream,

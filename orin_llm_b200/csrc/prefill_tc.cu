@@ -250,6 +250,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *s_tmem;
+    // Up to here only this CTA's shared memory and TMEM were touched, so with a programmatic dependent launch all of it
+    // overlaps the tail of the prologue kernel.  From here on the kernel reads what that kernel wrote (the fp16 queries,
+    // the appended K/V rows) and writes the output: wait for everything before it in the stream to complete.
+    pdl_trigger();
+    pdl_wait();
     const uint32_t TM_S = tmem, TM_O = tmem + NSB * BN;   // score buffer b at TM_S + 128 b, the accumulator behind them
 
     if (warp == 0) {
@@ -548,9 +553,9 @@ cudaError_t launch_prefill_tc(const PrefillArgs& a, int sm_count, cudaStream_t s
     t.status = a.status;
     t.n_head = a.n_head; t.n_kv = a.n_kv; t.n_past = a.n_past; t.batch = a.batch; t.G = G; t.TQ = TQ;
     dim3 grid((a.batch + TQ - 1) / TQ, a.n_kv);
-    prefill_tc_kernel<<<grid, kThreads, SMEM_BYTES, stream>>>(tmQ, tmK, tmV, t);
+    const cudaError_t e = launch_dependent(prefill_tc_kernel, grid, kThreads, SMEM_BYTES, stream, 1, tmQ, tmK, tmV, t);
     if (launches) *launches += 1;
-    return cudaGetLastError();
+    return e;
 }
 
 } // namespace oattn

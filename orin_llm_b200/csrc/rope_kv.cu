@@ -106,14 +106,19 @@ __global__ void __launch_bounds__(kPrologueThreads) prefill_prologue_kernel(cons
     const int b = blockIdx.x, tid = threadIdx.x;
     const int hd = p.head_dim, pos = p.n_past + b;
     const bool rope_q = (p.fuse & 1) != 0, rope_k = (p.fuse & 2) != 0, append = (p.fuse & 4) != 0;
-    if (b == 0 && tid == 0 && p.status) *p.status = 0;
+    // Programmatic dependent launch: the attention kernel of this call may start its set-up now, and the cos/sin table
+    // (arguments only) is made while the kernel before this one drains; inputs, scratch and cache are touched after
+    // the wait.
+    pdl_trigger();
     if (rope_q || rope_k) {
         for (int i = tid; i < p.rope.n_rot / 2; i += kPrologueThreads) {
             const float f = rope_freq(i, p.rope.n_rot, p.rope.theta, p.rope.freq_factors);
             rope_cs(pos, f, s_cos[i], s_sin[i]);
         }
-        __syncthreads();
     }
+    pdl_wait();
+    __syncthreads();
+    if (b == 0 && tid == 0 && p.status) *p.status = 0;
     // bias and per-head RMSNorm in front of the rotation (src/model_gpu.cu:372-377): 1/rms of every q and k head row
     __shared__ float s_rn[kPrologueMaxRows];
     if (p.pre.norm_q || p.pre.norm_k) {
@@ -191,9 +196,9 @@ cudaError_t launch_kv_shift(uint16_t* kc, uint16_t* vc, int n_layer, int n_kv, i
 }
 
 cudaError_t launch_prefill_prologue(const PrefillArgs& a, cudaStream_t stream, unsigned long long* launches) {
-    prefill_prologue_kernel<<<a.batch, kPrologueThreads, 0, stream>>>(a);
+    const cudaError_t e = launch_dependent(prefill_prologue_kernel, dim3(a.batch), kPrologueThreads, 0, stream, 1, a);
     if (launches) *launches += 1;
-    return cudaGetLastError();
+    return e;
 }
 
 } // namespace oattn
