@@ -82,6 +82,10 @@ def run(args):
         b200 = run_build(exe["e2e_b200"], model, tmp, "b200", args, forced)
         # the same binary with call-sequence fusion on: the four calls per layer run as the fused launches
         fused = run_build(exe["e2e_b200"], model, tmp, "b200f", args, forced, env={"OATTN_FUSE_CALL_SEQUENCE": "1"})
+        if args.overlap is not None:
+            ov = run_build(exe["e2e_b200"], model, tmp, "b200o", args, forced,
+                           env={"OATTN_FUSE_CALL_SEQUENCE": "1", "OATTN_DECODE_OVERLAP": str(args.overlap)})
+            out["b200_dropin_fused_sequence_overlap%d" % args.overlap] = timing(ov)
         out["reference_gpu"] = timing(ref)
         out["b200_dropin"] = timing(b200)
         out["b200_dropin_fused_sequence"] = timing(fused)
@@ -113,6 +117,8 @@ def parser():
     ap.add_argument("--cpu", action="store_true")
     ap.add_argument("--zerocopy", action="store_true")
     ap.add_argument("--no-warmup", action="store_true")
+    ap.add_argument("--overlap", type=int, default=None, choices=[0, 1, 2],
+                    help="also run the fused-sequence build with this decode launch ordering (OATTN_DECODE_OVERLAP)")
     ap.add_argument("--timeout", type=int, default=900)
     return ap
 

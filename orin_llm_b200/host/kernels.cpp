@@ -26,9 +26,16 @@ void check(int rc, const char* what);
 // Hosts that never call init()/attn_scratch_assign() (the reference's model_gpu.cu linked as it is) still work: the
 // first wrapper call initialises the current device; prefill scratch is allocated on demand (prefill is never
 // captured in a graph); decode falls back to the library's built-in scratch block.
+// OATTN_DECODE_OVERLAP=0|1|2 in the environment selects the decode launch ordering (oattn_set_decode_overlap).
+void apply_environment() {
+    const char* e = getenv("OATTN_DECODE_OVERLAP");
+    if (e && e[0] >= '0' && e[0] <= '2' && e[1] == 0) check(oattn_set_decode_overlap(e[0] - '0'), "OATTN_DECODE_OVERLAP");
+}
+
 void ensure_ready() {
     if (g_ready) return;
     check(oattn_init(-1), "init (on first use)");
+    apply_environment();
     g_ready = true;
 }
 
@@ -139,6 +146,7 @@ int init_device(int device) {
         fprintf(stderr, "[cuda::init] %s %s\n", oattn_strerror(rc), oattn_last_cuda_error());
         return -1;
     }
+    apply_environment();
     g_ready = true;
     return 0;
 }
