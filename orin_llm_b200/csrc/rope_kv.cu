@@ -135,35 +135,86 @@ __global__ void __launch_bounds__(kPrologueThreads) prefill_prologue_kernel(cons
         }
         __syncthreads();
     }
-    // One warp per head row (q rows first, then the k rows when they are appended): the lanes walk the row's rotation
-    // pairs, so consecutive lanes touch consecutive addresses and no index arithmetic beyond the pair index is needed.
+    // One warp per head row: the q rows, then (with the append) the k rows and the v rows.  The lanes walk the row's
+    // pairs, so consecutive lanes touch consecutive addresses.  A warp first loads the values of all its rows of a batch
+    // and only then rotates and stores them: sources and destinations may alias as far as the compiler can tell, so
+    // row-by-row code would pay one global round trip per row.
     const float qs = p.scale * LOG2E;
     const int warp = tid >> 5, lane = tid & 31;
-    const int rows = p.n_head + (append ? p.n_kv : 0);
-    for (int row = warp; row < rows; row += kPrologueThreads / 32) {
-        const bool is_q = row < p.n_head;
-        const int head = is_q ? row : row - p.n_head;
-        const float* src = is_q ? p.q + ((size_t)b * p.n_head + head) * hd : p.k_new + ((size_t)b * p.n_kv + head) * hd;
-        const float* bias0 = is_q ? p.pre.bias_q : p.pre.bias_k;
-        const float* bias = bias0 ? bias0 + (size_t)head * hd : nullptr;
-        const float* nw = is_q ? p.pre.norm_q : p.pre.norm_k;
-        const float rn = nw ? s_rn[row] : 1.f;
-        if (is_q) {
-            __half* dst = p.q16 + ((size_t)b * p.n_head + head) * hd;
-            rope_row_to_half(src, bias, nw, rn, hd, rope_q, p.rope, s_cos, s_sin, lane, 32,
-                             [&](int e, float v) { dst[e] = __float2half_rn(v * qs); });
+    const int half = hd / 2;
+    const int rows = p.n_head + (append ? 2 * p.n_kv : 0);
+    struct Row {
+        int kind, head, n_rot;          // kind 0 = q, 1 = k, 2 = v
+        const float* src; const float* bias; const float* nw; float rn;
+    };
+    auto describe = [&](int row) {
+        Row r;
+        r.kind = row < p.n_head ? 0 : (row < p.n_head + p.n_kv ? 1 : 2);
+        r.head = r.kind == 0 ? row : (r.kind == 1 ? row - p.n_head : row - p.n_head - p.n_kv);
+        const float* base = r.kind == 0 ? p.q : (r.kind == 1 ? p.k_new : p.v_new);
+        const int heads = r.kind == 0 ? p.n_head : p.n_kv;
+        r.src = base + ((size_t)b * heads + r.head) * hd;
+        const float* bias0 = r.kind == 0 ? p.pre.bias_q : (r.kind == 1 ? p.pre.bias_k : p.pre.bias_v);
+        r.bias = bias0 ? bias0 + (size_t)r.head * hd : nullptr;
+        r.nw = r.kind == 0 ? p.pre.norm_q : (r.kind == 1 ? p.pre.norm_k : nullptr);
+        r.rn = r.nw ? s_rn[row] : 1.f;
+        const bool rot = r.kind == 0 ? rope_q : (r.kind == 1 ? rope_k : false);
+        r.n_rot = rot ? p.rope.n_rot : 0;
+        return r;
+    };
+    auto pair_of = [&](const Row& r, int pp, int& i0, int& i1) {
+        if (pp < r.n_rot / 2) {
+            rope_pair_index(p.rope.rope_type, pp, r.n_rot, i0, i1);
         } else {
-            uint16_t* dst = p.kc + ((size_t)head * p.n_ctx + pos) * hd;
-            rope_row_to_half(src, bias, nw, rn, hd, rope_k, p.rope, s_cos, s_sin, lane, 32,
-                             [&](int e, float v) { dst[e] = __half_as_ushort(__float2half_rn(v)); });
+            i0 = r.n_rot + 2 * (pp - r.n_rot / 2);
+            i1 = i0 + 1;
         }
-    }
-    if (append) {
-        for (int head = warp; head < p.n_kv; head += kPrologueThreads / 32) {
-            const float* src = p.v_new + ((size_t)b * p.n_kv + head) * hd;
-            const float* bv = p.pre.bias_v ? p.pre.bias_v + (size_t)head * hd : nullptr;
-            uint16_t* dst = p.vc + ((size_t)head * p.n_ctx + pos) * hd;
-            for (int i = lane; i < hd; i += 32) dst[i] = __half_as_ushort(__float2half_rn(pre_value(src, bv, nullptr, 1.f, i)));
+    };
+    constexpr int RB = 6;            // rows in flight per warp (32 + 8 + 8 head rows over 8 warps)
+    constexpr int NW = kPrologueThreads / 32;
+    for (int r0 = warp; r0 < rows; r0 += NW * RB) {
+        float xa[RB][2], xb[RB][2];
+#pragma unroll
+        for (int u = 0; u < RB; ++u) {
+            const int row = r0 + u * NW;
+            if (row >= rows) continue;
+            const Row r = describe(row);
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int pp = lane + 32 * j;
+                if (pp >= half) continue;
+                int i0, i1;
+                pair_of(r, pp, i0, i1);
+                xa[u][j] = pre_value(r.src, r.bias, r.nw, r.rn, i0);
+                xb[u][j] = pre_value(r.src, r.bias, r.nw, r.rn, i1);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < RB; ++u) {
+            const int row = r0 + u * NW;
+            if (row >= rows) continue;
+            const Row r = describe(row);
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int pp = lane + 32 * j;
+                if (pp >= half) continue;
+                int i0, i1;
+                pair_of(r, pp, i0, i1);
+                float x0 = xa[u][j], x1 = xb[u][j];
+                if (pp < r.n_rot / 2) {
+                    x0 = xa[u][j] * s_cos[pp] - xb[u][j] * s_sin[pp];
+                    x1 = xa[u][j] * s_sin[pp] + xb[u][j] * s_cos[pp];
+                }
+                if (r.kind == 0) {
+                    __half* dst = p.q16 + ((size_t)b * p.n_head + r.head) * hd;
+                    dst[i0] = __float2half_rn(x0 * qs);
+                    dst[i1] = __float2half_rn(x1 * qs);
+                } else {
+                    uint16_t* dst = (r.kind == 1 ? p.kc : p.vc) + ((size_t)r.head * p.n_ctx + pos) * hd;
+                    dst[i0] = __half_as_ushort(__float2half_rn(x0));
+                    dst[i1] = __half_as_ushort(__float2half_rn(x1));
+                }
+            }
         }
     }
 }
