@@ -3,12 +3,14 @@
 The reference is single-device; this is the one multi-GPU step the path has.  The KV sequence of
 every kv head is cut into `world` contiguous slices, rank r keeping rows
 [bounds[r], bounds[r+1]) in its own HBM.  A decode step is
-    local partial (m, l, O) over the slice      oattn_decode_partial
-    all-gather of the world records             NCCL over NVLink (torch.distributed)
-    log-sum-exp combine on every rank           oattn_combine
-The record of one rank is [n_head][head_dim + 4] fp32 = {O, m, l, 0, 0}: 8448 bytes for 16 heads
-of 128, so the exchange is latency-bound; it is issued on the compute stream and is
-graph-capturable together with the two kernels.
+    local partial (m, l, O) over the slice       the split kernel
+    exchange of the world records                 [n_head][head_dim + 4] fp32 = {O, m, l, 0, 0} per rank
+    log-sum-exp merge on every rank
+The exchange is latency-bound (8448 bytes per rank for 16 heads of 128).  Two forms:
+    PeerSplitKVDecoder   the merge kernel stores its record into every rank's exchange buffer over NVLink (peer
+                         stores, every value tagged with the call's generation) and waits for the others' records
+                         in its own buffer: no collective call, two launches per step, graph-capturable
+    SplitKVDecoder       oattn_decode_partial -> NCCL all-gather (torch.distributed) -> oattn_combine
 
 The slicing and the gather are plain host logic that also runs on CPU tensors with the gloo
 backend (that is how they are tested without GPUs); the kernels are reached only through
