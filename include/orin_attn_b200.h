@@ -73,6 +73,14 @@ int oattn_init(int device);      /* device < 0: the calling thread's current dev
 /* Convenience for hosts without an arena of their own: `bytes` of device memory on the current device (cudaMalloc),
  * never freed by the library.  The one allocating entry point; nothing else in this interface calls it. */
 int oattn_scratch_alloc(size_t bytes, void** ptr);
+/* Returns a block obtained from oattn_scratch_alloc (cudaFree; NULL is accepted).  Synchronises the device as cudaFree
+ * does: never call it on a hot path or under stream capture. */
+int oattn_scratch_free(void* ptr);
+/* Address and size of the library's built-in scratch block on the current device (the block oattn_decode_noalloc
+ * uses, see there): lets a host that may not allocate pass it as the `workspace` of oattn_decode / oattn_decode_ex
+ * when oattn_decode_workspace_bytes() fits.  No allocation, no stream operation.  The same sharing rule applies: calls
+ * that use the block must not overlap on the GPU.  No counterpart in the reference. */
+int oattn_builtin_scratch(void** ptr, size_t* bytes);
 /* Number of SMs of the initialised device (0 before oattn_init). */
 int oattn_sm_count(void);
 
@@ -103,9 +111,11 @@ int oattn_kv_shift(uint16_t* kc, uint16_t* vc, int n_layer, int n_kv, int head_d
 
 /* ---- decode: one query token, split-KV flash decoding + log-sum-exp combine --------------- */
 
-/* Bytes of scratch the decode calls need for their per-split partial results (m, l, O).
+/* Bytes of scratch the decode calls need for their per-split and per-group partial results (m, l, O).
  * Follows the reference's scratch_size()/scratch_assign() pattern (src/kernels.cu:1753-1776):
- * the caller allocates once and passes the block on every call.  256-byte aligned. */
+ * the caller allocates once and passes the block on every call.  256-byte aligned; it need not be
+ * cleared (the arrival counters of the in-launch merge live inside the library, one set per
+ * workspace address).  Two calls that run on the GPU at the same time need two workspaces. */
 size_t oattn_decode_workspace_bytes(int n_head, int n_kv, int head_dim);
 
 /* Replaces the decode sequence rope_*_ind(q), rope_*_ind(k), kv_store_ind,
@@ -113,8 +123,9 @@ size_t oattn_decode_workspace_bytes(int n_head, int n_kv, int head_dim);
  * Attends q [n_head][head_dim] over cache rows 0..*d_pos.  With fuse == OATTN_FUSE_NONE it is
  * exactly flash_attention_decode_ind (k_new, v_new, rope may be NULL).  With fuse flags the new
  * token's K/V row (k_new, v_new: [n_kv][head_dim] fp32) is rotated, converted and stored at row
- * *d_pos inside the same launch.  Two launches: split kernel (grid fixed by n_kv and the SM
- * count) and combine kernel. */
+ * *d_pos inside the same launch.  ONE launch (grid fixed by n_kv and the SM count): the CTAs
+ * that finish last merge the per-split partials themselves (the cross-warp merge of
+ * src/kernels.cu:1280-1344 extended over CTAs).  q, k_new, v_new and out must be 16-byte aligned. */
 int oattn_decode(const float* q, const float* k_new, const float* v_new, uint16_t* kc, uint16_t* vc,
                  float* out, int n_head, int n_kv, int head_dim, int n_ctx, const int* d_pos, float scale,
                  int fuse, const oattn_rope_params* rope, void* workspace, size_t workspace_bytes, void* stream);
@@ -127,11 +138,12 @@ int oattn_decode(const float* q, const float* k_new, const float* v_new, uint16_
  * loads the library holds that block until the process ends.  Shapes whose partials do not fit
  * (n_head * splits * (head_dim + 2) * 4 bytes, splits = 2 * SMs / n_kv) are refused with OATTN_ERR_WORKSPACE and a
  * message in oattn_last_cuda_error(); nothing is allocated or freed, here or later.  The block's device address is
- * looked up by oattn_init (if a device was never initialised the first call does it; make that first call outside
- * any stream capture.  All calls on a device share the one block and it keeps what the previous call wrote: nothing
- * in it has to start at zero (each call overwrites the slots it later reads), but two calls that run on the GPU at
- * the same time -- different streams, or a graph replay overlapping an eager call -- would overwrite each other's
- * partials, so keep calls to this entry point ordered on one stream. */
+ * looked up by oattn_init; on a device that was never initialised the first call to this entry point runs
+ * oattn_init(-1) itself, so make that first call outside any stream capture.  All calls on a device share the one
+ * block and it keeps what the previous call wrote: nothing in it has to start at zero (each call overwrites the
+ * slots it later reads), but two calls that run on the GPU at the same time -- different streams, or a graph replay
+ * overlapping an eager call -- would overwrite each other's partials, so keep calls to this entry point ordered on
+ * one stream. */
 size_t oattn_decode_noalloc_max_bytes(void);
 int oattn_decode_noalloc(const float* q, const uint16_t* kc, const uint16_t* vc, float* out, int n_head, int n_kv,
                          int head_dim, int n_ctx, const int* d_pos, float scale, void* stream);
@@ -152,10 +164,11 @@ int oattn_combine(const float* parts, int n_parts, float* out, int n_head, int h
 
 /* ---- multi-GPU exchange without a collective call (no reference counterpart) ----------------------------------
  * The record exchange of split-KV decode is 8 KB per rank: latency-bound.  Instead of all-gather + combine, the
- * per-rank merge kernel stores its record straight into every rank's exchange buffer over NVLink (plain peer
- * stores).  Every fp32 value travels in one aligned 8-byte word together with the generation number of the call, so
- * the receiver needs neither a fence nor a flag: oattn_peer_wait_combine polls the words of its own buffer until
- * they carry the current generation (bounded, ~2 s, then a status word is set) and merges the `world` records.
+ * CTA that finishes a kv head's merge stores the record straight into every rank's exchange buffer over NVLink
+ * (plain peer stores).  Every fp32 value travels in one aligned 8-byte word together with the generation number of
+ * the call, so the receiver needs neither a fence nor a flag: it polls the words of its own buffer until they carry
+ * the current generation (bounded, ~2 s by default, see oattn_set_wait_limit_cycles; then a status word is set and the
+ * output is left untouched) and merges the `world` records.
  *   exchange buffer   oattn_peer_buffer_bytes(world, n_head, head_dim) bytes on every rank, peer-mapped (e.g. CUDA
  *                     VMM / torch symmetric memory), zero-filled before first use; `peer_bufs_dev` is a DEVICE array
  *                     of `world` pointers (entry r = rank r's buffer as seen from this GPU, own buffer included)
@@ -168,10 +181,10 @@ int oattn_decode_partial_push(const float* q, const uint16_t* kc, const uint16_t
                               int n_ctx, const int* d_len, float scale, void* workspace, size_t workspace_bytes,
                               const void* peer_bufs_dev, int rank, int world, void* state, void* stream);
 int oattn_peer_wait_combine(const void* my_buf, int world, float* out, int n_head, int head_dim, void* state, void* stream);
-/* Both steps in two launches instead of three: the merge launch that stores this rank's record into every exchange
- * buffer also waits for the other ranks' records and writes the merged out [n_head][head_dim].  Every rank must be
- * running on a GPU of its own (the launch waits for kernels of the other ranks); do not mix with the two calls above
- * on the same state block.  No counterpart in the reference. */
+/* Both steps in ONE launch instead of two: the CTA that stores this rank's record into every exchange buffer also
+ * waits for the other ranks' records and writes the merged out [n_head][head_dim].  Every rank must be running on a
+ * GPU of its own (the launch waits for kernels of the other ranks); do not mix with the two calls above on the same
+ * state block.  No counterpart in the reference. */
 int oattn_decode_peer(const float* q, const uint16_t* kc, const uint16_t* vc, float* out, int n_head, int n_kv, int head_dim,
                       int n_ctx, const int* d_len, float scale, void* workspace, size_t workspace_bytes,
                       const void* peer_bufs_dev, int rank, int world, void* state, void* stream);
@@ -186,6 +199,11 @@ int oattn_decode_peer_fused(const float* q, const float* k_new, const float* v_n
                             const void* peer_bufs_dev, int rank, int world, void* state, void* stream);
 /* Blocking read of the status word (0 = every wait so far was satisfied). */
 int oattn_peer_status(const void* state, int n_head, int* status);
+/* Bound of the device-side waits for the peers' records, in SM clock cycles (default 4e9, about two seconds; at least
+ * 1000).  When a wait runs out the kernel raises the status word, leaves the output untouched and returns, so the
+ * context stays usable; the next complete exchange works again.  Process-wide; applies to launches made after the
+ * call (a captured graph keeps the bound it was captured with). */
+int oattn_set_wait_limit_cycles(long long cycles);
 
 /* ---- the steps on either side of attention, folded into the same launches -------------------- */
 
@@ -250,23 +268,25 @@ int oattn_set_prefill_impl(int impl);
  *   0  (default) ordinary launches.
  *   1  programmatic dependent launches: a decode kernel may be scheduled while the preceding kernel of the
  *      stream drains, and waits for it to complete before it reads or writes anything.  Same results as 0.
- *   2  as 1, and the split kernel reads *d_pos and starts fetching cache rows below the valid length BEFORE that wait.
- *      The caller vouches that neither is written by the kernels launched on the stream since the previous
- *      non-decode launch (true for the reference's decode graph, src/model_gpu.cu:295-344: the position is copied in
- *      before the graph starts, every layer has its own cache, and other kernels run between two calls on one
- *      cache).  Do not use for back-to-back calls that append to the same cache.  Measured on B200: about 13 % more
- *      throughput for short contexts (1K to 4K rows), 4 % for 131072 rows per GPU on 8 GPUs, nothing for 1M rows on
- *      one GPU. */
+ *   2  as 1, and the kernel reads *d_pos and fetches its first cache tiles (rows below *d_pos) BEFORE that wait, so
+ *      that consecutive calls stream back to back.  The newest row (row *d_pos) is never taken from that early
+ *      fetch: it comes from k_new / v_new (fused append) or is re-read after the wait, so the reference's unfused
+ *      sequence rope, rope, kv_store_ind, flash_attention_decode_ind (src/model_gpu.cu:277-282) is safe.  The caller
+ *      vouches that the position word and the cache rows BELOW *d_pos are not written by the kernel launched just
+ *      before the call (true for the reference's decode graph, src/model_gpu.cu:295-344: the position is copied in
+ *      before the graph starts and every layer has its own cache).  Do not use for back-to-back calls on one
+ *      cache, e.g. a decode call right behind the prefill call that filled it. */
 int oattn_set_decode_overlap(int mode);
 
-/* Lower bound on the 64-row tiles one decode split handles (default 2): short contexts then
- * use fewer, fuller splits.  Process-wide tuning knob; must not change between the capture and
+/* Lower bound on the 64-row tiles one decode split handles (default 1).  Independently of it, contexts of up to 4
+ * tiles stay in one CTA per kv head and contexts of up to 64 tiles use at most 16 (one merge level).  Process-wide
+ * tuning knob; must not change between the capture and
  * the replays of a CUDA graph. */
 int oattn_set_decode_min_tiles(int tiles);
 
 /* Opt-in kernel timing for benchmarks (off by default; the hot calls allocate nothing either way:
  * the events are created here).  After oattn_profile_enable(n) every oattn_decode /
- * oattn_decode_partial call brackets its split-KV kernel (not the combine kernel) with a pair of
+ * oattn_decode_partial call brackets its kernel with a pair of
  * CUDA events on the call's stream, for the first n calls.  oattn_profile_collect waits for those
  * events, writes the elapsed milliseconds of each recorded call to ms (host, `capacity` floats),
  * stores the count in *n_written and rearms the counter.  oattn_profile_enable(0) destroys the

@@ -18,13 +18,13 @@ PART_PAD = 4
 
 # Every symbol include/orin_attn_b200.h declares.
 EXPORTS = [
-    "oattn_strerror", "oattn_last_cuda_error", "oattn_init", "oattn_scratch_alloc", "oattn_sm_count", "oattn_rope",
+    "oattn_strerror", "oattn_last_cuda_error", "oattn_init", "oattn_scratch_alloc", "oattn_scratch_free", "oattn_builtin_scratch", "oattn_sm_count", "oattn_rope",
     "oattn_kv_store", "oattn_kv_shift", "oattn_decode_workspace_bytes", "oattn_decode",
     "oattn_decode_ex", "oattn_prefill_ex", "oattn_decode_noalloc_max_bytes", "oattn_decode_noalloc",
     "oattn_decode_partial", "oattn_combine", "oattn_peer_buffer_bytes", "oattn_peer_state_bytes",
     "oattn_decode_partial_push", "oattn_peer_wait_combine", "oattn_decode_peer", "oattn_decode_peer_fused", "oattn_peer_status", "oattn_prefill_workspace_bytes", "oattn_prefill",
     "oattn_prefill_status",
-    "oattn_set_prefill_impl", "oattn_set_decode_min_tiles", "oattn_set_decode_overlap", "oattn_profile_enable", "oattn_profile_collect",
+    "oattn_set_prefill_impl", "oattn_set_decode_min_tiles", "oattn_set_decode_overlap", "oattn_set_wait_limit_cycles", "oattn_profile_enable", "oattn_profile_collect",
     "oattn_launch_count",
 ]
 
@@ -68,6 +68,8 @@ def lib():
     L.oattn_init.argtypes = [i]
     L.oattn_sm_count.argtypes = []
     L.oattn_scratch_alloc.argtypes = [sz, ctypes.POINTER(ctypes.c_void_p)]
+    L.oattn_scratch_free.argtypes = [vp]
+    L.oattn_builtin_scratch.argtypes = [ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(sz)]
     L.oattn_rope.argtypes = [vp, i, i, i, i, f, i, i, vp, vp, vp]
     L.oattn_kv_store.argtypes = [vp, vp, vp, vp, i, i, i, i, i, vp, vp]
     L.oattn_kv_shift.argtypes = [vp, vp, i, i, i, i, i, i, vp]
@@ -98,6 +100,7 @@ def lib():
     L.oattn_set_prefill_impl.argtypes = [i]
     L.oattn_set_decode_min_tiles.argtypes = [i]
     L.oattn_set_decode_overlap.argtypes = [i]
+    L.oattn_set_wait_limit_cycles.argtypes = [ctypes.c_longlong]
     L.oattn_profile_enable.argtypes = [i]
     L.oattn_profile_collect.argtypes = [ctypes.POINTER(ctypes.c_float), i, ctypes.POINTER(ctypes.c_int)]
     L.oattn_launch_count.restype = ctypes.c_ulonglong

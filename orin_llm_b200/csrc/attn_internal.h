@@ -22,6 +22,34 @@ __host__ __device__ inline size_t peer_buffer_bytes(int world, int n_head, int h
     return (rec + 255) & ~(size_t)255;
 }
 
+// Splits per first-level merge group of the decode kernel: about sqrt(n_splits), so that both levels of the merge
+// tree are one pass (at most 16 partials) for up to 256 splits.
+inline int decode_group_size(int n_splits) {
+    int g = 2;
+    while (g * g < n_splits && g < 16) ++g;
+    return g;
+}
+
+// Decode scratch (caller-owned): the un-normalised partial of every split, [n_kv][n_splits][G][hd] fp32 and
+// [n_kv][n_splits][G][2] (m in raw-score units, l), and the same for every group of `group` neighbouring splits.
+struct DecodeWsLayout {
+    size_t part_o, part_ml, grp_o, grp_ml, total;   // byte offsets, 256-byte aligned
+    int n_splits, group, n_groups;
+};
+inline DecodeWsLayout decode_ws_layout(int n_head, int n_kv, int head_dim, int n_splits) {
+    auto al = [](size_t v) { return (v + 255) & ~(size_t)255; };
+    DecodeWsLayout w;
+    w.n_splits = n_splits;
+    w.group = decode_group_size(n_splits);
+    w.n_groups = (n_splits + w.group - 1) / w.group;
+    w.part_o = 0;
+    w.part_ml = w.part_o + al((size_t)n_head * n_splits * head_dim * sizeof(float));
+    w.grp_o = w.part_ml + al((size_t)n_head * n_splits * 2 * sizeof(float));
+    w.grp_ml = w.grp_o + al((size_t)n_head * w.n_groups * head_dim * sizeof(float));
+    w.total = w.grp_ml + al((size_t)n_head * w.n_groups * 2 * sizeof(float));
+    return w;
+}
+
 struct DecodeArgs {
     const float* q;        // [n_head][hd] fp32
     const float* k_new;    // [n_kv][hd] fp32 or nullptr
@@ -29,15 +57,18 @@ struct DecodeArgs {
     uint16_t* kc;          // [n_kv][n_ctx][hd] fp16 bits
     uint16_t* vc;
     float* out;            // [n_head][hd] (final) or [n_head][hd+PART_PAD] (partial record)
-    float* ws_o;           // [n_head][n_splits][hd]
-    float* ws_ml;          // [n_head][n_splits][2]  (m in natural-log units of the scaled score, l)
+    float* ws_o;           // scratch, see DecodeWsLayout
+    float* ws_ml;
+    float* grp_o;
+    float* grp_ml;
+    unsigned* tickets;     // arrival counters: [n_kv][n_groups] first level, then [n_kv] second level; zero at rest
     const int* d_pos;      // device scalar
     int pos_bias;          // valid rows = *d_pos + pos_bias  (1: d_pos is the new token's position; 0: d_pos is a length)
-    int n_head, n_kv, head_dim, n_ctx, n_splits, min_tiles;
+    int n_head, n_kv, head_dim, n_ctx, n_splits, group, n_groups, min_tiles;
     float scale;
     int fuse;
     RopeArgs rope;
-    int emit_partial;      // combine writes the un-normalised record instead of the normalised output
+    int emit_partial;      // write the un-normalised record instead of the normalised output
     PreArgs pre;                   // optional bias / per-head RMSNorm in front of RoPE
     const int* d_rope_pos = nullptr;   // position used for RoPE when it is not the local row index (sharded cache)
     int8_t* out_qs = nullptr;      // optional q8_1 form of the output: int8 [n_head*hd] ...
@@ -45,20 +76,26 @@ struct DecodeArgs {
     const unsigned long long* peer_bufs = nullptr;   // multi-GPU peer exchange: device array of `world` buffer pointers
     int* gen_push = nullptr;                          // [n_head] generation counters (private to this rank)
     int rank = 0, world = 1;
-    int overlap = 0;                                  // 0 plain launches, 1 dependent launches, 2 + K/V prefetch before the wait
-    int fused_wait = 0;                               // the merge launch also waits for every rank's record and writes `out`
+    int overlap = 0;                                  // 0 plain launch, 1 dependent launch, 2 + K/V prefetch before the wait
+    int fused_wait = 0;                               // also wait for every rank's record and write the merged `out`
     int* peer_status = nullptr;                       // raised when that wait ran out
+    long long wait_cycles = 4000000000LL;             // bound of that wait, in SM clock cycles
 };
 
 // Size of the scratch block built into the library for oattn_decode_noalloc, and its device address on the
 // current device (looked up once per device).
 constexpr size_t kStaticScratchBytes = 2u << 20;
 cudaError_t decode_static_scratch(void** ptr);
+// Arrival counters for the decode launches that use `workspace` on the current device: a slot of a zero-initialised
+// table inside the library image (one slot per distinct workspace address, least recently used slot recycled).
+constexpr int kTicketSlots = 64;
+constexpr int kTicketWords = 512;
+cudaError_t decode_ticket_slot(const void* workspace, unsigned** tickets);
 
 // Number of KV splits per kv head the decode launch uses on a device with `sm_count` SMs.
 int decode_num_splits(int n_kv, int sm_count);
 cudaError_t decode_set_attributes();
-// ev_start / ev_stop (optional) are recorded around the split kernel only.
+// One launch; ev_start / ev_stop (optional) are recorded around it.
 cudaError_t launch_decode(const DecodeArgs& a, cudaStream_t stream, unsigned long long* launches,
                           cudaEvent_t ev_start = nullptr, cudaEvent_t ev_stop = nullptr);
 // Merge n_parts records [n_parts][n_head][hd+PART_PAD] -> out [n_head][hd].
@@ -66,7 +103,8 @@ cudaError_t launch_combine_records(const float* parts, int n_parts, float* out, 
                                    cudaStream_t stream, unsigned long long* launches);
 
 cudaError_t launch_peer_wait_combine(const void* my_buf, int world, float* out, int n_head, int head_dim, int* gen_wait,
-                                     int* status, int overlap, cudaStream_t stream, unsigned long long* launches);
+                                     int* status, long long wait_cycles, int overlap, cudaStream_t stream,
+                                     unsigned long long* launches);
 
 // Launch with (overlap != 0) or without the programmatic-stream-serialization attribute.
 template <typename Kernel, typename... Args>

@@ -15,12 +15,12 @@ struct DeviceState {
     int sm_count = 0;
 };
 DeviceState g_dev[kMaxDevices];
-int g_cur = -1;                       // device of the last oattn_init
 int g_prefill_impl = 0;               // 0 = tcgen05, 1 = mma.sync
-int g_decode_min_tiles = 2;
+int g_decode_min_tiles = 1;
 int g_decode_overlap = 0;
+long long g_wait_cycles = 4000000000LL;   // bound of the device-side waits for peers' records (about two seconds)
 unsigned long long g_launches = 0;
-char g_cuda_err[256] = "";
+thread_local char g_cuda_err[256] = "";
 
 // opt-in timing of the split-KV kernel (oattn_profile_enable)
 cudaEvent_t* g_prof_ev = nullptr;   // 2 * g_prof_cap events: start, stop per record
@@ -55,19 +55,16 @@ int check_rope(int fuse, const oattn_rope_params* rope, int head_dim, RopeArgs& 
     return OATTN_OK;
 }
 
-bool device_ready() { return g_cur >= 0 && g_dev[g_cur].ready; }
+// State of the calling thread's current device, or nullptr before oattn_init() succeeded on it.
+const DeviceState* cur_dev() {
+    int d = -1;
+    if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= kMaxDevices) return nullptr;
+    return g_dev[d].ready ? &g_dev[d] : nullptr;
+}
+bool device_ready() { return cur_dev() != nullptr; }
 
-struct DecodeWs {
-    size_t o_bytes, ml_bytes, total;
-    int n_splits;
-};
-DecodeWs decode_ws(int n_head, int n_kv, int head_dim, int sm_count) {
-    DecodeWs w;
-    w.n_splits = decode_num_splits(n_kv, sm_count);
-    w.o_bytes = align256((size_t)n_head * w.n_splits * head_dim * sizeof(float));
-    w.ml_bytes = align256((size_t)n_head * w.n_splits * 2 * sizeof(float));
-    w.total = w.o_bytes + w.ml_bytes;
-    return w;
+DecodeWsLayout decode_ws(int n_head, int n_kv, int head_dim, int sm_count) {
+    return decode_ws_layout(n_head, n_kv, head_dim, decode_num_splits(n_kv, sm_count));
 }
 
 } // namespace
@@ -106,10 +103,11 @@ int oattn_init(int device) {
         if ((e = prefill_tc_set_attributes()) != cudaSuccess) return cuda_fail(e, "prefill (tcgen05) attributes");
         void* scratch = nullptr;      // look the built-in scratch block up now, so that oattn_decode_noalloc never has to
         if ((e = decode_static_scratch(&scratch)) != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(built-in scratch)");
+        unsigned* tickets = nullptr;  // ... and the arrival counters of the decode launches
+        if ((e = decode_ticket_slot(nullptr, &tickets)) != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(arrival counters)");
         g_dev[device].sm_count = sms;
         g_dev[device].ready = true;
     }
-    g_cur = device;
     return OATTN_OK;
 }
 
@@ -120,7 +118,22 @@ int oattn_scratch_alloc(size_t bytes, void** ptr) {
     return e == cudaSuccess ? OATTN_OK : cuda_fail(e, "cudaMalloc(scratch)");
 }
 
-int oattn_sm_count(void) { return device_ready() ? g_dev[g_cur].sm_count : 0; }
+int oattn_scratch_free(void* ptr) {
+    if (!ptr) return OATTN_OK;
+    cudaError_t e = cudaFree(ptr);
+    return e == cudaSuccess ? OATTN_OK : cuda_fail(e, "cudaFree(scratch)");
+}
+
+int oattn_builtin_scratch(void** ptr, size_t* bytes) {
+    if (!ptr || !bytes) return OATTN_ERR_ARG;
+    if (!device_ready()) return OATTN_ERR_DEVICE;
+    cudaError_t e = decode_static_scratch(ptr);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(built-in scratch)");
+    *bytes = kStaticScratchBytes;
+    return OATTN_OK;
+}
+
+int oattn_sm_count(void) { const DeviceState* d = cur_dev(); return d ? d->sm_count : 0; }
 
 int oattn_rope(float* x, int rows, int head_dim, int rope_type, int n_rot, float theta, int n_past, int heads,
                const int* d_pos, const float* freq_factors, void* stream) {
@@ -155,8 +168,9 @@ int oattn_kv_shift(uint16_t* kc, uint16_t* vc, int n_layer, int n_kv, int head_d
 }
 
 size_t oattn_decode_workspace_bytes(int n_head, int n_kv, int head_dim) {
-    if (!device_ready() || check_shape(n_head, n_kv, head_dim) != OATTN_OK) return 0;
-    return decode_ws(n_head, n_kv, head_dim, g_dev[g_cur].sm_count).total;
+    const DeviceState* d = cur_dev();
+    if (!d || check_shape(n_head, n_kv, head_dim) != OATTN_OK) return 0;
+    return decode_ws(n_head, n_kv, head_dim, d->sm_count).total;
 }
 
 struct PeerTarget {
@@ -189,25 +203,36 @@ static int decode_common(const float* q, const float* k_new, const float* v_new,
                          int n_head, int n_kv, int head_dim, int n_ctx, const int* d_pos, int pos_bias, float scale,
                          int fuse, const oattn_rope_params* rope, int emit_partial, void* workspace, size_t workspace_bytes,
                          void* stream, const PeerTarget* peer = nullptr, const oattn_ext* ext = nullptr) {
-    if (!device_ready()) return OATTN_ERR_DEVICE;
+    const DeviceState* dev = cur_dev();
+    if (!dev) return OATTN_ERR_DEVICE;
     int rc = check_shape(n_head, n_kv, head_dim);
     if (rc != OATTN_OK) return rc;
     const bool q8_only = ext && ext->out_qs && !emit_partial;     // the fp32 output is optional next to the q8_1 one
     if (!q || !kc || !vc || (!out && !q8_only) || !d_pos || n_ctx <= 0 || !(scale > 0.0f)) return OATTN_ERR_ARG;
+    // q, k_new, v_new and the biases are read, out is written, as float4
+    if (((uintptr_t)out | (uintptr_t)q | (uintptr_t)k_new | (uintptr_t)v_new) & 15) return OATTN_ERR_ARG;
+    if (ext && (((uintptr_t)ext->bias_q | (uintptr_t)ext->bias_k | (uintptr_t)ext->bias_v) & 15)) return OATTN_ERR_ARG;
     if (fuse & ~OATTN_FUSE_ALL) return OATTN_ERR_ARG;
     if ((fuse & OATTN_FUSE_ROPE_K) && !(fuse & OATTN_FUSE_KV_APPEND)) return OATTN_ERR_ARG;
     if ((fuse & OATTN_FUSE_KV_APPEND) && (!k_new || !v_new)) return OATTN_ERR_ARG;
     DecodeArgs a;
     if ((rc = check_rope(fuse, rope, head_dim, a.rope)) != OATTN_OK) return rc;
     if ((rc = apply_ext(ext, fuse, !emit_partial, n_head, n_kv, a.pre, &a.out_qs, &a.out_scales)) != OATTN_OK) return rc;
-    const DecodeWs w = decode_ws(n_head, n_kv, head_dim, g_dev[g_cur].sm_count);
+    const DecodeWsLayout w = decode_ws(n_head, n_kv, head_dim, dev->sm_count);
     if (!workspace || ((uintptr_t)workspace & 255) || workspace_bytes < w.total) return OATTN_ERR_WORKSPACE;
+    if ((size_t)n_kv * (w.n_groups + 1) > (size_t)kTicketWords) return OATTN_ERR_UNSUPPORTED;
     a.q = q; a.k_new = k_new; a.v_new = v_new; a.kc = kc; a.vc = vc; a.out = out;
-    a.ws_o = reinterpret_cast<float*>(workspace);
-    a.ws_ml = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + w.o_bytes);
+    uint8_t* wsb = reinterpret_cast<uint8_t*>(workspace);
+    a.ws_o = reinterpret_cast<float*>(wsb + w.part_o);
+    a.ws_ml = reinterpret_cast<float*>(wsb + w.part_ml);
+    a.grp_o = reinterpret_cast<float*>(wsb + w.grp_o);
+    a.grp_ml = reinterpret_cast<float*>(wsb + w.grp_ml);
+    cudaError_t te = decode_ticket_slot(workspace, &a.tickets);
+    if (te != cudaSuccess) return cuda_fail(te, "arrival counters");
     a.d_pos = d_pos; a.pos_bias = pos_bias;
     a.n_head = n_head; a.n_kv = n_kv; a.head_dim = head_dim; a.n_ctx = n_ctx;
-    a.n_splits = w.n_splits; a.min_tiles = g_decode_min_tiles; a.overlap = g_decode_overlap;
+    a.n_splits = w.n_splits; a.group = w.group; a.n_groups = w.n_groups; a.min_tiles = g_decode_min_tiles; a.overlap = g_decode_overlap;
+    a.wait_cycles = g_wait_cycles;
     a.scale = scale; a.fuse = fuse; a.emit_partial = emit_partial;
     if (peer) { a.peer_bufs = peer->bufs; a.gen_push = peer->gen_push; a.rank = peer->rank; a.world = peer->world;
                 a.fused_wait = peer->fused_wait; a.peer_status = peer->status; a.d_rope_pos = peer->rope_pos; }
@@ -239,10 +264,14 @@ size_t oattn_decode_noalloc_max_bytes(void) { return kStaticScratchBytes; }
 
 int oattn_decode_noalloc(const float* q, const uint16_t* kc, const uint16_t* vc, float* out, int n_head, int n_kv,
                          int head_dim, int n_ctx, const int* d_pos, float scale, void* stream) {
-    if (!device_ready()) return OATTN_ERR_DEVICE;
+    if (!device_ready()) {
+        // first use on this device: set it up here (address look-ups, kernel attributes); keep it out of stream capture
+        const int irc = oattn_init(-1);
+        if (irc != OATTN_OK) return irc;
+    }
     int rc = check_shape(n_head, n_kv, head_dim);
     if (rc != OATTN_OK) return rc;
-    const DecodeWs w = decode_ws(n_head, n_kv, head_dim, g_dev[g_cur].sm_count);
+    const DecodeWsLayout w = decode_ws(n_head, n_kv, head_dim, cur_dev()->sm_count);
     if (w.total > kStaticScratchBytes) {
         snprintf(g_cuda_err, sizeof(g_cuda_err),
                  "oattn_decode_noalloc: this shape needs %zu bytes of scratch, the built-in block holds %zu; use oattn_decode "
@@ -250,7 +279,7 @@ int oattn_decode_noalloc(const float* q, const uint16_t* kc, const uint16_t* vc,
         return OATTN_ERR_WORKSPACE;
     }
     void* scratch = nullptr;
-    cudaError_t e = decode_static_scratch(&scratch);     // first call on a device looks the address up
+    cudaError_t e = decode_static_scratch(&scratch);     // the address oattn_init looked up for this device
     if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(built-in scratch)");
     return decode_common(q, nullptr, nullptr, const_cast<uint16_t*>(kc), const_cast<uint16_t*>(vc), out, n_head, n_kv,
                          head_dim, n_ctx, d_pos, 1, scale, OATTN_FUSE_NONE, nullptr, 0, scratch, w.total, stream);
@@ -323,8 +352,9 @@ int oattn_peer_wait_combine(const void* my_buf, int world, float* out, int n_hea
     if (!my_buf || !out || !state || n_head <= 0 || world < 1 || world > DECODE_MAX_RANKS) return OATTN_ERR_ARG;
     if (head_dim != 64 && head_dim != 128) return OATTN_ERR_UNSUPPORTED;
     int* st = reinterpret_cast<int*>(state);
+    if ((uintptr_t)out & 15) return OATTN_ERR_ARG;
     cudaError_t e = launch_peer_wait_combine(my_buf, world, out, n_head, head_dim, st + n_head, st + 2 * n_head,
-                                             g_decode_overlap, (cudaStream_t)stream, &g_launches);
+                                             g_wait_cycles, g_decode_overlap, (cudaStream_t)stream, &g_launches);
     return e == cudaSuccess ? OATTN_OK : cuda_fail(e, "peer wait/combine launch");
 }
 
@@ -339,7 +369,7 @@ int oattn_combine(const float* parts, int n_parts, float* out, int n_head, int h
     if (!parts || !out || n_head <= 0 || n_parts <= 0) return OATTN_ERR_ARG;
     if (head_dim != 64 && head_dim != 128) return OATTN_ERR_UNSUPPORTED;
     if (n_parts > DECODE_MAX_SPLITS) return OATTN_ERR_UNSUPPORTED;
-    if ((uintptr_t)parts & 15) return OATTN_ERR_ARG;
+    if (((uintptr_t)parts & 15) || ((uintptr_t)out & 15)) return OATTN_ERR_ARG;
     cudaError_t e = launch_combine_records(parts, n_parts, out, n_head, head_dim, (cudaStream_t)stream, &g_launches);
     return e == cudaSuccess ? OATTN_OK : cuda_fail(e, "combine launch");
 }
@@ -367,7 +397,8 @@ int oattn_prefill_ex(const float* q, const float* k_new, const float* v_new, uin
                      int n_head, int n_kv, int head_dim, int n_ctx, int n_past, int batch, float scale, int fuse,
                      const oattn_rope_params* rope, const oattn_ext* ext, void* workspace, size_t workspace_bytes,
                      void* stream) {
-    if (!device_ready()) return OATTN_ERR_DEVICE;
+    const DeviceState* dev = cur_dev();
+    if (!dev) return OATTN_ERR_DEVICE;
     int rc = check_shape(n_head, n_kv, head_dim);
     if (rc != OATTN_OK) return rc;
     if (!q || !kc || !vc || !out || n_ctx <= 0 || !(scale > 0.0f)) return OATTN_ERR_ARG;
@@ -389,7 +420,7 @@ int oattn_prefill_ex(const float* q, const float* k_new, const float* v_new, uin
     cudaError_t e = launch_prefill_prologue(a, s, &g_launches);
     if (e != cudaSuccess) return cuda_fail(e, "prefill prologue launch");
     if (g_prefill_impl == 0) {
-        e = launch_prefill_tc(a, g_dev[g_cur].sm_count, s, &g_launches);
+        e = launch_prefill_tc(a, dev->sm_count, s, &g_launches);
         if (e == cudaSuccess) return OATTN_OK;
         if (e != cudaErrorNotSupported) return cuda_fail(e, "prefill (tcgen05) launch");
     }
@@ -406,6 +437,12 @@ int oattn_set_prefill_impl(int impl) {
 int oattn_set_decode_overlap(int mode) {
     if (mode < 0 || mode > 2) return OATTN_ERR_ARG;
     g_decode_overlap = mode;
+    return OATTN_OK;
+}
+
+int oattn_set_wait_limit_cycles(long long cycles) {
+    if (cycles < 1000) return OATTN_ERR_ARG;
+    g_wait_cycles = cycles;
     return OATTN_OK;
 }
 

@@ -1,4 +1,4 @@
-// Single-token decode attention over the fp16 KV cache: split-KV flash decoding.
+// Single-token decode attention over the fp16 KV cache: split-KV flash decoding in ONE launch.
 //
 // Stands in for flash_attention_decode_mma_k (src/kernels.cu:1107-1345), which walks the whole
 // sequence with one CTA per kv head.  Here the sequence of every kv head is cut into
@@ -11,14 +11,25 @@
 // cp.async copies, three stages deep; rows at or past the valid length are zero-filled by the
 // copy itself.  Warp w owns rows 16w..16w+15 of every tile: S = Q K^T with the (padded to 16)
 // query heads of the group as the M dimension of mma.m16n8k16, online softmax in fp32 with
-// quad shuffles for max and sum, O += P V with V fragments taken by ldmatrix.trans.  The four
-// warps' (m, l, O) are merged through shared memory, and the CTA writes one partial per head.
-// A second small kernel merges the partials of all slices (log-sum-exp combine).
+// quad shuffles for max and sum, O += P V with V fragments taken by ldmatrix.trans.
+//
+// Merge, all inside the launch (the reference merges its four warps the same way,
+// src/kernels.cu:1280-1344; here the tree has two more levels): the four warps' (m, l, O) are
+// merged through shared memory into the CTA's partial; the CTA stores it and draws an arrival
+// ticket for its group of about sqrt(n_splits) neighbouring splits; whoever draws a group's last ticket merges the
+// group's partials, stores the result and draws a ticket of the kv head; the last of those
+// merges the groups and writes the output (or the per-rank record of the multi-GPU path, which
+// it can also push to the peers and merge with theirs).  Nobody waits for anybody: a CTA that is
+// not last simply leaves.  Partials are always merged in index order, so the result does not
+// depend on who arrives last.  The counters wrap to zero on the last ticket (atomicInc), which
+// keeps a captured launch replayable.
 //
 // Optional fused prologue: RoPE of q, RoPE + fp16 conversion + cache store of the new token's
 // k/v row (rope_*_ind, kv_store_ind of src/model_gpu.cu:277-281).  The CTA whose slice contains
 // the new row stores it and patches it into its own shared-memory tile, so no CTA ever reads a
 // row another CTA is writing.
+#include <mutex>
+
 #include "attn_internal.h"
 
 namespace oattn {
@@ -39,9 +50,13 @@ struct DecodeSmem {
     static constexpr int KNEW_OFF = Q_OFF + Q_BYTES;
     static constexpr int VNEW_OFF = KNEW_OFF + ROWB;
     static constexpr int CS_OFF = VNEW_OFF + ROWB;        // cos[HD/2], sin[HD/2] fp32
-    static constexpr int TOTAL = CS_OFF + HD * 4;
-    // merge buffers alias the stage area once the pipeline has drained
-    static constexpr int MERGE_O_BYTES = 4 * 16 * HD * 4;
+    static constexpr int IN_OFF = CS_OFF + HD * 4;        // fp32 staging of q (16 rows), k_new, v_new (+ their biases)
+    static constexpr int IN_ROWS = 18;
+    static constexpr int TOTAL = IN_OFF + IN_ROWS * HD * 4;
+    // merge buffers alias the stage area once the pipeline has drained: [4 warps][16 rows][HD + 8] fp32 (the 8
+    // floats of padding spread the rows over the banks) and [4][16][2] for (m, l)
+    static constexpr int MERGE_STRIDE = HD + 8;
+    static constexpr int MERGE_O_BYTES = 4 * 16 * MERGE_STRIDE * 4;
     static constexpr int MERGE_ML_OFF = MERGE_O_BYTES;
     static_assert(MERGE_O_BYTES + 4 * 16 * 2 * 4 <= kStages * STAGE_BYTES, "merge area must fit in the stage area");
 };
@@ -55,6 +70,10 @@ __host__ __device__ inline SplitPlan plan_splits(int npos, int n_splits, int min
     s.n_tiles = (npos + DECODE_TILE - 1) / DECODE_TILE;
     int tps = (s.n_tiles + n_splits - 1) / n_splits;
     if (tps < min_tiles) tps = min_tiles;
+    // short contexts are latency-bound: up to 4 tiles stay in one CTA (no merge across CTAs at all), up to 64 tiles
+    // use at most 16 CTAs per kv head (one merge level instead of two)
+    if (s.n_tiles <= 4) { if (tps < s.n_tiles) tps = s.n_tiles; }
+    else if (s.n_tiles <= 64) { if (tps < (s.n_tiles + 15) / 16) tps = (s.n_tiles + 15) / 16; }
     if (tps < 1) tps = 1;
     s.tiles_per_split = tps;
     s.active = (s.n_tiles + tps - 1) / tps;
@@ -63,32 +82,338 @@ __host__ __device__ inline SplitPlan plan_splits(int npos, int n_splits, int min
 
 __device__ __forceinline__ int clamp_len(int v, int n_ctx) { return v < 0 ? 0 : (v > n_ctx ? n_ctx : v); }
 
+// ---- how the threads of a CTA share one kv head's [G][HD] block of fp32 values ------------------------------------
+// The block is cut into float4 pieces; thread `tid` owns pieces tid, tid + 128, ... (piece -> row = head in the group,
+// col4 = which four dims).  With HD = 128 a warp owns whole rows (rows warp, warp + 4, ...), a lane four dims.
+template <int HD, bool WIDE>
+struct Slots {
+    static constexpr int F4_PER_ROW = HD / 4;
+    static constexpr int ROWS = WIDE ? 16 : 8;
+    static constexpr int N = ROWS * F4_PER_ROW / kThreads;
+    static_assert(N >= 1, "at least one piece per thread");
+    __device__ static __forceinline__ int row(int tid, int k) { return (tid + k * kThreads) / F4_PER_ROW; }
+    __device__ static __forceinline__ int col4(int tid, int k) { return (tid + k * kThreads) % F4_PER_ROW; }
+};
+
+// Running log-sum-exp merge of one piece: acc = sum_i e^(m_i - M) O_i, L = sum_i e^(m_i - M) l_i, M = max m_i.
+struct RunState {
+    float M, L;
+    float4 acc;
+};
+__device__ __forceinline__ RunState run_empty() { return RunState{-CUDART_INF_F, 0.f, make_float4(0.f, 0.f, 0.f, 0.f)}; }
+
+// Adds n <= 8 parts; c turns a difference of m values into a base-2 exponent.
+__device__ __forceinline__ void run_add(RunState& s, const float (&m)[8], const float (&l)[8], const float4 (&o)[8], int n, float c) {
+    float mx = s.M;
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+        if (i < n) mx = fmaxf(mx, m[i]);
+    if (mx == -CUDART_INF_F) return;           // only empty parts so far
+    const float a = (s.M == -CUDART_INF_F) ? 0.f : fast_exp2((s.M - mx) * c);
+    s.L *= a;
+    s.acc.x *= a; s.acc.y *= a; s.acc.z *= a; s.acc.w *= a;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        if (i < n) {
+            const float w = (m[i] == -CUDART_INF_F) ? 0.f : fast_exp2((m[i] - mx) * c);
+            s.L = fmaf(w, l[i], s.L);
+            s.acc.x = fmaf(w, o[i].x, s.acc.x);
+            s.acc.y = fmaf(w, o[i].y, s.acc.y);
+            s.acc.z = fmaf(w, o[i].z, s.acc.z);
+            s.acc.w = fmaf(w, o[i].w, s.acc.w);
+        }
+    }
+    s.M = mx;
+}
+
+// Merges parts 0..n-1 of one kv head, stored [part][G][HD] and [part][G][2], in index order.  The parts were written by
+// other SMs a moment ago: read them from L2 (ld.cg), never through this SM's L1.  This runs on the critical path of the
+// launch as a chain of L2 round trips, so a pass issues every load it needs before it uses any of them: the lanes that
+// share a row (HD/4 of them) each fetch the (m, l) of one part and exchange the weights by shuffle, and every lane keeps
+// its O pieces of up to 16 parts in flight.  Called by all threads of the CTA.
+template <int HD, bool WIDE>
+__device__ __forceinline__ void merge_parts(const float* o_base, const float* ml_base, int n, int G, float c,
+                                            RunState (&st)[Slots<HD, WIDE>::N]) {
+    using S = Slots<HD, WIDE>;
+    constexpr int LPR = S::F4_PER_ROW;            // lanes per row: 32 or 16
+    constexpr int PASS = 16;                      // parts per pass
+    constexpr int KB = S::N < 2 ? S::N : 2;       // pieces per thread handled together
+    const int tid = threadIdx.x;
+    const int j = tid % LPR;
+#pragma unroll
+    for (int k = 0; k < S::N; ++k) st[k] = run_empty();
+    for (int i0 = 0; i0 < n; i0 += PASS) {
+        const int nn = min(PASS, n - i0);
+#pragma unroll
+        for (int k0 = 0; k0 < S::N; k0 += KB) {
+            float2 ml[KB];
+            float4 o[KB][PASS];
+#pragma unroll
+            for (int kk = 0; kk < KB; ++kk) {
+                const int row = S::row(tid, k0 + kk), c4 = S::col4(tid, k0 + kk);
+                const bool valid = row < G;
+                ml[kk] = make_float2(-CUDART_INF_F, 0.f);
+                if (valid && j < nn) ml[kk] = __ldcg(reinterpret_cast<const float2*>(ml_base + ((size_t)(i0 + j) * G + row) * 2));
+#pragma unroll
+                for (int i = 0; i < PASS; ++i) {
+                    o[kk][i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (valid && i < nn) o[kk][i] = __ldcg(reinterpret_cast<const float4*>(o_base + ((size_t)(i0 + i) * G + row) * HD + c4 * 4));
+                }
+            }
+#pragma unroll
+            for (int kk = 0; kk < KB; ++kk) {
+                RunState& r = st[k0 + kk];
+                float mx = ml[kk].x;
+#pragma unroll
+                for (int off = PASS / 2; off; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off, LPR));
+                const float m_new = fmaxf(r.M, mx);
+                const bool empty = m_new == -CUDART_INF_F;
+                const float a = (empty || r.M == -CUDART_INF_F) ? 0.f : fast_exp2((r.M - m_new) * c);
+                const float w = (empty || ml[kk].x == -CUDART_INF_F) ? 0.f : fast_exp2((ml[kk].x - m_new) * c);
+                r.L *= a;
+                r.acc.x *= a; r.acc.y *= a; r.acc.z *= a; r.acc.w *= a;
+#pragma unroll
+                for (int i = 0; i < PASS; ++i) {
+                    // parts are added in index order; lanes >= nn hold w = 0 and o = 0
+                    const float wi = __shfl_sync(0xffffffffu, w, i, LPR);
+                    const float li = __shfl_sync(0xffffffffu, ml[kk].y, i, LPR);
+                    r.L = fmaf(wi, li, r.L);
+                    r.acc.x = fmaf(wi, o[kk][i].x, r.acc.x);
+                    r.acc.y = fmaf(wi, o[kk][i].y, r.acc.y);
+                    r.acc.z = fmaf(wi, o[kk][i].z, r.acc.z);
+                    r.acc.w = fmaf(wi, o[kk][i].w, r.acc.w);
+                }
+                r.M = m_new;
+            }
+        }
+    }
+}
+
+template <int HD, bool WIDE>
+__device__ __forceinline__ void store_part(float* o_base, float* ml_base, int G, const RunState (&st)[Slots<HD, WIDE>::N]) {
+    using S = Slots<HD, WIDE>;
+    const int tid = threadIdx.x;
+#pragma unroll
+    for (int k = 0; k < S::N; ++k) {
+        const int row = S::row(tid, k), c4 = S::col4(tid, k);
+        if (row < G) {
+            *reinterpret_cast<float4*>(o_base + (size_t)row * HD + c4 * 4) = st[k].acc;
+            if (c4 == 0) *reinterpret_cast<float2*>(ml_base + (size_t)row * 2) = make_float2(st[k].M, st[k].L);
+        }
+    }
+}
+
+// All threads of the CTA store their share of a partial, then one ticket is drawn from `counter`, which counts
+// 0..n-1 and wraps to zero.  Returns true in every thread of the CTA that drew the last ticket.  Its later reads of
+// the other arrivals' partials go to L2 (ld.cg), where those stores were made visible before their tickets were drawn,
+// and cannot start before the ticket is known (barrier + branch).
+__device__ __forceinline__ bool arrive_last(unsigned* counter, int n) {
+    __shared__ unsigned s_ticket;
+    if (n <= 1) return true;
+    __syncthreads();                 // every thread's stores precede thread 0's fence (the fence is cumulative)
+    if (threadIdx.x == 0) {
+        __threadfence();
+        s_ticket = atomicInc(counter, (unsigned)(n - 1));
+    }
+    __syncthreads();
+    return s_ticket == (unsigned)(n - 1);
+}
+
+// ---- record exchange between ranks: tagged 8-byte words ---------------------------------------------------------
+__device__ __forceinline__ unsigned long long tag_word(float v, unsigned tag) {
+    return ((unsigned long long)tag << 32) | (unsigned long long)__float_as_uint(v);
+}
+__device__ __forceinline__ void peer_store_pair(unsigned long long* dst, float v0, float v1, unsigned tag) {
+    asm volatile("st.relaxed.sys.global.v2.u64 [%0], {%1, %2};\n" ::"l"(dst), "l"(tag_word(v0, tag)), "l"(tag_word(v1, tag)) : "memory");
+}
+__device__ __forceinline__ void peer_load_pair(const unsigned long long* src, unsigned long long& w0, unsigned long long& w1) {
+    asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];\n" : "=l"(w0), "=l"(w1) : "l"(src) : "memory");
+}
+__device__ __forceinline__ bool tagged(unsigned long long w, unsigned g) { return (unsigned)(w >> 32) == g; }
+
+// Waits until the records of generation g of every rank have landed for one head and merges dims 4*c4..4*c4+3 of them.
+// `recs`: rank 0's record of that head in this rank's exchange buffer, records of consecutive ranks `rank_stride` words
+// apart.  A word is taken once its tag equals g; all polls of a round are independent loads.  The wait is bounded by
+// `limit` SM clock cycles; false = it ran out (nothing merged).
+__device__ __forceinline__ bool wait_records(const unsigned long long* recs, size_t rank_stride, int world, int hd, int c4,
+                                             unsigned g, long long limit, RunState& fin) {
+    const long long t0 = clock64();
+    fin = run_empty();
+    for (int r0 = 0; r0 < world; r0 += 8) {
+        const int nn = min(8, world - r0);
+        unsigned pending = (1u << nn) - 1u;
+        float m[8], l[8];
+        float4 o[8];
+        while (pending) {
+            unsigned long long w[8][6];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                if (pending >> i & 1u) {
+                    const unsigned long long* rec = recs + (size_t)(r0 + i) * rank_stride;
+                    peer_load_pair(rec + c4 * 4, w[i][0], w[i][1]);
+                    peer_load_pair(rec + c4 * 4 + 2, w[i][2], w[i][3]);
+                    peer_load_pair(rec + hd, w[i][4], w[i][5]);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                if ((pending >> i & 1u) && tagged(w[i][0], g) && tagged(w[i][1], g) && tagged(w[i][2], g) && tagged(w[i][3], g) &&
+                    tagged(w[i][4], g) && tagged(w[i][5], g)) {
+                    o[i] = make_float4(__uint_as_float((unsigned)w[i][0]), __uint_as_float((unsigned)w[i][1]),
+                                       __uint_as_float((unsigned)w[i][2]), __uint_as_float((unsigned)w[i][3]));
+                    m[i] = __uint_as_float((unsigned)w[i][4]);
+                    l[i] = __uint_as_float((unsigned)w[i][5]);
+                    pending &= ~(1u << i);
+                }
+            }
+            if (pending && clock64() - t0 > limit) return false;
+        }
+        run_add(fin, m, l, o, nn, LOG2E);      // records carry m in natural-log units of the scaled score
+    }
+    return true;
+}
+
+// q8_1 form of four consecutive output values per lane (see store_q8_group): a group of 32 values sits in 8 neighbouring
+// lanes.  Called by all 32 lanes; `valid` only guards the stores.
+__device__ __forceinline__ void store_q8_group4(float4 x, bool valid, size_t flat, int8_t* qs, float* scales) {
+    float amax = fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w)));
+#pragma unroll
+    for (int off = 4; off; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+    const float d = __fdiv_rn(amax, 127.0f);
+    if (!valid) return;
+    char4 q = make_char4(0, 0, 0, 0);
+    if (amax != 0.0f) {
+        q.x = (signed char)roundf(__fdiv_rn(x.x, d));
+        q.y = (signed char)roundf(__fdiv_rn(x.y, d));
+        q.z = (signed char)roundf(__fdiv_rn(x.z, d));
+        q.w = (signed char)roundf(__fdiv_rn(x.w, d));
+    }
+    *reinterpret_cast<char4*>(qs + flat) = q;
+    if ((flat & 31) == 0) scales[flat >> 5] = d;
+}
+
+__device__ __forceinline__ float4 normalised(const RunState& s) {
+    if (!(s.L > 0.f)) return make_float4(0.f, 0.f, 0.f, 0.f);
+    return make_float4(s.acc.x / s.L, s.acc.y / s.L, s.acc.z / s.L, s.acc.w / s.L);
+}
+
+// What the CTA that holds a kv head's merged (M, L, O) does with it.  Called by all threads of that CTA.
+template <int HD, bool WIDE, typename Args>
+__device__ __forceinline__ void emit_final(const Args& p, int kvh, int G, const RunState (&st)[Slots<HD, WIDE>::N]) {
+    using S = Slots<HD, WIDE>;
+    const int tid = threadIdx.x;
+    if (!p.emit_partial) {
+#pragma unroll
+        for (int k = 0; k < S::N; ++k) {
+            const int row = S::row(tid, k), c4 = S::col4(tid, k);
+            const bool valid = row < G;
+            const size_t flat = (size_t)(kvh * G + row) * HD + c4 * 4;
+            const float4 v = valid ? normalised(st[k]) : make_float4(0.f, 0.f, 0.f, 0.f);
+            if (valid && p.out) *reinterpret_cast<float4*>(p.out + flat) = v;
+            if (p.out_qs) store_q8_group4(v, valid, flat, p.out_qs, p.out_scales);
+        }
+        return;
+    }
+    if (!p.peer_bufs) {
+        // per-rank record {O, m, l, 0, 0}, m in natural-log units of the scaled score
+#pragma unroll
+        for (int k = 0; k < S::N; ++k) {
+            const int row = S::row(tid, k), c4 = S::col4(tid, k);
+            if (row < G) {
+                float* rec = p.out + (size_t)(kvh * G + row) * (HD + PART_PAD);
+                *reinterpret_cast<float4*>(rec + c4 * 4) = st[k].acc;
+                if (c4 == 0) *reinterpret_cast<float4*>(rec + HD) = make_float4(st[k].M * p.scale, st[k].L, 0.f, 0.f);
+            }
+        }
+        return;
+    }
+    // Peer exchange: the record goes straight into every rank's exchange buffer (plain stores over NVLink), every
+    // value tagged with the generation of the call.  Only this CTA touches the generation counters of its heads.
+    unsigned g[S::N];
+#pragma unroll
+    for (int k = 0; k < S::N; ++k) {
+        const int row = S::row(tid, k);
+        g[k] = row < G ? (unsigned)(__ldcg(p.gen_push + kvh * G + row) + 1) : 0u;
+    }
+    __syncthreads();      // every thread has read its generations before anyone advances them below
+    constexpr size_t rec_sz = HD + PART_PAD;
+#pragma unroll
+    for (int k = 0; k < S::N; ++k) {
+        const int row = S::row(tid, k), c4 = S::col4(tid, k);
+        if (row < G) {
+            const int head = kvh * G + row;
+            for (int r = 0; r < p.world; ++r) {
+                unsigned long long* rec = reinterpret_cast<unsigned long long*>(p.peer_bufs[r]) +
+                                          ((size_t)((g[k] & 1) * p.world + p.rank) * p.n_head + head) * rec_sz;
+                peer_store_pair(rec + c4 * 4, st[k].acc.x, st[k].acc.y, g[k]);
+                peer_store_pair(rec + c4 * 4 + 2, st[k].acc.z, st[k].acc.w, g[k]);
+                if (c4 == 0) peer_store_pair(rec + HD, st[k].M * p.scale, st[k].L, g[k]);
+            }
+        }
+    }
+    if (p.fused_wait) {
+        const unsigned long long* mine = reinterpret_cast<const unsigned long long*>(p.peer_bufs[p.rank]);
+#pragma unroll
+        for (int k = 0; k < S::N; ++k) {
+            const int row = S::row(tid, k), c4 = S::col4(tid, k);
+            if (row < G) {
+                const int head = kvh * G + row;
+                RunState fin;
+                const unsigned long long* recs = mine + ((size_t)(g[k] & 1) * p.world * p.n_head + head) * rec_sz;
+                if (wait_records(recs, (size_t)p.n_head * rec_sz, p.world, HD, c4, g[k], p.wait_cycles, fin))
+                    *reinterpret_cast<float4*>(p.out + (size_t)head * HD + c4 * 4) = normalised(fin);
+                else if (p.peer_status)
+                    atomicExch(p.peer_status, 1);
+            }
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < S::N; ++k) {
+        const int row = S::row(tid, k);
+        if (row < G && S::col4(tid, k) == 0) p.gen_push[kvh * G + row] = (int)g[k];
+    }
+}
+
 template <int HD, bool WIDE>
 __global__ void __launch_bounds__(kThreads, 2) decode_split_kernel(const DecodeArgs p) {
     using L = DecodeSmem<HD>;
+    using S = Slots<HD, WIDE>;
     extern __shared__ __align__(128) uint8_t smem[];
     const int split = blockIdx.x, kvh = blockIdx.y;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int r = lane >> 2, t = lane & 3;
     const int G = p.n_head / p.n_kv;
 
-    // The merge kernel of this call may start launching now; it waits for this grid to complete before it reads.
+    // The next kernel of the stream may start launching now; it waits for this grid to complete before it reads
+    // anything this grid writes.
     pdl_trigger();
-    // Unless the caller vouched for the position word and the cache rows below the valid length (overlap 2), nothing
+    // Unless the caller vouched for the position word and the cache rows below the newest one (overlap 2), nothing
     // is read before every preceding kernel of the stream has completed.
     if (p.overlap != 2) pdl_wait();
 
     const int npos = clamp_len(*p.d_pos + p.pos_bias, p.n_ctx);
     const SplitPlan plan = plan_splits(npos, p.n_splits, p.min_tiles);
-    if (split >= plan.active) return;
+    if (split >= max(plan.active, 1)) return;
+    if (plan.active == 0) {
+        // no valid row at all: the empty result (zero output, or a record with m = -inf, l = 0)
+        if (p.overlap == 2) pdl_wait();
+        RunState st[S::N];
+#pragma unroll
+        for (int k = 0; k < S::N; ++k) st[k] = run_empty();
+        emit_final<HD, WIDE>(p, kvh, G, st);
+        return;
+    }
     const int tile0 = split * plan.tiles_per_split;
     const int tile1 = min(tile0 + plan.tiles_per_split, plan.n_tiles);
     const int nt = tile1 - tile0;
 
     const bool append = (p.fuse & 4) != 0;
-    const bool owner = append && split == plan.active - 1;   // this CTA's last tile holds row npos-1
+    // The CTA whose last tile holds row npos-1 takes that row from the caller's k_new / v_new (fused append) or, when
+    // tiles are fetched ahead of the dependency wait, re-reads it after the wait: the kernel just before this one
+    // may be the one that stores it (kv_store_ind, src/model_gpu.cu:281).  Either way it is patched into this CTA's
+    // shared-memory tile and left out of the asynchronous copies.
+    const bool owner = (append || p.overlap == 2) && split == plan.active - 1;
     const int new_pos = npos - 1;
-    // rows the async copies may read: the new row is not in the cache yet when it is fused
     const int nload = owner ? new_pos : npos;
 
     const __half* Kg = reinterpret_cast<const __half*>(p.kc) + (size_t)kvh * p.n_ctx * HD;
@@ -112,16 +437,14 @@ __global__ void __launch_bounds__(kThreads, 2) decode_split_kernel(const DecodeA
         }
     };
 
+    // all stages are filled before anything else happens: tile s is copy group s
 #pragma unroll
-    for (int s = 0; s < kStages - 1; ++s) {
+    for (int s = 0; s < kStages; ++s) {
         if (s < nt) load_tile(s, s);
         cp_async_commit();
     }
 
-    // the first tiles are in flight; q, the new K/V row and the scratch block belong to preceding kernels
-    if (p.overlap == 2) pdl_wait();
-
-    // ---- prologue: RoPE table, Q -> fp16 fragments, new K/V row ------------------------------
+    // RoPE table while the first tiles are in flight: it needs only the position word(s) and the model's constants
     float* s_cos = reinterpret_cast<float*>(smem + L::CS_OFF);
     float* s_sin = s_cos + HD / 2;
     const bool rope_q = (p.fuse & 1) != 0, rope_k = (p.fuse & 2) != 0;
@@ -132,41 +455,76 @@ __global__ void __launch_bounds__(kThreads, 2) decode_split_kernel(const DecodeA
             // index when the cache holds only a slice of the sequence
             rope_cs(p.d_rope_pos ? *p.d_rope_pos : new_pos, f, s_cos[i], s_sin[i]);
         }
-        __syncthreads();
     }
+
+    // q, the new K/V row and the scratch block belong to preceding kernels
+    if (p.overlap == 2) pdl_wait();
+
+    // ---- prologue: Q -> fp16 fragments, new K/V row ------------------------------------------
+    // All global reads of the inputs are issued together (one round trip): q rows, then k_new and v_new, with their
+    // biases added, land in a small fp32 staging area; the per-row work below reads shared memory only.
+    float* s_in = reinterpret_cast<float*>(smem + L::IN_OFF);
     {
+        const int rows = G + ((owner && append) ? 2 : 0);
+        for (int idx = tid; idx < rows * (HD / 4); idx += kThreads) {
+            const int row = idx / (HD / 4), c4 = idx % (HD / 4);
+            const float* src;
+            const float* bias;
+            if (row < G) {
+                src = p.q + (size_t)(kvh * G + row) * HD;
+                bias = p.pre.bias_q ? p.pre.bias_q + (size_t)(kvh * G + row) * HD : nullptr;
+            } else if (row == G) {
+                src = p.k_new + (size_t)kvh * HD;
+                bias = p.pre.bias_k ? p.pre.bias_k + (size_t)kvh * HD : nullptr;
+            } else {
+                src = p.v_new + (size_t)kvh * HD;
+                bias = p.pre.bias_v ? p.pre.bias_v + (size_t)kvh * HD : nullptr;
+            }
+            float4 v = *reinterpret_cast<const float4*>(src + c4 * 4);
+            if (bias) {
+                const float4 bv = *reinterpret_cast<const float4*>(bias + c4 * 4);
+                v.x += bv.x; v.y += bv.y; v.z += bv.z; v.w += bv.w;
+            }
+            const int srow = row < G ? row : 16 + (row - G);
+            *reinterpret_cast<float4*>(s_in + srow * HD + c4 * 4) = v;
+        }
         // rows >= G of the 16-row query tile are zero
         for (int i = tid; i < 16 * L::CHUNKS; i += kThreads) {
             const int row = i / L::CHUNKS;
             if (row >= G) *reinterpret_cast<uint4*>(smem + L::Q_OFF + swz<L::ROWB>(row, i % L::CHUNKS)) = make_uint4(0, 0, 0, 0);
         }
+        if (owner && !append && tid < 2 * L::CHUNKS) {
+            // the newest row as the cache holds it now that every preceding kernel has completed
+            const int which = tid / L::CHUNKS, chunk = tid % L::CHUNKS;
+            const uint4 v = __ldcg(reinterpret_cast<const uint4*>((which ? Vg : Kg) + (size_t)new_pos * HD + chunk * 8));
+            *reinterpret_cast<uint4*>(smem + (which ? L::VNEW_OFF : L::KNEW_OFF) + chunk * 16) = v;
+        }
+    }
+    __syncthreads();
+    {
         // one warp per head row, round-robin
         for (int h = warp; h < G; h += kThreads / 32) {
-            const float* src = p.q + (size_t)(kvh * G + h) * HD;
-            const float* bq = p.pre.bias_q ? p.pre.bias_q + (size_t)(kvh * G + h) * HD : nullptr;
-            const float rn = p.pre.norm_q ? warp_row_rnorm(src, bq, HD, p.pre.eps, lane) : 1.f;
-            rope_row_to_half(src, bq, p.pre.norm_q, rn, HD, rope_q, p.rope, s_cos, s_sin, lane, 32, [&](int e, float v) {
+            const float* src = s_in + h * HD;
+            const float rn = p.pre.norm_q ? warp_row_rnorm(src, nullptr, HD, p.pre.eps, lane) : 1.f;
+            rope_row_to_half(src, nullptr, p.pre.norm_q, rn, HD, rope_q, p.rope, s_cos, s_sin, lane, 32, [&](int e, float v) {
                 *reinterpret_cast<__half*>(smem + L::Q_OFF + swz<L::ROWB>(h, e >> 3) + (e & 7) * 2) = __float2half_rn(v);
             });
         }
-        if (owner) {
+        if (owner && append) {
             __half* s_k = reinterpret_cast<__half*>(smem + L::KNEW_OFF);
             __half* s_v = reinterpret_cast<__half*>(smem + L::VNEW_OFF);
             if (warp == 0) {
-                const float* src = p.k_new + (size_t)kvh * HD;
-                const float* bk = p.pre.bias_k ? p.pre.bias_k + (size_t)kvh * HD : nullptr;
-                const float rn = p.pre.norm_k ? warp_row_rnorm(src, bk, HD, p.pre.eps, lane) : 1.f;
-                rope_row_to_half(src, bk, p.pre.norm_k, rn, HD, rope_k, p.rope, s_cos, s_sin, lane, 32,
+                const float* src = s_in + 16 * HD;
+                const float rn = p.pre.norm_k ? warp_row_rnorm(src, nullptr, HD, p.pre.eps, lane) : 1.f;
+                rope_row_to_half(src, nullptr, p.pre.norm_k, rn, HD, rope_k, p.rope, s_cos, s_sin, lane, 32,
                                  [&](int e, float v) { s_k[e] = __float2half_rn(v); });
             } else if (warp == 1) {
-                const float* bv = p.pre.bias_v ? p.pre.bias_v + (size_t)kvh * HD : nullptr;
-                for (int e = lane; e < HD; e += 32)
-                    s_v[e] = __float2half_rn(pre_value(p.v_new + (size_t)kvh * HD, bv, nullptr, 1.f, e));
+                for (int e = lane; e < HD; e += 32) s_v[e] = __float2half_rn(s_in[17 * HD + e]);
             }
         }
     }
     __syncthreads();
-    if (owner && tid < 2 * L::CHUNKS) {
+    if (owner && append && tid < 2 * L::CHUNKS) {
         // store the new row into the cache (kv_store_k, src/kernels.cu:1660-1678)
         const int which = tid / L::CHUNKS, chunk = tid % L::CHUNKS;
         const uint4 v = *reinterpret_cast<const uint4*>(smem + (which ? L::VNEW_OFF : L::KNEW_OFF) + chunk * 16);
@@ -193,10 +551,12 @@ __global__ void __launch_bounds__(kThreads, 2) decode_split_kernel(const DecodeA
     const int wr0 = warp * 16;
 
     for (int it = 0; it < nt; ++it) {
-        cp_async_wait<kStages - 2>();
-        __syncthreads();
-        {
-            const int nxt = it + kStages - 1;
+        // tile t is copy group t; kStages groups were committed up front and one more per iteration from it = 1 on, so
+        // at most kStages-1 (first iteration) or kStages-2 groups may still be in flight once tile `it` has landed
+        if (it == 0) cp_async_wait<kStages - 1>(); else cp_async_wait<kStages - 2>();
+        __syncthreads();                       // landed for every thread, and everybody is done with tile it-1
+        if (it >= 1) {
+            const int nxt = it - 1 + kStages;  // refill the stage tile it-1 used
             if (nxt < nt) load_tile(nxt, nxt % kStages);
             cp_async_commit();
         }
@@ -206,7 +566,7 @@ __global__ void __launch_bounds__(kThreads, 2) decode_split_kernel(const DecodeA
         const uint32_t sV = sK + L::TILE_BYTES;
 
         if (owner && it == nt - 1) {
-            // patch the new token's row into this CTA's copy of the tile
+            // patch the newest row into this CTA's copy of the tile
             const int prow = new_pos - row0;
             if (tid < 2 * L::CHUNKS) {
                 const int which = tid / L::CHUNKS, chunk = tid % L::CHUNKS;
@@ -285,320 +645,141 @@ __global__ void __launch_bounds__(kThreads, 2) decode_split_kernel(const DecodeA
         }
     }
 
-    // ---- merge the four warps ------------------------------------------------------------------
+    // ---- merge the four warps: every warp scales its O by e^(m_w - M) and the sums are taken in warp order ---------
     cp_async_wait<0>();
     __syncthreads();
-    float* mO = reinterpret_cast<float*>(smem);                        // [4][16][HD]
+    float* mO = reinterpret_cast<float*>(smem);                        // [4][16][MERGE_STRIDE]
     float* mML = reinterpret_cast<float*>(smem + L::MERGE_ML_OFF);     // [4][16][2]
 #pragma unroll
     for (int hh = 0; hh < NH; ++hh) {
         float l = l_run[hh];
         l += __shfl_xor_sync(0xffffffffu, l, 1);
         l += __shfl_xor_sync(0xffffffffu, l, 2);
-        const int row = r + 8 * hh;
-        if (t == 0) {
-            mML[(warp * 16 + row) * 2 + 0] = m_run[hh];
-            mML[(warp * 16 + row) * 2 + 1] = l;
-        }
-#pragma unroll
-        for (int j = 0; j < HD / 8; ++j) {
-            float2 v = make_float2(o[j][2 * hh], o[j][2 * hh + 1]);
-            *reinterpret_cast<float2*>(&mO[(warp * 16 + row) * HD + 8 * j + 2 * t]) = v;
-        }
+        if (t == 0) *reinterpret_cast<float2*>(&mML[(warp * 16 + r + 8 * hh) * 2]) = make_float2(m_run[hh], l);
     }
     __syncthreads();
-    const bool direct = (plan.active == 1) && !p.emit_partial;
-    for (int idx = tid; idx < G * HD; idx += kThreads) {
-        const int row = idx / HD, d = idx % HD;
+#pragma unroll
+    for (int hh = 0; hh < NH; ++hh) {
+        const int row = r + 8 * hh;
         float M = -CUDART_INF_F;
 #pragma unroll
         for (int w = 0; w < 4; ++w) M = fmaxf(M, mML[(w * 16 + row) * 2]);
-        float Lsum = 0.f, O = 0.f;
+        const float wgt = (m_run[hh] == -CUDART_INF_F) ? 0.f : fast_exp2((m_run[hh] - M) * c);
+        float* dst = mO + (size_t)(warp * 16 + row) * L::MERGE_STRIDE + 2 * t;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) {
-            const float mw = mML[(w * 16 + row) * 2];
-            const float wgt = (mw == -CUDART_INF_F) ? 0.f : fast_exp2((mw - M) * c);
-            Lsum += wgt * mML[(w * 16 + row) * 2 + 1];
-            O += wgt * mO[(w * 16 + row) * HD + d];
-        }
-        const int head = kvh * G + row;
-        if (direct) {
-            const float val = O / Lsum;
-            if (p.out) p.out[(size_t)head * HD + d] = val;
-            if (p.out_qs) store_q8_group(val, (size_t)head * HD + d, p.out_qs, p.out_scales);
-        } else {
-            p.ws_o[((size_t)head * p.n_splits + split) * HD + d] = O;
-            if (d == 0) {
-                p.ws_ml[((size_t)head * p.n_splits + split) * 2 + 0] = M * p.scale;
-                p.ws_ml[((size_t)head * p.n_splits + split) * 2 + 1] = Lsum;
+        for (int j = 0; j < HD / 8; ++j)
+            *reinterpret_cast<float2*>(dst + 8 * j) = make_float2(o[j][2 * hh] * wgt, o[j][2 * hh + 1] * wgt);
+    }
+    __syncthreads();
+    RunState st[S::N];
+#pragma unroll
+    for (int k = 0; k < S::N; ++k) {
+        const int row = S::row(tid, k), c4 = S::col4(tid, k);
+        st[k] = run_empty();
+        if (row < G) {
+            float mw[4], lw[4];
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float2 ml = *reinterpret_cast<const float2*>(&mML[(w * 16 + row) * 2]);
+                mw[w] = ml.x;
+                lw[w] = ml.y;
+                st[k].M = fmaxf(st[k].M, ml.x);
+            }
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float wgt = (mw[w] == -CUDART_INF_F) ? 0.f : fast_exp2((mw[w] - st[k].M) * c);
+                st[k].L = fmaf(wgt, lw[w], st[k].L);
+                const float4 v = *reinterpret_cast<const float4*>(mO + (size_t)(w * 16 + row) * L::MERGE_STRIDE + c4 * 4);
+                st[k].acc.x += v.x; st[k].acc.y += v.y; st[k].acc.z += v.z; st[k].acc.w += v.w;
             }
         }
     }
-}
 
-// ---- log-sum-exp combine -----------------------------------------------------------------------
-// One CTA per head, 8 warps.  Part s of head h: O at o_base + h*o_hs + s*o_ss (hd floats), (m, l)
-// at ml_base + h*ml_hs + s*ml_ss.  n_parts < 0: derive the number of parts from *d_pos with the
-// same plan as the split kernel (and do nothing when that kernel already wrote the result).
-struct CombineArgs {
-    const float* o_base;
-    const float* ml_base;
-    long long o_hs, o_ss, ml_hs, ml_ss;
-    float* out;
-    int head_dim;
-    int n_parts;
-    const int* d_pos;
-    int pos_bias, n_ctx, n_splits, min_tiles;
-    int emit_partial;
-    // peer exchange (multi-GPU): when peer_bufs is set the un-normalised record of head h is stored straight into
-    // every rank's exchange buffer (plain stores over NVLink), each value tagged with the generation of the call
-    const unsigned long long* peer_bufs;   // device array of `world` pointers (this rank's own buffer included)
-    int* gen_push;                          // [n_head] private generation counters of this rank
-    int rank, world, n_head;
-    int8_t* out_qs;                         // optional q8_1 form of the final output (see store_q8_group)
-    float* out_scales;
-    int fused_wait;                         // also wait for all ranks' records and write the final output to `out`
-    int* status;                            // raised when that wait ran out
-};
-
-constexpr int kCombineThreads = 512;
-constexpr int kPeerWaitThreads = 128 + 32;   // head_dim (at most 128) value pollers + up to DECODE_MAX_RANKS (m, l) pollers
-constexpr int kCombineWarps = kCombineThreads / 32;
-
-// ---- record exchange between ranks: tagged 8-byte words ---------------------------------------------------------
-__device__ __forceinline__ void peer_store_word(unsigned long long* dst, float v, unsigned tag) {
-    const unsigned long long w = ((unsigned long long)tag << 32) | (unsigned long long)__float_as_uint(v);
-    asm volatile("st.relaxed.sys.global.u64 [%0], %1;\n" ::"l"(dst), "l"(w) : "memory");
-}
-__device__ __forceinline__ unsigned long long peer_load_word(const unsigned long long* src) {
-    unsigned long long w;
-    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];\n" : "=l"(w) : "l"(src) : "memory");
-    return w;
-}
-
-// Wait for every rank's record of generation g for head h in this rank's exchange buffer and merge them.
-// Called by all threads of a CTA of at least head_dim + world threads.  Thread d < head_dim polls the words that carry
-// O[d] of every source rank (all polls of one round are independent loads); thread head_dim + r polls m and l of
-// rank r.  A word is taken once its tag equals g.  The wait is bounded (about two seconds), after which a status
-// word is raised and the output is left untouched.
-__device__ __forceinline__ void peer_wait_merge(const unsigned char* my_buf, int g, int h, int world, int n_head, int hd,
-                                                float* out, int* status) {
-    __shared__ int s_fail;
-    __shared__ float s_m[DECODE_MAX_RANKS], s_l[DECODE_MAX_RANKS];
-    const int tid = threadIdx.x;
-    __syncthreads();
-    if (tid == 0) s_fail = 0;
-    __syncthreads();
-    const size_t rec_sz = hd + PART_PAD;
-    const unsigned long long* recs = reinterpret_cast<const unsigned long long*>(my_buf) +
-                                     ((size_t)(g & 1) * world * n_head + h) * rec_sz;
-    const size_t rank_stride = (size_t)n_head * rec_sz;
-    float o[DECODE_MAX_RANKS];
-    const long long t0 = clock64();
-    if (tid < hd) {
-        unsigned pending = (1u << world) - 1u;      // world <= DECODE_MAX_RANKS = 16
-        while (pending) {
-            unsigned long long w[DECODE_MAX_RANKS];
-#pragma unroll
-            for (int r = 0; r < DECODE_MAX_RANKS; ++r)
-                if (pending >> r & 1u) w[r] = peer_load_word(recs + r * rank_stride + tid);
-#pragma unroll
-            for (int r = 0; r < DECODE_MAX_RANKS; ++r) {
-                if ((pending >> r & 1u) && (unsigned)(w[r] >> 32) == (unsigned)g) {
-                    o[r] = __uint_as_float((unsigned)w[r]);
-                    pending &= ~(1u << r);
-                }
-            }
-            if (pending && clock64() - t0 > 4000000000LL) { s_fail = 1; break; }
-        }
-    } else if (tid < hd + world) {
-        const int r = tid - hd;
-        const unsigned long long* rec = recs + r * rank_stride + hd;
-        for (;;) {
-            const unsigned long long wm = peer_load_word(rec), wl = peer_load_word(rec + 1);
-            if ((unsigned)(wm >> 32) == (unsigned)g && (unsigned)(wl >> 32) == (unsigned)g) {
-                s_m[r] = __uint_as_float((unsigned)wm);
-                s_l[r] = __uint_as_float((unsigned)wl);
-                break;
-            }
-            if (clock64() - t0 > 4000000000LL) { s_fail = 1; break; }
-        }
-    }
-    __syncthreads();
-    if (s_fail) {
-        if (tid == 0 && status) atomicExch(status, 1);
+    // ---- merge across the CTAs of this kv head -------------------------------------------------------------------
+    if (plan.active == 1) {
+        emit_final<HD, WIDE>(p, kvh, G, st);
         return;
     }
-    if (tid < hd) {
-        float M = -CUDART_INF_F;
-        for (int r = 0; r < world; ++r) M = fmaxf(M, s_m[r]);
-        float L = 0.f, acc = 0.f;
-#pragma unroll
-        for (int r = 0; r < DECODE_MAX_RANKS; ++r) {
-            if (r < world) {
-                const float w = (s_m[r] == -CUDART_INF_F) ? 0.f : __expf(s_m[r] - M);
-                L = fmaf(w, s_l[r], L);
-                acc = fmaf(w, o[r], acc);
-            }
-        }
-        out[(size_t)h * hd + tid] = L > 0.f ? acc / L : 0.f;
+    const size_t blk = (size_t)G * HD;       // floats of one partial
+    {
+        const size_t part = (size_t)kvh * p.n_splits + split;
+        store_part<HD, WIDE>(p.ws_o + part * blk, p.ws_ml + part * G * 2, G, st);
     }
+    // few partials merge in one level (one pass of merge_parts); more go through groups of p.group neighbours
+    const int group = plan.active <= 16 ? plan.active : p.group;
+    const int grp = split / group;
+    const int grp_n = min(group, plan.active - grp * group);
+    if (!arrive_last(p.tickets + kvh * p.n_groups + grp, grp_n)) return;
+    {
+        const size_t part0 = (size_t)kvh * p.n_splits + (size_t)grp * group;
+        merge_parts<HD, WIDE>(p.ws_o + part0 * blk, p.ws_ml + part0 * G * 2, grp_n, G, c, st);
+    }
+    const int n_grp = (plan.active + group - 1) / group;
+    if (n_grp > 1) {
+        const size_t gpart = (size_t)kvh * p.n_groups + grp;
+        store_part<HD, WIDE>(p.grp_o + gpart * blk, p.grp_ml + gpart * G * 2, G, st);
+        if (!arrive_last(p.tickets + p.n_kv * p.n_groups + kvh, n_grp)) return;
+        const size_t g0 = (size_t)kvh * p.n_groups;
+        merge_parts<HD, WIDE>(p.grp_o + g0 * blk, p.grp_ml + g0 * G * 2, n_grp, G, c, st);
+    }
+    emit_final<HD, WIDE>(p, kvh, G, st);
 }
 
-__global__ void __launch_bounds__(kCombineThreads) combine_kernel(const CombineArgs p) {
-    __shared__ float s_w[DECODE_MAX_SPLITS];
-    __shared__ float s_red[kCombineWarps];
-    __shared__ float4 s_acc[kCombineWarps][32];
-    const int h = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int hd = p.head_dim;
-
-    pdl_trigger();
-    pdl_wait();      // the split kernel's partials (or the gathered records) must be complete
-
-    int n = p.n_parts;
-    if (n < 0) {
-        const int npos = clamp_len(*p.d_pos + p.pos_bias, p.n_ctx);
-        const SplitPlan plan = plan_splits(npos, p.n_splits, p.min_tiles);
-        n = plan.active;
-        if (n == 1 && !p.emit_partial) return;   // the split kernel wrote the output itself
-    }
-    const float* ml = p.ml_base + (size_t)h * p.ml_hs;
-    const float* ob = p.o_base + (size_t)h * p.o_hs;
-
-    // The partials were written a moment ago and sit in L2; the kernel is a chain of L2 round trips, so every
-    // phase issues all of its loads before it uses any of them.  (m, l) of part tid: one load per thread
-    // (n <= DECODE_MAX_SPLITS = kCombineThreads).
-    float2 my = make_float2(-CUDART_INF_F, 0.f);
-    if (tid < n) my = make_float2(ml[(size_t)tid * p.ml_ss], ml[(size_t)tid * p.ml_ss + 1]);
-    // prefetch this warp's O rows (up to 4 parts in flight per lane) while the weights are being computed
-    constexpr int U = 4;
-    float4 pre[U];
-    const bool lane_ok = lane * 4 < hd;
+// ---- log-sum-exp combine of gathered records -----------------------------------------------------------------
+// One CTA per head, one thread per four dims: records [n_parts][n_head][hd + PART_PAD] -> out [n_head][hd].
+__global__ void combine_records_kernel(const float* parts, int n_parts, float* out, int n_head, int hd) {
+    const int h = blockIdx.x, c4 = threadIdx.x;
+    if (c4 * 4 >= hd) return;
+    const size_t rec = hd + PART_PAD;
+    RunState fin = run_empty();
+    for (int i0 = 0; i0 < n_parts; i0 += 8) {
+        const int nn = min(8, n_parts - i0);
+        float m[8], l[8];
+        float4 o[8];
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-        const int s = warp + u * kCombineWarps;
-        pre[u] = (lane_ok && s < n) ? *reinterpret_cast<const float4*>(ob + (size_t)s * p.o_ss + lane * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
-    }
-
-    float mx = my.x;
-#pragma unroll
-    for (int off = 16; off; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
-    if (lane == 0) s_red[warp] = mx;
-    __syncthreads();
-    float M = -CUDART_INF_F;
-#pragma unroll
-    for (int w = 0; w < kCombineWarps; ++w) M = fmaxf(M, s_red[w]);
-    __syncthreads();
-
-    const float wgt = (my.x == -CUDART_INF_F) ? 0.f : __expf(my.x - M);
-    if (tid < n) s_w[tid] = wgt;
-    float lsum = wgt * my.y;
-#pragma unroll
-    for (int off = 16; off; off >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, off);
-    if (lane == 0) s_red[warp] = lsum;
-    __syncthreads();
-    float Lsum = 0.f;
-#pragma unroll
-    for (int w = 0; w < kCombineWarps; ++w) Lsum += s_red[w];
-
-    // O: warp w takes parts w, w+16, ...; lane takes 4 consecutive dims
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-        const int s = warp + u * kCombineWarps;
-        const float w = s < n ? s_w[s] : 0.f;
-        acc.x = fmaf(w, pre[u].x, acc.x);
-        acc.y = fmaf(w, pre[u].y, acc.y);
-        acc.z = fmaf(w, pre[u].z, acc.z);
-        acc.w = fmaf(w, pre[u].w, acc.w);
-    }
-    if (lane_ok) {
-        for (int s0 = warp + U * kCombineWarps; s0 < n; s0 += U * kCombineWarps) {
-            float4 v[U];
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const int s = s0 + u * kCombineWarps;
-                v[u] = s < n ? *reinterpret_cast<const float4*>(ob + (size_t)s * p.o_ss + lane * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const int s = s0 + u * kCombineWarps;
-                const float w = s < n ? s_w[s] : 0.f;
-                acc.x = fmaf(w, v[u].x, acc.x);
-                acc.y = fmaf(w, v[u].y, acc.y);
-                acc.z = fmaf(w, v[u].z, acc.z);
-                acc.w = fmaf(w, v[u].w, acc.w);
+        for (int i = 0; i < 8; ++i) {
+            if (i < nn) {
+                const float* r = parts + ((size_t)(i0 + i) * n_head + h) * rec;
+                o[i] = *reinterpret_cast<const float4*>(r + c4 * 4);
+                m[i] = r[hd];
+                l[i] = r[hd + 1];
             }
         }
+        run_add(fin, m, l, o, nn, LOG2E);
     }
-    s_acc[warp][lane] = acc;
-    __syncthreads();
-    if (tid < hd) {
-        const int l4 = tid >> 2, e = tid & 3;
-        float v = 0.f;
-#pragma unroll
-        for (int w = 0; w < kCombineWarps; ++w) {
-            const float4 a = s_acc[w][l4];
-            v += (e == 0) ? a.x : (e == 1) ? a.y : (e == 2) ? a.z : a.w;
-        }
-        if (p.emit_partial && p.peer_bufs) {
-            const unsigned g = (unsigned)(p.gen_push[h] + 1);   // generation of this call; only this CTA touches gen_push[h]
-            const size_t rec_sz = hd + PART_PAD;
-            for (int r = 0; r < p.world; ++r) {
-                unsigned long long* rec = reinterpret_cast<unsigned long long*>(p.peer_bufs[r]) +
-                                          ((size_t)((g & 1) * p.world + p.rank) * p.n_head + h) * rec_sz;
-                peer_store_word(rec + tid, v, g);
-                if (tid == 0) {
-                    peer_store_word(rec + hd + 0, M, g);
-                    peer_store_word(rec + hd + 1, Lsum, g);
-                }
-            }
-        } else if (p.emit_partial) {
-            float* rec = p.out + (size_t)h * (hd + PART_PAD);
-            rec[tid] = v;
-            if (tid == 0) {
-                rec[hd + 0] = M;
-                rec[hd + 1] = Lsum;
-                rec[hd + 2] = 0.f;
-                rec[hd + 3] = 0.f;
-            }
-        } else {
-            const float val = Lsum > 0.f ? v / Lsum : 0.f;
-            if (p.out) p.out[(size_t)h * hd + tid] = val;
-            if (p.out_qs) store_q8_group(val, (size_t)h * hd + tid, p.out_qs, p.out_scales);
-        }
-    }
-    if (p.emit_partial && p.peer_bufs) {
-        const int g = p.gen_push[h] + 1;
-        if (p.fused_wait) {
-            // same launch also waits for the other ranks' records of this generation and writes the final output
-            peer_wait_merge(reinterpret_cast<const unsigned char*>(p.peer_bufs[p.rank]), g, h, p.world, p.n_head, hd,
-                            p.out, p.status);
-        }
-        __syncthreads();
-        if (tid == 0) p.gen_push[h] = g;
-    }
+    *reinterpret_cast<float4*>(out + (size_t)h * hd + c4 * 4) = normalised(fin);
 }
 
 // ---- wait for every rank's record of this generation and merge them -------------------------------------------
-// One CTA per head, in a launch of its own (the form that can run after all pushes on a single GPU); the work is
-// peer_wait_merge above.
+// One CTA per head, one thread per four dims, in a launch of its own: the form that can run after all pushes on a
+// single GPU.
 struct PeerWaitArgs {
     const unsigned char* my_buf;
     float* out;
     int* gen_wait;      // [n_head]
     int* status;
     int world, n_head, head_dim;
+    long long wait_cycles;
 };
 
-__global__ void __launch_bounds__(kPeerWaitThreads) peer_wait_combine_kernel(const PeerWaitArgs p) {
-    const int h = blockIdx.x;
+__global__ void peer_wait_combine_kernel(const PeerWaitArgs p) {
+    const int h = blockIdx.x, c4 = threadIdx.x;
     pdl_trigger();
     pdl_wait();
-    const int g = p.gen_wait[h] + 1;
-    peer_wait_merge(p.my_buf, g, h, p.world, p.n_head, p.head_dim, p.out, p.status);
+    const unsigned g = (unsigned)(__ldcg(p.gen_wait + h) + 1);
     __syncthreads();
-    if (threadIdx.x == 0) p.gen_wait[h] = g;
+    if (c4 * 4 < p.head_dim) {
+        const size_t rec_sz = p.head_dim + PART_PAD;
+        const unsigned long long* recs = reinterpret_cast<const unsigned long long*>(p.my_buf) +
+                                         ((size_t)(g & 1) * p.world * p.n_head + h) * rec_sz;
+        RunState fin;
+        if (wait_records(recs, (size_t)p.n_head * rec_sz, p.world, p.head_dim, c4, g, p.wait_cycles, fin))
+            *reinterpret_cast<float4*>(p.out + (size_t)h * p.head_dim + c4 * 4) = normalised(fin);
+        else if (p.status)
+            atomicExch(p.status, 1);
+    }
+    __syncthreads();
+    if (c4 == 0) p.gen_wait[h] = (int)g;
 }
 
 template <int HD, bool WIDE>
@@ -629,6 +810,51 @@ cudaError_t decode_static_scratch(void** ptr) {
         g_static_scratch_addr[dev] = p;
     }
     *ptr = g_static_scratch_addr[dev];
+    return cudaSuccess;
+}
+
+// ---- arrival counters ----------------------------------------------------------------------------------
+// The counters of the in-launch merge must be zero when a launch starts and are zero again when it ends.  They live
+// in the library image (zero-initialised when the module is loaded) rather than in the caller's workspace, which
+// nobody promises to clear.  A slot is bound to a workspace address on first use; launches that use different
+// workspaces therefore never share counters, and launches that share a workspace must not overlap anyway.
+static __device__ unsigned g_tickets[kTicketSlots * kTicketWords];
+namespace {
+struct TicketTable {
+    unsigned* base = nullptr;
+    const void* owner[kTicketSlots] = {};
+    unsigned long long stamp[kTicketSlots] = {};
+    unsigned long long clock = 0;
+};
+TicketTable g_ticket_tab[64];
+std::mutex g_ticket_mutex;
+} // namespace
+
+cudaError_t decode_ticket_slot(const void* workspace, unsigned** tickets) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> lock(g_ticket_mutex);
+    TicketTable& tab = g_ticket_tab[dev];
+    if (!tab.base) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_tickets);
+        if (e != cudaSuccess) return e;
+        tab.base = reinterpret_cast<unsigned*>(p);
+    }
+    if (!workspace) { *tickets = tab.base; return cudaSuccess; }      // set-up call: only the address look-up
+    int pick = -1, oldest = 0;
+    for (int i = 0; i < kTicketSlots; ++i) {
+        if (tab.owner[i] == workspace) { pick = i; break; }
+        if (tab.stamp[i] < tab.stamp[oldest]) oldest = i;
+    }
+    if (pick < 0) {
+        pick = oldest;                    // never used (stamp 0) or least recently used
+        tab.owner[pick] = workspace;
+    }
+    tab.stamp[pick] = ++tab.clock;
+    *tickets = tab.base + (size_t)pick * kTicketWords;
     return cudaSuccess;
 }
 
@@ -666,72 +892,20 @@ cudaError_t launch_decode(const DecodeArgs& a, cudaStream_t stream, unsigned lon
     if (a.head_dim == 128) e = wide ? launch_split<128, true>(a, stream) : launch_split<128, false>(a, stream);
     else                   e = wide ? launch_split<64, true>(a, stream) : launch_split<64, false>(a, stream);
     if (ev_stop) cudaEventRecordWithFlags(ev_stop, stream, ev_flags);
-    if (e != cudaSuccess) return e;
-    CombineArgs c;
-    c.o_base = a.ws_o;
-    c.ml_base = a.ws_ml;
-    c.o_hs = (long long)a.n_splits * a.head_dim;
-    c.o_ss = a.head_dim;
-    c.ml_hs = (long long)a.n_splits * 2;
-    c.ml_ss = 2;
-    c.out = a.out;
-    c.head_dim = a.head_dim;
-    c.n_parts = -1;
-    c.d_pos = a.d_pos;
-    c.pos_bias = a.pos_bias;
-    c.n_ctx = a.n_ctx;
-    c.n_splits = a.n_splits;
-    c.min_tiles = a.min_tiles;
-    c.emit_partial = a.emit_partial;
-    c.peer_bufs = a.peer_bufs;
-    c.gen_push = a.gen_push;
-    c.rank = a.rank;
-    c.world = a.world;
-    c.n_head = a.n_head;
-    c.fused_wait = a.fused_wait;
-    c.status = a.peer_status;
-    c.out_qs = a.out_qs;
-    c.out_scales = a.out_scales;
-    e = launch_dependent(combine_kernel, dim3(a.n_head), kCombineThreads, 0, stream, a.overlap, c);
-    if (launches) *launches += 2;
+    if (launches) *launches += 1;
     return e;
 }
 
 cudaError_t launch_combine_records(const float* parts, int n_parts, float* out, int n_head, int head_dim,
                                    cudaStream_t stream, unsigned long long* launches) {
-    CombineArgs c;
-    const long long rec = head_dim + PART_PAD;
-    c.o_base = parts;
-    c.ml_base = parts + head_dim;
-    c.o_hs = rec;
-    c.o_ss = rec * n_head;
-    c.ml_hs = rec;
-    c.ml_ss = rec * n_head;
-    c.out = out;
-    c.head_dim = head_dim;
-    c.n_parts = n_parts;
-    c.d_pos = nullptr;
-    c.pos_bias = 0;
-    c.n_ctx = 0;
-    c.n_splits = 0;
-    c.min_tiles = 1;
-    c.emit_partial = 0;
-    c.peer_bufs = nullptr;
-    c.gen_push = nullptr;
-    c.rank = 0;
-    c.world = 1;
-    c.n_head = n_head;
-    c.fused_wait = 0;
-    c.status = nullptr;
-    c.out_qs = nullptr;
-    c.out_scales = nullptr;
-    combine_kernel<<<n_head, kCombineThreads, 0, stream>>>(c);
+    combine_records_kernel<<<n_head, 32, 0, stream>>>(parts, n_parts, out, n_head, head_dim);
     if (launches) *launches += 1;
     return cudaGetLastError();
 }
 
 cudaError_t launch_peer_wait_combine(const void* my_buf, int world, float* out, int n_head, int head_dim, int* gen_wait,
-                                     int* status, int overlap, cudaStream_t stream, unsigned long long* launches) {
+                                     int* status, long long wait_cycles, int overlap, cudaStream_t stream,
+                                     unsigned long long* launches) {
     PeerWaitArgs w;
     w.my_buf = reinterpret_cast<const unsigned char*>(my_buf);
     w.out = out;
@@ -740,7 +914,8 @@ cudaError_t launch_peer_wait_combine(const void* my_buf, int world, float* out, 
     w.world = world;
     w.n_head = n_head;
     w.head_dim = head_dim;
-    cudaError_t e = launch_dependent(peer_wait_combine_kernel, dim3(n_head), kPeerWaitThreads, 0, stream, overlap, w);
+    w.wait_cycles = wait_cycles;
+    cudaError_t e = launch_dependent(peer_wait_combine_kernel, dim3(n_head), 32, 0, stream, overlap, w);
     if (launches) *launches += 1;
     return e;
 }

@@ -16,6 +16,7 @@ void* g_decode_ws = nullptr;         // scratch handed over by attn_scratch_assi
 size_t g_decode_ws_bytes = 0;
 void* g_prefill_ws = nullptr;
 size_t g_prefill_ws_bytes = 0;
+bool g_prefill_ws_owned = false;     // allocated here (on demand), not handed over by attn_scratch_assign
 
 inline size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
@@ -25,7 +26,8 @@ void check(int rc, const char* what);
 
 // Hosts that never call init()/attn_scratch_assign() (the reference's model_gpu.cu linked as it is) still work: the
 // first wrapper call initialises the current device; prefill scratch is allocated on demand (prefill is never
-// captured in a graph); decode falls back to the library's built-in scratch block.
+// captured in a graph); decode, which the reference captures in a graph (src/model_gpu.cu:295-316), never allocates:
+// without an assigned block it runs on the library's built-in scratch block.
 // OATTN_DECODE_OVERLAP=0|1|2 in the environment selects the decode launch ordering (oattn_set_decode_overlap).
 void apply_environment() {
     const char* e = getenv("OATTN_DECODE_OVERLAP");
@@ -44,18 +46,34 @@ void ensure_prefill_scratch(int n_head, int n_kv, int head_dim, int batch) {
     if (g_prefill_ws && g_prefill_ws_bytes >= need) return;
     void* p = nullptr;
     check(oattn_scratch_alloc(need, &p), "prefill scratch");
-    g_prefill_ws = p;            // a smaller block handed over earlier stays with its owner
+    // a smaller block allocated here earlier is returned; one handed over by the host stays with its owner
+    if (g_prefill_ws_owned) check(oattn_scratch_free(g_prefill_ws), "prefill scratch (release)");
+    g_prefill_ws = p;
     g_prefill_ws_bytes = need;
+    g_prefill_ws_owned = true;
 }
 
-// Fused decode needs a real workspace (the built-in block serves the unfused call only).
-void ensure_decode_scratch(int n_head, int n_kv, int head_dim) {
+// Decode scratch allocated at a point that is never under stream capture (a prefill call).
+void alloc_decode_scratch_outside_capture(int n_head, int n_kv, int head_dim) {
     if (g_decode_ws) return;
     const size_t need = oattn_decode_workspace_bytes(n_head, n_kv, head_dim);
     void* p = nullptr;
     check(oattn_scratch_alloc(need, &p), "decode scratch");
     g_decode_ws = p;
     g_decode_ws_bytes = need;
+}
+
+// Scratch of a decode call that may be running under stream capture: the assigned block, else the library's built-in
+// block.  Never allocates; a shape too large for the built-in block is a usage error with a clear message.
+void decode_scratch(int n_head, int n_kv, int head_dim, void** ws, size_t* bytes) {
+    if (g_decode_ws) { *ws = g_decode_ws; *bytes = g_decode_ws_bytes; return; }
+    check(oattn_builtin_scratch(ws, bytes), "built-in decode scratch");
+    const size_t need = oattn_decode_workspace_bytes(n_head, n_kv, head_dim);
+    if (need > *bytes) {
+        fprintf(stderr, "[cuda::attention_decode_fused] this shape needs %zu bytes of decode scratch, the built-in block holds %zu: "
+                        "call attn_scratch_assign() once before the first decode call\n", need, *bytes);
+        abort();
+    }
 }
 
 void check(int rc, const char* what) {
@@ -151,6 +169,7 @@ int init_device(int device) {
     return 0;
 }
 
+void attn_flush() { flush_pending(); }
 void set_stream(void* stream) { flush_pending(); s_stream = stream; }
 void attn_set_stream(void* stream) { flush_pending(); s_stream = stream; }
 void attn_fuse_call_sequence(bool on) { flush_pending(); g_fuse_sequence = on ? 1 : 0; }
@@ -164,6 +183,8 @@ void attn_scratch_assign(void* base, int n_head, int n_kv, int head_dim, int max
     flush_pending();
     g_decode_ws = base;
     g_decode_ws_bytes = oattn_decode_workspace_bytes(n_head, n_kv, head_dim);
+    if (g_prefill_ws_owned) check(oattn_scratch_free(g_prefill_ws), "prefill scratch (release)");
+    g_prefill_ws_owned = false;
     g_prefill_ws = static_cast<uint8_t*>(base) + align256(g_decode_ws_bytes);
     g_prefill_ws_bytes = oattn_prefill_workspace_bytes(n_head, n_kv, head_dim, max_batch);
 }
@@ -200,7 +221,7 @@ void flash_attention(const float* q, const uint16_t* kc, const uint16_t* vc, flo
     ensure_ready();
     ensure_prefill_scratch(n_head, n_kv, head_dim, batch);
     if (fuse_sequence()) {
-        ensure_decode_scratch(n_head, n_kv, head_dim);       // prefill is never captured: a safe place to allocate it
+        alloc_decode_scratch_outside_capture(n_head, n_kv, head_dim);       // prefill is never captured: a safe place
         if (sequence_matches(q, kc, vc, n_head, n_kv, head_dim, n_ctx, n_past, batch, nullptr)) {
             const oattn_rope_params rp = {g_rope[0].rope_type, g_rope[0].n_rot, g_rope[0].theta, g_rope[0].ff};
             const PendingStore t = g_store;
@@ -247,9 +268,11 @@ void attention_decode_fused(const float* q, const float* k, const float* v, uint
     const oattn_rope_params rp = {rope_type, n_rot, theta, freq_factors};
     ensure_ready();
     flush_pending();
-    ensure_decode_scratch(n_head, n_kv, head_dim);
-    check(oattn_decode(q, k, v, kc, vc, out, n_head, n_kv, head_dim, n_ctx, d_pos, scale, OATTN_FUSE_ALL, &rp, g_decode_ws,
-                       g_decode_ws_bytes, s_stream), "attention_decode_fused");
+    void* ws = nullptr;
+    size_t ws_bytes = 0;
+    decode_scratch(n_head, n_kv, head_dim, &ws, &ws_bytes);
+    check(oattn_decode(q, k, v, kc, vc, out, n_head, n_kv, head_dim, n_ctx, d_pos, scale, OATTN_FUSE_ALL, &rp, ws, ws_bytes,
+                       s_stream), "attention_decode_fused");
 }
 void attention_prefill_fused(const float* q, const float* k, const float* v, uint16_t* kc, uint16_t* vc, float* out,
                              int n_head, int n_kv, int head_dim, int n_ctx, int n_past, int batch, float scale,
@@ -276,9 +299,11 @@ void attention_decode_fused(const float* q, const float* k, const float* v, uint
     const oattn_ext ext = to_ext(extras);
     ensure_ready();
     flush_pending();
-    ensure_decode_scratch(n_head, n_kv, head_dim);
+    void* ws = nullptr;
+    size_t ws_bytes = 0;
+    decode_scratch(n_head, n_kv, head_dim, &ws, &ws_bytes);
     check(oattn_decode_ex(q, k, v, kc, vc, out, n_head, n_kv, head_dim, n_ctx, d_pos, scale, OATTN_FUSE_ALL, &rp, &ext,
-                          g_decode_ws, g_decode_ws_bytes, s_stream), "attention_decode_fused");
+                          ws, ws_bytes, s_stream), "attention_decode_fused");
 }
 void attention_prefill_fused(const float* q, const float* k, const float* v, uint16_t* kc, uint16_t* vc, float* out,
                              int n_head, int n_kv, int head_dim, int n_ctx, int n_past, int batch, float scale,

@@ -38,9 +38,16 @@ void attn_set_stream(void* stream);
 // recorded, in order.  Visible difference: q and k are not rotated in place any more; turn it on only for a host that,
 // like the reference, does not read them after attention.
 void attn_fuse_call_sequence(bool on);
+// Issues whatever rope / kv_store calls are still recorded, in order.  With fusion on, a host must call this before it
+// launches a kernel of its own that reads q, k or the cache, before it synchronises or ends a stream capture, and
+// before it frees a buffer a recorded call names -- recorded calls are otherwise only issued by the next call
+// through these wrappers.  (The reference's own sequence, where the attention call directly follows, never needs it.)
+void attn_flush();
 
 // Optional.  Without them the first wrapper call initialises the current device, prefill scratch is allocated on
-// demand and decode uses the library's built-in scratch block (oattn_decode_noalloc).
+// demand and decode (fused or not) runs on the library's built-in 2 MiB scratch block: no decode call ever allocates,
+// so all of them may be captured in a CUDA graph as src/model_gpu.cu:295-316 does.  A shape whose decode scratch does
+// not fit the built-in block aborts with a message that asks for attn_scratch_assign().
 size_t attn_scratch_size(int n_head, int n_kv, int head_dim, int max_batch);
 void attn_scratch_assign(void* base, int n_head, int n_kv, int head_dim, int max_batch);
 

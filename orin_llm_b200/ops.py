@@ -262,8 +262,13 @@ def set_prefill_impl(impl):
 
 def set_decode_overlap(mode):
     """0 ordinary launches (default), 1 dependent launches, 2 also prefetch K/V before waiting for the preceding kernel
-    (the caller vouches for the position word and the cache rows; see the C header)."""
+    (the caller vouches for the position word and the cache rows below the newest one; see the C header)."""
     capi.check(capi.lib().oattn_set_decode_overlap(mode))
+
+
+def set_wait_limit_cycles(cycles):
+    """Bound of the device-side waits for the peers' records, in SM clock cycles (default 4e9)."""
+    capi.check(capi.lib().oattn_set_wait_limit_cycles(int(cycles)))
 
 
 def set_decode_min_tiles(tiles):
@@ -271,12 +276,12 @@ def set_decode_min_tiles(tiles):
 
 
 def profile_enable(max_records):
-    """Time the split-KV kernel of the next `max_records` decode calls (0 switches it off)."""
+    """Time the decode kernel of the next `max_records` decode calls (0 switches it off)."""
     capi.check(capi.lib().oattn_profile_enable(max_records))
 
 
 def profile_collect(capacity=65536):
-    """Milliseconds of the split-KV kernel for each decode call recorded since the last collect."""
+    """Milliseconds of the decode kernel for each decode call recorded since the last collect."""
     buf = (ctypes.c_float * capacity)()
     n = ctypes.c_int(0)
     capi.check(capi.lib().oattn_profile_collect(buf, capacity, ctypes.byref(n)))

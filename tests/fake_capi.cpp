@@ -23,6 +23,14 @@ const char* oattn_strerror(int) { return "fake"; }
 const char* oattn_last_cuda_error(void) { return ""; }
 int oattn_init(int device) { g_log += "init/" + std::to_string(device) + ";"; return OATTN_OK; }
 int oattn_scratch_alloc(size_t bytes, void** ptr) { note("scratch_alloc"); *ptr = malloc(bytes); return OATTN_OK; }
+int oattn_scratch_free(void* ptr) { note("scratch_free"); free(ptr); return OATTN_OK; }
+int oattn_builtin_scratch(void** ptr, size_t* bytes) {
+    static char block[8192];
+    note("builtin_scratch");
+    *ptr = block;
+    *bytes = sizeof(block);
+    return OATTN_OK;
+}
 int oattn_set_decode_overlap(int mode) { g_log += "overlap/" + std::to_string(mode) + ";"; return OATTN_OK; }
 size_t oattn_decode_workspace_bytes(int, int, int) { return 4096; }
 size_t oattn_prefill_workspace_bytes(int, int, int, int max_batch) { return 1024 * (size_t)max_batch; }

@@ -59,6 +59,15 @@ void shim_decode_layer_mismatched(float* q, float* k, const float* k_stored, con
     cuda::flash_attention_decode_ind(q, kc, vc, out, n_head, n_kv, hd, n_ctx, d_pos, scale);
 }
 void shim_fuse_call_sequence(int on) { cuda::attn_fuse_call_sequence(on != 0); }
+void shim_flush() { cuda::attn_flush(); }
+// rope(q), rope(k), kv_store of a decode step with no attention call behind them
+void shim_decode_producers_only(float* q, float* k, const float* v, uint16_t* kc, uint16_t* vc, int n_head, int n_kv, int hd,
+                                int n_ctx, const int* d_pos, int rope_type, int n_rot, float theta) {
+    auto rope_ind = rope_type == 1 ? cuda::rope_neox_ind : cuda::rope_normal_ind;
+    rope_ind(q, n_head, hd, n_rot, theta, d_pos, nullptr);
+    rope_ind(k, n_kv, hd, n_rot, theta, d_pos, nullptr);
+    cuda::kv_store_ind(kc, vc, k, v, n_kv, hd, n_ctx, d_pos);
+}
 void shim_kv_shift(uint16_t* kc, uint16_t* vc, int n_layer, int n_kv, int hd, int n_ctx, int n_keep, int shift) {
     cuda::kv_shift(kc, vc, n_layer, n_kv, hd, n_ctx, n_keep, shift);
 }

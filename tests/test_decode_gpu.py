@@ -80,7 +80,7 @@ def test_split_count_invariance(ops):
             ops.set_decode_min_tiles(mt)
             outs.append(run_decode(ops, q[0], K, V, npos, scale))
     finally:
-        ops.set_decode_min_tiles(2)
+        ops.set_decode_min_tiles(1)
     for o in outs[1:]:
         assert np.abs(o - outs[0]).max() < 2e-5
 
@@ -240,7 +240,7 @@ def test_long_context_3b_shape_properties(ops, oracle):
             ops.flash_attention_decode_ind(dev(q), dK, dV, out2, n_head, n_kv, hd, L, d_pos, float(scale))
             torch.cuda.synchronize()
         finally:
-            ops.set_decode_min_tiles(2)
+            ops.set_decode_min_tiles(1)
         assert (out2 - out).abs().max().item() < 2e-5
         del dK, dV
 
@@ -321,3 +321,81 @@ def test_launch_overlap_modes_give_the_same_output(ops, oracle, mode):
         want = oracle.attn_batch(qs[l][None].copy(), ks[l][None].copy(), vs[l][None].copy(), K.astype(np.float32),
                                  V.astype(np.float32), pos, scale, True, 1, hd, 1e6, None)[0]
         assert_close(got[l], want, "mode %d layer %d" % (mode, l))
+
+
+def test_unfused_store_then_decode_under_early_fetch(ops, oracle):
+    """The reference's unfused decode sequence (src/model_gpu.cu:281-282): kv_store_ind writes row *d_pos, the decode call
+    right behind it reads it.  Under launch ordering 2 the decode kernel fetches cache tiles before it waits for the
+    store kernel; the newest row must still be the stored one.  Several layers captured in one graph, compared bit
+    for bit with ordinary launches and with the oracle."""
+    n_head, n_kv, hd, n_ctx, layers, pos = 28, 4, 128, 2048, 5, 1500
+    scale = np.float32(1.0 / np.sqrt(hd))
+    rng = np.random.default_rng(91)
+    caches, qs, ks, vs = [], [], [], []
+    for l in range(layers):
+        q, K, V = make_qkv(910 + l, n_head, n_kv, hd, pos, n_ctx)
+        # the row that the store will overwrite holds a decoy: a stale read would change the result visibly
+        K[:, pos] = np.float16(3.0)
+        V[:, pos] = np.float16(-7.0)
+        caches.append((K, V))
+        qs.append(q[0])
+        ks.append(f16_round(rng.standard_normal((n_kv, hd)).astype(np.float32)))
+        vs.append(f16_round(rng.standard_normal((n_kv, hd)).astype(np.float32)))
+    d_pos = torch.tensor([pos], dtype=torch.int32, device="cuda")
+    dq, dk, dv = dev(np.stack(qs)), dev(np.stack(ks)), dev(np.stack(vs))
+    ws = ops.decode_workspace(n_head, n_kv, hd)
+
+    def run(mode):
+        ops.set_decode_overlap(mode)
+        try:
+            dK = [dev(K) for K, _ in caches]
+            dV = [dev(V) for _, V in caches]
+            out = torch.zeros(layers, n_head, hd, device="cuda")
+            stream = torch.cuda.Stream()
+            stream.wait_stream(torch.cuda.current_stream())
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(stream):
+                ops.set_stream(stream)
+                try:
+                    graph.capture_begin()
+                    for l in range(layers):
+                        ops.kv_store_ind(dK[l], dV[l], dk[l], dv[l], n_kv, hd, n_ctx, d_pos)
+                        ops.flash_attention_decode_ind(dq[l], dK[l], dV[l], out[l], n_head, n_kv, hd, n_ctx, d_pos, float(scale), ws)
+                    graph.capture_end()
+                finally:
+                    ops.set_stream(None)
+            graph.replay()
+            torch.cuda.synchronize()
+            return out.cpu().numpy()
+        finally:
+            ops.set_decode_overlap(0)
+
+    base = run(0)
+    got = run(2)
+    assert np.array_equal(got, base)
+    for l in (0, layers - 1):
+        K, V = caches[l]
+        kc32, vc32 = K.astype(np.float32), V.astype(np.float32)
+        kc32[:, pos] = ks[l]
+        vc32[:, pos] = vs[l]
+        want = oracle.attend(qs[l], kc32, vc32, pos + 1, scale)
+        assert_close(got[l], want, "unfused sequence, early fetch, layer %d" % l)
+
+
+def test_many_workspaces_do_not_share_arrival_counters(ops, oracle):
+    """More distinct workspaces than the library has counter slots, used one after the other and then again: every call
+    must still merge completely (a slot is recycled only when its previous user is at rest)."""
+    n_head, n_kv, hd, npos = 16, 2, 128, 9000
+    q, K, V = make_qkv(77, n_head, n_kv, hd, npos)
+    scale = np.float32(1.0 / np.sqrt(hd))
+    want = oracle.attend(q[0], K.astype(np.float32), V.astype(np.float32), npos, scale)
+    nbytes = ops.decode_workspace(n_head, n_kv, hd).numel()
+    spaces = [torch.empty(nbytes, dtype=torch.uint8, device="cuda") for _ in range(70)]
+    first = None
+    for rnd in range(2):
+        for ws in spaces[:: 1 if rnd == 0 else 7]:
+            got = run_decode(ops, q[0], K, V, npos, float(scale), workspace=ws)
+            if first is None:
+                first = got
+                assert_close(got, want, "first workspace")
+            assert np.array_equal(got, first)

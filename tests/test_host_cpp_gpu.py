@@ -158,11 +158,11 @@ def test_call_sequence_fusion(shim, ops, oracle):
             shim.shim_decode_layer_unfused(dq[t].data_ptr(), dk[t].data_ptr(), dv[t].data_ptr(), kc.data_ptr(), vc.data_ptr(),
                                            out[t].data_ptr(), n_head, n_kv, hd, n_ctx, d_pos.data_ptr(), float(scale), rope_type,
                                            hd, theta)
-            assert ops.launch_count() - l0 == 2
+            assert ops.launch_count() - l0 == 1
         torch.cuda.synchronize()
         assert_close(out.cpu().numpy(), want, "call-sequence fusion")
         assert torch.equal(dq.cpu(), torch.from_numpy(q)), "q must be left as it was"
-        # a sequence whose stored k is not the k that was rotated does not fuse: five launches, q rotated in place
+        # a sequence whose stored k is not the k that was rotated does not fuse: four launches, q rotated in place
         q0, k0, k_other = dev(q[0]), dev(k[0]), dev(k[1])
         kc2 = torch.zeros_like(kc); vc2 = torch.zeros_like(kc)
         o0 = torch.empty(n_head, hd, device="cuda")
@@ -172,7 +172,7 @@ def test_call_sequence_fusion(shim, ops, oracle):
                                           vc2.data_ptr(), o0.data_ptr(), n_head, n_kv, hd, n_ctx, d_pos.data_ptr(), float(scale),
                                           rope_type, hd, theta)
         torch.cuda.synchronize()
-        assert ops.launch_count() - l0 == 5
+        assert ops.launch_count() - l0 == 4
         assert not torch.equal(q0.cpu(), torch.from_numpy(q[0]))
         assert torch.equal(kc2[:, 7].cpu(), torch.from_numpy(k[1]).half())      # the unrotated other k, as asked
     finally:

@@ -32,6 +32,7 @@ def host(tmp_path):
         getattr(L, name).argtypes = [vp] * 6 + [i] * 6 + [f, i, i, f]
     L.shim_decode_layer_mismatched.argtypes = [vp] * 7 + [i] * 4 + [vp, f, i, i, f]
     L.shim_kv_shift.argtypes = [vp, vp, i, i, i, i, i, i]
+    L.shim_decode_producers_only.argtypes = [vp] * 5 + [i] * 4 + [vp, i, i, f]
     return L
 
 
@@ -67,7 +68,29 @@ def test_prefill_allocates_scratch_on_demand_and_grows(host):
     prefill_unfused(host, batch=8)
     assert log(host) == ["rope", "rope", "kv_store", "prefill/0"]
     prefill_unfused(host, batch=64)                                               # larger chunk: a larger block
-    assert log(host) == ["rope", "rope", "kv_store", "scratch_alloc", "prefill/0"]
+    assert log(host) == ["rope", "rope", "kv_store", "scratch_alloc", "scratch_free", "prefill/0"]   # the old one is returned
+
+
+def test_fused_decode_never_allocates(host):
+    """attention_decode_fused may be the first call a host makes, under stream capture (src/model_gpu.cu:295-316):
+    without an assigned block it must run on the built-in scratch block, not allocate."""
+    host.shim_decode_layer_fused(Q, K, V, KC, VC, OUT, *DEC, DPOS, 0.1, 1, 128, 1e6)
+    assert log(host) == ["init/-1", "builtin_scratch", "decode/7"]
+    n = host.shim_scratch_size(12, 2, 128, 64)
+    buf = ctypes.create_string_buffer(n)
+    host.shim_scratch_assign(ctypes.addressof(buf), 12, 2, 128, 64)
+    host.shim_decode_layer_fused(Q, K, V, KC, VC, OUT, *DEC, DPOS, 0.1, 1, 128, 1e6)
+    assert log(host) == ["decode/7"]
+
+
+def test_recorded_calls_without_an_attention_call_are_issued_by_flush(host):
+    host.shim_fuse_call_sequence(1)
+    host.shim_decode_producers_only(Q, K, V, KC, VC, 12, 2, 128, 4096, DPOS, 1, 128, 1e6)
+    assert log(host) == ["init/-1"]                  # recorded, nothing issued yet
+    host.shim_flush()
+    assert log(host) == ["rope", "rope", "kv_store"]
+    host.shim_flush()
+    assert log(host) == []
 
 
 def test_assigned_scratch_is_used(host):

@@ -124,3 +124,57 @@ def test_fused_prologue_on_a_sharded_cache(ops, oracle):
     want2 = oracle.attend(qo, K.astype(np.float32), V.astype(np.float32), n_loc, scale)
     assert_close(out2.cpu().numpy(), want2, "q-only rotation on a slice")
     assert torch.equal(dK2.view(torch.int16), dev(K).view(torch.int16))
+
+
+def test_a_wait_that_runs_out_returns_a_status(ops, oracle):
+    """A rank whose peer is late: the bounded wait runs out after about a millisecond, raises the status word, leaves the
+    output untouched and returns, so the context stays usable.  Once the late record has arrived the same exchange
+    completes, and so does the next one.  (Two emulated ranks on one GPU; nothing waits for a kernel that is not
+    already finished, and no wait is unbounded.)"""
+    from orin_llm_b200.dist import slice_bounds
+    n_head, n_kv, hd, L, world = 16, 2, 128, 4000, 2
+    scale = np.float32(1.0 / np.sqrt(hd))
+    nbytes = ops.peer_buffer_bytes(world, n_head, hd)
+    bufs = [torch.zeros(nbytes, dtype=torch.uint8, device="cuda") for _ in range(world)]
+    states = [torch.zeros(ops.peer_state_bytes(n_head), dtype=torch.uint8, device="cuda") for _ in range(world)]
+    ptrs = torch.tensor([b.data_ptr() for b in bufs], dtype=torch.int64, device="cuda")
+    bounds = slice_bounds(L, world)
+    ops.set_wait_limit_cycles(2_000_000)          # about a millisecond
+    try:
+        for step in range(2):
+            q, K, V = make_qkv(640 + step, n_head, n_kv, hd, L)
+            want = oracle.attend(q[0], K.astype(np.float32), V.astype(np.float32), L, scale)
+            dq = dev(q[0])
+            sl = [(dev(K[:, bounds[r]:bounds[r + 1]]), dev(V[:, bounds[r]:bounds[r + 1]]),
+                   torch.tensor([bounds[r + 1] - bounds[r]], dtype=torch.int32, device="cuda"), bounds[r + 1] - bounds[r])
+                  for r in range(world)]
+
+            def push(r):
+                Kl, Vl, d_len, n_loc = sl[r]
+                ops.attn_decode_partial_push(dq, Kl, Vl, n_head, n_kv, hd, n_loc, d_len, float(scale), ptrs.data_ptr(), r, world,
+                                             states[r])
+            outs = [torch.full((n_head, hd), 123.0, device="cuda") for _ in range(world)]
+            push(0)
+            if step == 0:
+                # rank 1 has not pushed yet: rank 0's wait must give up
+                ops.attn_peer_wait_combine(bufs[0], world, outs[0], n_head, hd, states[0])
+                torch.cuda.synchronize()
+                assert ops.peer_status(states[0], n_head) == 1
+                assert (outs[0] == 123.0).all()
+                # the late rank arrives; its own wait finds both records
+                push(1)
+                ops.attn_peer_wait_combine(bufs[1], world, outs[1], n_head, hd, states[1])
+                torch.cuda.synchronize()
+                assert ops.peer_status(states[1], n_head) == 0
+                assert_close(outs[1].cpu().numpy(), want, "late rank")
+                states[0].view(torch.int32)[2 * n_head] = 0      # the host clears the status word it has handled
+            else:
+                push(1)
+                for r in range(world):
+                    ops.attn_peer_wait_combine(bufs[r], world, outs[r], n_head, hd, states[r])
+                torch.cuda.synchronize()
+                for r in range(world):
+                    assert ops.peer_status(states[r], n_head) == 0
+                    assert_close(outs[r].cpu().numpy(), want, "exchange after a timed-out one, rank %d" % r)
+    finally:
+        ops.set_wait_limit_cycles(4_000_000_000)
