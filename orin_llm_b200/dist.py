@@ -7,9 +7,10 @@ every kv head is cut into `world` contiguous slices, rank r keeping rows
     exchange of the world records                 [n_head][head_dim + 4] fp32 = {O, m, l, 0, 0} per rank
     log-sum-exp merge on every rank
 The exchange is latency-bound (8448 bytes per rank for 16 heads of 128).  Two forms:
-    PeerSplitKVDecoder   the merge kernel stores its record into every rank's exchange buffer over NVLink (peer
-                         stores, every value tagged with the call's generation) and waits for the others' records
-                         in its own buffer: no collective call, two launches per step, graph-capturable
+    PeerSplitKVDecoder   the CTA of the decode launch that finishes a kv head's merge stores the record into every rank's
+                         exchange buffer over NVLink (peer stores, every value tagged with the call's generation) and
+                         waits for the others' records in its own buffer: no collective call, ONE launch per layer
+                         call, graph-capturable
     SplitKVDecoder       oattn_decode_partial -> NCCL all-gather (torch.distributed) -> oattn_combine
 
 The slicing and the gather are plain host logic that also runs on CPU tensors with the gloo
@@ -34,6 +35,9 @@ def slice_bounds(n_rows, world):
 def gather_records(local, world_buf, group=None):
     """All-gather one record per rank.  local: [n_head][hd+4]; world_buf: [world][n_head][hd+4]."""
     world = dist.get_world_size(group) if dist.is_initialized() else 1
+    if world_buf.dim() != local.dim() + 1 or world_buf.shape[0] != world or tuple(world_buf.shape[1:]) != tuple(local.shape):
+        raise ValueError("gather_records: buffer of shape %s does not hold %d records of shape %s" % (
+            tuple(world_buf.shape), world, tuple(local.shape)))
     if world == 1:
         world_buf[0].copy_(local)
         return world_buf
@@ -46,15 +50,19 @@ def gather_records(local, world_buf, group=None):
 
 
 class PeerSplitKVDecoder:
-    """Split-KV decode whose record exchange is done by the kernels themselves: the per-rank merge kernel stores
-    its record into every rank's exchange buffer with plain peer stores over NVLink (every value tagged with the call's
-    generation number), then waits (bounded) until the other ranks' values of this generation have arrived in its own
-    buffer and writes the merged output.  One small kernel after
-    the split kernel, no collective call, graph-capturable; fused=False keeps the wait in a launch of its own.
-    The exchange buffers come from torch's symmetric memory (CUDA VMM mappings of every rank's block); no multicast
-    object is created and no library kernel ever sees a peer pointer."""
+    """Split-KV decode whose record exchange is done by the decode kernel itself: the CTA that finishes a kv head's
+    merge stores the record into every rank's exchange buffer with plain peer stores over NVLink (every value tagged
+    with the call's generation number), then waits (bounded) until the other ranks' values of this generation have
+    arrived in its own buffer and writes the merged output.  One launch per layer call, no collective call,
+    graph-capturable; fused=False keeps the wait in a launch of its own.
+    The exchange buffers come from torch's symmetric memory (CUDA VMM mappings of every rank's block).  torch would also
+    bind such a block to an NVLink multicast object where the hardware has one; TORCH_SYMM_MEM_DISABLE_MULTICAST=1 is set
+    here (unless the caller set it) so that none is created: the kernels use plain peer stores only, and a rank must
+    never exit while bound to a multicast object.  No library kernel ever sees a peer pointer."""
 
     def __init__(self, n_head, n_kv, head_dim, group=None, fused=True):
+        import os
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm_mem
         from . import ops
         self.ops = ops

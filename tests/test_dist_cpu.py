@@ -64,12 +64,25 @@ def _worker(rank, world, port, L, fail_rank):
         assert bounds[0] == 0 and bounds[-1] == L and all(b % 64 == 0 for b in bounds[:-1])
         lo, hi = bounds[rank], bounds[rank + 1]
         local = torch.from_numpy(_record_from_oracle(orc, q[0], K32, V32, lo, hi, scale))
+        if rank == fail_rank:
+            # a rank that has nothing to contribute (its slice was lost) sends the neutral record m = -inf, l = 0
+            local = torch.from_numpy(_record_from_oracle(orc, q[0], K32, V32, 0, 0, scale))
         parts = torch.zeros(world, n_head, hd + 4)
         gather_records(local, parts)
         p = parts.numpy()
         merged = lse_merge([(p[r, :, hd], p[r, :, hd + 1], p[r, :, :hd]) for r in range(world)])
-        want = orc.attend(q[0], K32, V32, L, scale)
+        if fail_rank < 0:
+            want = orc.attend(q[0], K32, V32, L, scale)
+        else:
+            # the merge must equal attention over the rows of the remaining ranks
+            keep = np.concatenate([np.arange(bounds[r], bounds[r + 1]) for r in range(world) if r != fail_rank])
+            want = orc.attend(q[0], np.ascontiguousarray(K32[:, keep]), np.ascontiguousarray(V32[:, keep]), len(keep), scale)
         assert_close(merged, want, "rank %d merged" % rank)
+        # a buffer sized for another world size is refused before any communication
+        with pytest.raises(ValueError):
+            gather_records(local, torch.zeros(world + 1, n_head, hd + 4))
+        with pytest.raises(ValueError):
+            gather_records(local[:, :-1], parts)
         # every rank holds the same gathered records
         chk = [torch.zeros_like(parts) for _ in range(world)]
         dist.all_gather(chk, parts)
@@ -82,6 +95,12 @@ def _worker(rank, world, port, L, fail_rank):
 def test_split_kv_exchange_gloo(world, L):
     port = _free_port()
     mp.spawn(_worker, args=(world, port, L, -1), nprocs=world, join=True)
+
+
+@pytest.mark.parametrize("world,fail_rank", [(2, 1), (4, 2)])
+def test_a_rank_with_a_neutral_record_drops_out_of_the_merge(world, fail_rank):
+    port = _free_port()
+    mp.spawn(_worker, args=(world, port, 1000, fail_rank), nprocs=world, join=True)
 
 
 def test_slice_bounds_properties():
