@@ -9,7 +9,8 @@
  *
  * Conventions
  *   - Every pointer is a DEVICE pointer unless the comment says "host".
- *   - The caller owns every buffer; nothing here allocates, frees or synchronises.
+ *   - The caller owns every buffer; the attention calls allocate nothing, free nothing and never synchronise
+ *     (only the set-up helpers oattn_scratch_alloc/free and the memory-placement group do).
  *   - `stream` is a cudaStream_t passed as void* (the reference does the same in
  *     cuda::set_stream, src/kernels.h:10).  Every call is asynchronous on that stream and may
  *     be recorded into a CUDA graph: launch shapes never depend on the token position, which
@@ -81,6 +82,25 @@ int oattn_scratch_free(void* ptr);
  * when oattn_decode_workspace_bytes() fits.  No allocation, no stream operation.  The same sharing rule applies: calls
  * that use the block must not overlap on the GPU.  No counterpart in the reference. */
 int oattn_builtin_scratch(void** ptr, size_t* bytes);
+/* ---- memory placement for a discrete GPU (set-up time only; these are the entry points that allocate) -------------
+ * The reference was written for a unified-memory Orin: the GPU reads the weights through a zero-copy mapping of the
+ * memory-mapped model file (src/model_gpu.cu:96-149), writes the logits into mapped host memory (:210-211) and never
+ * clears its KV cache (:232-235).  On a B200 the first two put PCIe on the path of every token, the third leaves NaN
+ * bit patterns in rows that whole-tile loads touch.  These helpers are what the three places call instead.
+ *   oattn_weights_place      `bytes` of device memory holding a copy of host[0, bytes) (cudaMalloc + one blocking copy);
+ *                            a tensor at host + off is then at *dev + off.  Replaces cudaHostRegister +
+ *                            cudaHostGetDevicePointer.  Release with oattn_scratch_free.
+ *   oattn_logits_alloc       a device buffer for the output head to write and a pinned host buffer of the same size;
+ *   oattn_copy_to_host_async the copy between them on `stream` (a memcpy node when the stream is being captured: the
+ *                            decode graph then ends with it), replacing the mapped-host write of every logit;
+ *   oattn_logits_free        frees the pair.
+ *   oattn_device_clear       zero-fills device memory and waits (once, for the KV cache right after its allocation). */
+int oattn_weights_place(const void* host, size_t bytes, void** dev);
+int oattn_logits_alloc(size_t bytes, void** dev, void** pinned_host);
+int oattn_logits_free(void* dev, void* pinned_host);
+int oattn_copy_to_host_async(void* pinned_host, const void* dev, size_t bytes, void* stream);
+int oattn_device_clear(void* dev, size_t bytes);
+
 /* Number of SMs of the initialised device (0 before oattn_init). */
 int oattn_sm_count(void);
 

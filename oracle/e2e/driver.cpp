@@ -8,6 +8,13 @@
 // then G single-token steps.  With --force FILE the token fed at each step comes from FILE (teacher forcing), so that
 // several builds can be compared step by step even after their greedy choices diverge; the build's own argmax is
 // still recorded.  --warmup runs an untimed pass first, so that one-time costs stay out of TTFT and TPOT.
+// --top2-out FILE writes, for the point after the prompt and after every step, the two largest logits (the margin that
+// says how much a top-1 disagreement means).
+// Built with -DE2E_ATTN_HOOK against the CPU model source with two hook calls inserted (oracle/Makefile, target
+// e2e_cpu_dump; the arithmetic is untouched), --attn-out FILE records what every layer's attention consumed and produced:
+// for every token k and v before RoPE, and from position --attn-from on also q before RoPE, q and k after it and the
+// attention output.  Record = int32 {stage, layer, n_past, nq, nkv} + floats: stage 0 -> q[nq] k[nkv] v[nkv];
+// stage 1 -> q_rot[nq] k_rot[nkv] attn[nq]  (nq = 0: k and v only).
 #include <chrono>
 #include <cstdint>
 #include <cstdio>
@@ -19,8 +26,35 @@
 #include "gguf.h"
 #include "model.h"
 
+#ifdef E2E_ATTN_HOOK
+static FILE* g_attn_f = nullptr;
+static int g_attn_from = 0;
+extern "C" void e2e_attn_hook(int stage, int layer, int n_past, const float* q, const float* k, const float* v,
+                              const float* attn, int nq, int nkv) {
+    if (!g_attn_f) return;
+    const bool full = n_past >= g_attn_from;
+    if (stage == 1 && !full) return;
+    const int32_t head[5] = {stage, layer, n_past, full ? nq : 0, nkv};
+    fwrite(head, sizeof(int32_t), 5, g_attn_f);
+    if (full) fwrite(q, sizeof(float), nq, g_attn_f);
+    fwrite(k, sizeof(float), nkv, g_attn_f);
+    if (stage == 0) fwrite(v, sizeof(float), nkv, g_attn_f);
+    else fwrite(attn, sizeof(float), nq, g_attn_f);
+}
+#endif
+
 static double now_ms() {
     return std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now().time_since_epoch()).count();
+}
+
+static void top2(const float* x, int n, float* out) {
+    float a = -1e30f, b = -1e30f;
+    for (int i = 0; i < n; ++i) {
+        if (x[i] > a) { b = a; a = x[i]; }
+        else if (x[i] > b) b = x[i];
+    }
+    out[0] = a;
+    out[1] = b;
 }
 
 static int argmax(const float* x, int n) {
@@ -31,7 +65,8 @@ static int argmax(const float* x, int n) {
 }
 
 int main(int argc, char** argv) {
-    std::string path, force, tokens_out, logits_out;
+    std::string path, force, tokens_out, logits_out, top2_out, attn_out;
+    int attn_from = 0;
     int n_prompt = 45, n_gen = 16, n_ctx = 4096, batch = 512;
     uint64_t seed = 7;
     bool warmup = false;
@@ -48,6 +83,9 @@ int main(int argc, char** argv) {
         else if (a == "--warmup") warmup = true;
         else if (a == "--tokens-out") tokens_out = next();
         else if (a == "--logits-out") logits_out = next();
+        else if (a == "--top2-out") top2_out = next();
+        else if (a == "--attn-out") attn_out = next();
+        else if (a == "--attn-from") attn_from = atoi(next().c_str());
         else { fprintf(stderr, "unknown argument %s\n", a.c_str()); return 2; }
     }
     if (path.empty()) { fprintf(stderr, "usage: driver --model file.gguf [--prompt P --gen G --ctx C --batch B]\n"); return 2; }
@@ -83,6 +121,17 @@ int main(int argc, char** argv) {
         model.forward(prompt[0], n > 1 ? n : 0);
     }
 
+#ifdef E2E_ATTN_HOOK
+    if (!attn_out.empty()) {
+        g_attn_f = fopen(attn_out.c_str(), "wb");
+        g_attn_from = attn_from;
+    }
+#else
+    (void)attn_from;
+    if (!attn_out.empty()) { fprintf(stderr, "--attn-out needs the build with the attention hooks (e2e_cpu_dump)\n"); return 2; }
+#endif
+    std::vector<float> margins;               // top-1 and top-2 logit after the prompt and after every step
+
     // prefill
     const double t0 = now_ms();
     const float* logits = nullptr;
@@ -94,6 +143,8 @@ int main(int argc, char** argv) {
     std::vector<float> first_logits(logits, logits + n_vocab);
     std::vector<int32_t> own;                 // this build's argmax after the prompt and after every step
     own.push_back(argmax(logits, n_vocab));
+    margins.resize(2);
+    top2(logits, n_vocab, margins.data());
 
     // decode
     std::vector<double> step_ms;
@@ -104,6 +155,16 @@ int main(int argc, char** argv) {
         logits = model.forward(tok, n_past++);
         step_ms.push_back(now_ms() - t1);
         own.push_back(argmax(logits, n_vocab));
+        margins.resize(margins.size() + 2);
+        top2(logits, n_vocab, margins.data() + margins.size() - 2);
+    }
+#ifdef E2E_ATTN_HOOK
+    if (g_attn_f) { fclose(g_attn_f); g_attn_f = nullptr; }
+#endif
+    if (!top2_out.empty()) {
+        FILE* f = fopen(top2_out.c_str(), "wb");
+        fwrite(margins.data(), sizeof(float), margins.size(), f);
+        fclose(f);
     }
     double tpot = 0.0, tpot_rest = 0.0;
     for (size_t i = 0; i < step_ms.size(); ++i) {

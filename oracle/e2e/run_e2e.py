@@ -29,7 +29,7 @@ import make_gguf  # noqa: E402
 
 
 def binaries():
-    return {n: os.path.join(REFDIR, n) for n in ("e2e_cpu", "e2e_ref", "e2e_ref_zerocopy", "e2e_b200")}
+    return {n: os.path.join(REFDIR, n) for n in ("e2e_cpu", "e2e_ref", "e2e_ref_zerocopy", "e2e_b200", "e2e_b200_placed")}
 
 
 def available():
@@ -63,19 +63,63 @@ def compare(a, b):
             "logit_scale": float(np.abs(a["logits"]).max())}
 
 
+def against_golden(r, gold):
+    """A GPU build that was fed the CPU oracle's tokens: where does its own top-1 agree with the oracle's, and how
+    large was the oracle's top-1 - top-2 margin where it does not."""
+    n = min(len(r["tokens"]), len(gold["tokens"]))
+    same = r["tokens"][:n] == gold["tokens"][:n]
+    margin = gold["top2"][:n, 0] - gold["top2"][:n, 1]
+    idx, val = gold["head_idx"], gold["head_val"]
+    d = np.abs(np.take_along_axis(r["logits"], idx, axis=1) - val)
+    return {"top1_agreement": float(same.mean()), "points_compared": int(n),
+            "oracle_margin_median": float(np.median(margin)),
+            "oracle_margin_at_disagreements": [float(x) for x in margin[~same]],
+            "max_logit_diff_on_oracle_top64_after_prompt": float(d[0].max()),
+            "max_logit_diff_on_oracle_top64_after_last_step": float(d[1].max()),
+            "logit_scale": float(np.abs(val).max())}
+
+
+def run_golden(config, timeout=1800, model=None):
+    """An end-to-end configuration whose CPU-oracle run is stored in tests/golden/e2e_<config>_cpu.npz
+    (tests/golden/make_e2e_golden.py): writes the same synthetic model, runs the reference's GPU build and the drop-in
+    (call by call, and with call-sequence fusion) on the oracle's token sequence, and compares their top-1 choices and
+    logits with the oracle's.  Returns a dict with TTFT / TPOT of every build as well."""
+    gpath = os.path.join(os.path.dirname(os.path.dirname(HERE)), "tests", "golden", "e2e_%s_cpu.npz" % config)
+    g = np.load(gpath)
+    cfg = json.loads(str(g["params"]))
+    gold = {k: g[k] for k in ("tokens", "top2", "head_idx", "head_val")}
+    args = parser().parse_args(["--arch", cfg["arch"], "--prompt", str(cfg["prompt"]), "--gen", str(cfg["gen"]), "--ctx",
+                                str(cfg["ctx"]), "--batch", str(cfg["batch"]), "--seed", str(cfg["seed"]), "--timeout", str(timeout)])
+    exe = binaries()
+    out = {"config": config, **cfg, "oracle_run": json.loads(str(g["run"]))}
+    with tempfile.TemporaryDirectory() as tmp:
+        if model is None:
+            model = os.path.join(tmp, "model.gguf")
+            make_gguf.write_model(model, dict(make_gguf.ARCHS[cfg["arch"]]), seed=cfg["model_seed"], quant=cfg["quant"])
+        forced = os.path.join(tmp, "forced.bin")
+        gold["tokens"][:cfg["gen"]].astype(np.int32).tofile(forced)
+        builds = {"reference_gpu": (exe["e2e_ref"], None),
+                  "b200_dropin": (exe["e2e_b200_placed"] if os.path.exists(exe["e2e_b200_placed"]) else exe["e2e_b200"], None),
+                  "b200_dropin_fused_sequence": (exe["e2e_b200"], {"OATTN_FUSE_CALL_SEQUENCE": "1"})}
+        for name, (binary, env) in builds.items():
+            r = run_build(binary, model, tmp, name, args, forced, env=env)
+            out[name] = {**timing(r), "vs_cpu_oracle": against_golden(r, gold)}
+    return out
+
+
 def timing(r):
     return {k: r[k] for k in ("ttft_ms", "tpot_ms", "tpot_ms_after_first", "n_ctx")}
 
 
 def run(args):
     exe = binaries()
-    out = {"arch": args.arch, "layers": args.layers, "prompt": args.prompt, "gen": args.gen, "batch": args.batch}
+    out = {"arch": args.arch, "quant": args.quant, "layers": args.layers, "prompt": args.prompt, "gen": args.gen, "batch": args.batch}
     with tempfile.TemporaryDirectory() as tmp:
         model = os.path.join(tmp, "model.gguf")
         cfg = dict(make_gguf.ARCHS[args.arch])
         if args.layers:
             cfg["n_layer"] = args.layers
-        make_gguf.write_model(model, cfg, seed=args.model_seed)
+        make_gguf.write_model(model, cfg, seed=args.model_seed, quant=args.quant)
         ref = run_build(exe["e2e_ref"], model, tmp, "ref", args)
         forced = os.path.join(tmp, "forced.bin")
         ref["tokens"][:args.gen].astype(np.int32).tofile(forced)
@@ -86,6 +130,14 @@ def run(args):
             ov = run_build(exe["e2e_b200"], model, tmp, "b200o", args, forced,
                            env={"OATTN_FUSE_CALL_SEQUENCE": "1", "OATTN_DECODE_OVERLAP": str(args.overlap)})
             out["b200_dropin_fused_sequence_overlap%d" % args.overlap] = timing(ov)
+        if os.path.exists(exe["e2e_b200_placed"]):
+            # the same drop-in with the memory placement done in the source of model_gpu.cu (orin_llm_b200/host/placement.h)
+            # instead of by the test-only interposer: must give the same logits, bit for bit
+            placed = run_build(exe["e2e_b200_placed"], model, tmp, "b200p", args, forced)
+            out["b200_dropin_source_level_placement"] = timing(placed)
+            out["source_level_placement_vs_interposed"] = {
+                "logits_identical": bool(np.array_equal(placed["logits"], b200["logits"])),
+                "tokens_identical": bool(np.array_equal(placed["tokens"], b200["tokens"]))}
         out["reference_gpu"] = timing(ref)
         out["b200_dropin"] = timing(b200)
         out["b200_dropin_fused_sequence"] = timing(fused)
@@ -114,6 +166,9 @@ def parser():
     ap.add_argument("--batch", type=int, default=512)
     ap.add_argument("--seed", type=int, default=7)
     ap.add_argument("--model-seed", type=int, default=1234)
+    ap.add_argument("--quant", default="q8_0", choices=["q8_0", "q4_k_m"])
+    ap.add_argument("--golden", default=None, choices=["cfg1", "cfg5"],
+                    help="run the configuration whose CPU-oracle run is stored under tests/golden/ and compare with it")
     ap.add_argument("--cpu", action="store_true")
     ap.add_argument("--zerocopy", action="store_true")
     ap.add_argument("--no-warmup", action="store_true")
@@ -124,4 +179,5 @@ def parser():
 
 
 if __name__ == "__main__":
-    print(json.dumps(run(parser().parse_args())))
+    _a = parser().parse_args()
+    print(json.dumps(run_golden(_a.golden, _a.timeout) if _a.golden else run(_a)))

@@ -31,10 +31,21 @@ def _fp(a):
     return a.ctypes.data_as(_f32p)
 
 
-def build(ref_root="/root/reference"):
+def reference_root():
+    """Where the reference checkout lies: $ORIN_LLM_REFERENCE, else a directory `reference` beside this repository.
+    None when neither holds its sources."""
+    cands = [os.environ.get("ORIN_LLM_REFERENCE"), os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")]
+    for c in cands:
+        if c and os.path.isfile(os.path.join(c, "src", "model_cpu.cpp")):
+            return os.path.abspath(c)
+    return None
+
+
+def build(ref_root=None):
     """Compile the C restatement, and the reference harness when the reference tree is present."""
     subprocess.check_call(["make", "-s", "-C", HERE, "all"])
-    if os.path.isdir(os.path.join(ref_root, "src")):
+    ref_root = ref_root or reference_root()
+    if ref_root:
         subprocess.check_call(["make", "-s", "-C", HERE, "ref", "REF=" + ref_root])
         try:     # optional: the GPU-side cross-check needs nvcc and a minute of compile time
             subprocess.check_call(["make", "-s", "-C", HERE, "refcuda", "REF=" + ref_root])
@@ -141,6 +152,8 @@ class RefLib:
         L.ref_attend.argtypes = [_f32p, _f32p, _f32p, _f32p, _i, _i, _i, _i, _i, _f, _f32p]
         L.ref_attend_mt.argtypes = [_f32p, _f32p, _f32p, _f32p, _i, _i, _i, _i, _i, _f, _i]
         L.ref_attend_mt.restype = _i
+        if hasattr(L, "ref_dequantize_row"):
+            L.ref_dequantize_row.argtypes = [_i, ctypes.c_void_p, _f32p, ctypes.c_longlong]
         L.ref_attend_chunk_mt.argtypes = [_f32p, _f32p, _f32p, _f32p, _i, _i, _i, _i, _i, _i, _f, _i]
         L.ref_attend_chunk_mt.restype = _i
         L.ref_forward_probe.argtypes = [_f32p, _i, _i, _i, _i, _i, _i, _i, _f, _f32p] + [_f32p] * 6
@@ -162,6 +175,13 @@ class RefLib:
         self.L.ref_attend(_fp(q), _fp(kcache), _fp(vcache), _fp(out), n_head, n_kv, d, n_ctx, npos, scale,
                           _fp(score))
         return out
+
+    def dequantize_row(self, ggml_type, raw, n_elems):
+        """The reference's dequantize_row on a buffer of quantised blocks (uint8 array) -> fp32 [n_elems]."""
+        raw = np.ascontiguousarray(raw, np.uint8)
+        y = np.empty(n_elems, np.float32)
+        self.L.ref_dequantize_row(int(ggml_type), raw.ctypes.data_as(ctypes.c_void_p), _fp(y), n_elems)
+        return y
 
     def attend_mt(self, q, kcache, vcache, npos, scale, max_threads):
         n_head, d = q.shape

@@ -57,6 +57,12 @@ static int probe_impl(const float* x_in, int n_tok, int n_head, int n_kv, int d,
 
 extern "C" {
 
+// The reference's own weight dequantisation (src/model_cpu.cpp:142-158): `type` is the ggml type number.  Used to check
+// the synthetic GGUF writer's K-quant blocks.
+void ref_dequantize_row(int type, const void* x, float* y, long long k) {
+    llm::dequantize_row((llm::DType)type, x, y, (int64_t)k);
+}
+
 void ref_rope(float* x, int rope_type, int n_rot, float theta, int pos, const float* freq_factors) {
     if (rope_type == 1) llm::rope_neox(x, n_rot, theta, pos, freq_factors);
     else                llm::rope_normal(x, n_rot, theta, pos, freq_factors);

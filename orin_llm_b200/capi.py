@@ -18,7 +18,8 @@ PART_PAD = 4
 
 # Every symbol include/orin_attn_b200.h declares.
 EXPORTS = [
-    "oattn_strerror", "oattn_last_cuda_error", "oattn_init", "oattn_scratch_alloc", "oattn_scratch_free", "oattn_builtin_scratch", "oattn_sm_count", "oattn_rope",
+    "oattn_strerror", "oattn_last_cuda_error", "oattn_init", "oattn_scratch_alloc", "oattn_scratch_free", "oattn_builtin_scratch", "oattn_weights_place", "oattn_logits_alloc", "oattn_logits_free",
+    "oattn_copy_to_host_async", "oattn_device_clear", "oattn_sm_count", "oattn_rope",
     "oattn_kv_store", "oattn_kv_shift", "oattn_decode_workspace_bytes", "oattn_decode",
     "oattn_decode_ex", "oattn_prefill_ex", "oattn_decode_noalloc_max_bytes", "oattn_decode_noalloc",
     "oattn_decode_partial", "oattn_combine", "oattn_peer_buffer_bytes", "oattn_peer_state_bytes",
@@ -70,6 +71,12 @@ def lib():
     L.oattn_scratch_alloc.argtypes = [sz, ctypes.POINTER(ctypes.c_void_p)]
     L.oattn_scratch_free.argtypes = [vp]
     L.oattn_builtin_scratch.argtypes = [ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(sz)]
+    pvp = ctypes.POINTER(ctypes.c_void_p)
+    L.oattn_weights_place.argtypes = [vp, sz, pvp]
+    L.oattn_logits_alloc.argtypes = [sz, pvp, pvp]
+    L.oattn_logits_free.argtypes = [vp, vp]
+    L.oattn_copy_to_host_async.argtypes = [vp, vp, sz, vp]
+    L.oattn_device_clear.argtypes = [vp, sz]
     L.oattn_rope.argtypes = [vp, i, i, i, i, f, i, i, vp, vp, vp]
     L.oattn_kv_store.argtypes = [vp, vp, vp, vp, i, i, i, i, i, vp, vp]
     L.oattn_kv_shift.argtypes = [vp, vp, i, i, i, i, i, i, vp]

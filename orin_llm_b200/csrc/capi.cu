@@ -133,6 +133,53 @@ int oattn_builtin_scratch(void** ptr, size_t* bytes) {
     return OATTN_OK;
 }
 
+// ---- memory placement for a discrete GPU ---------------------------------------------------------------------
+int oattn_weights_place(const void* host, size_t bytes, void** dev) {
+    if (!host || !dev || bytes == 0) return OATTN_ERR_ARG;
+    if (!device_ready()) return OATTN_ERR_DEVICE;
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, bytes);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(weights)");
+    e = cudaMemcpy(p, host, bytes, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) { cudaFree(p); return cuda_fail(e, "cudaMemcpy(weights)"); }
+    *dev = p;
+    return OATTN_OK;
+}
+
+int oattn_logits_alloc(size_t bytes, void** dev, void** pinned_host) {
+    if (!dev || !pinned_host || bytes == 0) return OATTN_ERR_ARG;
+    if (!device_ready()) return OATTN_ERR_DEVICE;
+    void* d = nullptr;
+    void* h = nullptr;
+    cudaError_t e = cudaMalloc(&d, bytes);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc(logits)");
+    e = cudaHostAlloc(&h, bytes, cudaHostAllocDefault);
+    if (e != cudaSuccess) { cudaFree(d); return cuda_fail(e, "cudaHostAlloc(logits)"); }
+    *dev = d;
+    *pinned_host = h;
+    return OATTN_OK;
+}
+
+int oattn_logits_free(void* dev, void* pinned_host) {
+    cudaError_t e = cudaSuccess;
+    if (dev) e = cudaFree(dev);
+    if (pinned_host && e == cudaSuccess) e = cudaFreeHost(pinned_host);
+    return e == cudaSuccess ? OATTN_OK : cuda_fail(e, "logits free");
+}
+
+int oattn_copy_to_host_async(void* pinned_host, const void* dev, size_t bytes, void* stream) {
+    if (!pinned_host || !dev) return OATTN_ERR_ARG;
+    cudaError_t e = cudaMemcpyAsync(pinned_host, dev, bytes, cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+    return e == cudaSuccess ? OATTN_OK : cuda_fail(e, "cudaMemcpyAsync(device to host)");
+}
+
+int oattn_device_clear(void* dev, size_t bytes) {
+    if (!dev) return OATTN_ERR_ARG;
+    cudaError_t e = cudaMemset(dev, 0, bytes);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    return e == cudaSuccess ? OATTN_OK : cuda_fail(e, "cudaMemset");
+}
+
 int oattn_sm_count(void) { const DeviceState* d = cur_dev(); return d ? d->sm_count : 0; }
 
 int oattn_rope(float* x, int rows, int head_dim, int rope_type, int n_rot, float theta, int n_past, int heads,

@@ -1,6 +1,7 @@
 // Definitions of the reference-named wrappers on top of the C ABI.  Plain C++ (no CUDA headers):
 // everything device-side lives behind include/orin_attn_b200.h.
 #include "kernels.h"
+#include "placement.h"
 
 #include <stdio.h>
 #include <stdlib.h>
@@ -315,6 +316,59 @@ void attention_prefill_fused(const float* q, const float* k, const float* v, uin
     ensure_prefill_scratch(n_head, n_kv, head_dim, batch);
     check(oattn_prefill_ex(q, k, v, kc, vc, out, n_head, n_kv, head_dim, n_ctx, n_past, batch, scale, OATTN_FUSE_ALL, &rp, &ext,
                            g_prefill_ws, g_prefill_ws_bytes, s_stream), "attention_prefill_fused");
+}
+
+// ---- memory placement (placement.h) ------------------------------------------------------------------------------
+namespace {
+const unsigned char* g_w_host = nullptr;
+unsigned char* g_w_dev = nullptr;
+size_t g_w_bytes = 0;
+}
+
+void place_weights(const void* host_base, size_t bytes) {
+    ensure_ready();
+    if (g_w_dev) release_weights();
+    void* d = nullptr;
+    check(oattn_weights_place(host_base, bytes, &d), "place_weights");
+    g_w_host = static_cast<const unsigned char*>(host_base);
+    g_w_dev = static_cast<unsigned char*>(d);
+    g_w_bytes = bytes;
+}
+
+void* placed_weight(const void* host_ptr) {
+    const unsigned char* h = static_cast<const unsigned char*>(host_ptr);
+    if (!g_w_dev || h < g_w_host || h >= g_w_host + g_w_bytes) {
+        fprintf(stderr, "[cuda::placed_weight] %p lies outside the placed range\n", host_ptr);
+        abort();
+    }
+    return g_w_dev + (h - g_w_host);
+}
+
+void release_weights() {
+    if (g_w_dev) check(oattn_scratch_free(g_w_dev), "release_weights");
+    g_w_dev = nullptr;
+    g_w_host = nullptr;
+    g_w_bytes = 0;
+}
+
+void logits_alloc(size_t bytes, float** d_logits, float** h_logits) {
+    ensure_ready();
+    void* d = nullptr;
+    void* h = nullptr;
+    check(oattn_logits_alloc(bytes, &d, &h), "logits_alloc");
+    *d_logits = static_cast<float*>(d);
+    *h_logits = static_cast<float*>(h);
+}
+
+void logits_fetch(float* h_logits, const float* d_logits, size_t bytes) {
+    check(oattn_copy_to_host_async(h_logits, d_logits, bytes, s_stream), "logits_fetch");
+}
+
+void logits_free(float* d_logits, float* h_logits) { check(oattn_logits_free(d_logits, h_logits), "logits_free"); }
+
+void kv_cache_clear(void* base, size_t bytes) {
+    ensure_ready();
+    check(oattn_device_clear(base, bytes), "kv_cache_clear");
 }
 
 } // namespace llm::cuda

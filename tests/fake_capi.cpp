@@ -31,6 +31,11 @@ int oattn_builtin_scratch(void** ptr, size_t* bytes) {
     *bytes = sizeof(block);
     return OATTN_OK;
 }
+int oattn_weights_place(const void*, size_t bytes, void** dev) { note("weights_place"); *dev = malloc(bytes); return OATTN_OK; }
+int oattn_logits_alloc(size_t bytes, void** dev, void** host) { note("logits_alloc"); *dev = malloc(bytes); *host = malloc(bytes); return OATTN_OK; }
+int oattn_logits_free(void* dev, void* host) { note("logits_free"); free(dev); free(host); return OATTN_OK; }
+int oattn_copy_to_host_async(void*, const void*, size_t, void*) { note("copy_to_host"); return OATTN_OK; }
+int oattn_device_clear(void*, size_t) { note("device_clear"); return OATTN_OK; }
 int oattn_set_decode_overlap(int mode) { g_log += "overlap/" + std::to_string(mode) + ";"; return OATTN_OK; }
 size_t oattn_decode_workspace_bytes(int, int, int) { return 4096; }
 size_t oattn_prefill_workspace_bytes(int, int, int, int max_batch) { return 1024 * (size_t)max_batch; }

@@ -27,6 +27,10 @@ def test_reference_model_on_dropped_in_attention():
         # logits of the whole model: both GPU builds quantise activations to int8 for their GEMVs, which sets the noise
         # floor (the reference's own GPU path differs from its CPU path by the same amount)
         assert c["max_logit_diff_after_last_step"] <= 0.05 * c["logit_scale"], (name, c)
+    if "source_level_placement_vs_interposed" in r:
+        # weights / logits / KV placement done by edits to model_gpu.cu (host/placement.h) instead of the interposer
+        assert r["source_level_placement_vs_interposed"] == {"logits_identical": True, "tokens_identical": True}
+        assert 0 < r["b200_dropin_source_level_placement"]["tpot_ms_after_first"] < 50
     floor = r["reference_gpu_vs_reference_cpu"]["max_logit_diff_after_last_step"]
     assert r["b200_vs_reference_cpu"]["max_logit_diff_after_last_step"] <= 1.5 * floor + 1e-3
     for name in ("reference_gpu", "b200_dropin", "b200_dropin_fused_sequence"):
