@@ -557,6 +557,53 @@ def bench_decode(D, args, w, name, steps, warmup, exchange_arg="none", with_ref_
     return res
 
 
+def bench_kv_shift(args, reps=5):
+    """Context rolling (cuda::kv_shift, src/kernels.cu:1682-1700) on the Llama-3-8B cache at n_ctx 8192 (1 GiB of K and V):
+    drop the first 4096 rows of every layer and kv head, slide the rest down, clear the tail.  GB/s = bytes read + bytes
+    written / time; next to it the reference's own kernel (one thread per column walking the rows serially) on the same
+    cache when it was compiled."""
+    import torch
+    from orin_llm_b200 import ops
+    n_layer, n_kv, n_ctx, hd, n_keep, shift = 32, 8, 8192, 128, 0, 4096
+    cache = ops.KVCache(n_layer, n_kv, n_ctx, hd)
+    cache.buf.normal_()
+    moved = (n_ctx - shift - n_keep) * hd * 2 * n_kv * n_layer * 2      # bytes that change place (K and V)
+    cleared = shift * hd * 2 * n_kv * n_layer * 2
+    traffic = 2 * moved + cleared
+    sampler = ClockSampler(0)
+
+    def timed(fn):
+        fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+    sampler.start()
+    ms = timed(lambda: ops.kv_shift(cache.k, cache.v, n_layer, n_kv, hd, n_ctx, n_keep, shift))
+    clocks = sampler.stop()
+    peaks, peak_kind = measured_peaks()
+    res = {"value": traffic / (ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": ms, "steps": reps,
+           "config": {"cache_bytes": int(cache.buf.numel() * 2), "n_layer": n_layer, "n_kv": n_kv, "n_ctx": n_ctx, "n_keep": n_keep,
+                      "shift": shift, "l2": "the cache (1 GiB) is larger than L2"},
+           "roofline": {"bound": "hbm", "achieved": traffic / (ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                        "frac": traffic / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], "traffic": None,
+                        "algorithmic_bytes_per_launch": traffic, "kernel": "kv_shift_kernel",
+                        "peak_source": peak_kind + " (MEASURED_PEAKS.json hbm_gbs)"},
+           "clocks": clocks, "gpu_launches": reps + 1, "reference_cuda_kernel": None}
+    if not args.no_ref_cuda:
+        from oracle.oracle import RefCuda
+        if RefCuda.available():
+            rc = RefCuda()
+            r_ms = timed(lambda: rc.kv_shift(cache.k, cache.v, n_layer, n_kv, hd, n_ctx, n_keep, shift))
+            res["reference_cuda_kernel"] = {"value": traffic / (r_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_call": r_ms,
+                                            "kernel": "kv_shift of the reference (src/kernels.cu:1682-1700), compiled for sm_100a"}
+    return res
+
+
 def free_device_memory():
     import gc
     import torch
@@ -605,6 +652,10 @@ def run_b200(args, w):
             free_device_memory()
             secondary[name] = {k: r[k] for k in ("value", "unit", "ms_per_step", "steps", "roofline", "clocks", "gpu_launches")}
             secondary[name]["config"] = {k: r["config"][k] for k in ("chunk", "kv_offset", "layers_per_step", "l2")}
+
+        r = bench_kv_shift(args)
+        secondary["kv_shift_8b_ctx8192"] = r
+        free_device_memory()
 
     cpu = None
     if D.world == 1 and not args.no_cpu_baseline:

@@ -238,6 +238,13 @@ int oattn_set_wait_limit_cycles(long long cycles);
  *                32 consecutive values d = max|x| / 127, q = round-half-away(x / d) (0 for an all-zero group); int8
  *                [n_head*head_dim] and fp32 [n_head*head_dim/32], laid out as scratch_assign does
  *                (src/kernels.cu:1763-1776).  With these set, `out` may be NULL.
+ *   out_mmq, out_mmq_ds4 (prefill only, head_dim 128) the output in the form the reference's batched int8 GEMM reads,
+ *                replacing the quantize_mmq_q8_1_k pass in front of the Wo projection (src/kernels.cu:147-205, launched
+ *                at :1842-1850): 144-byte blocks of 128 values = four groups of 32, each group d = max|x| / 127 and
+ *                q = round-half-away(x * (127 / max|x|)); block (chunk c, token t) at index c * batch + t, which with
+ *                head_dim 128 is (head, token).  out_mmq_ds4 != 0: the four scales are fp16 pairs (d, sum of the
+ *                group's values), the form a Q4_K weight needs; 0: four fp32 d, the form a Q6_K weight needs
+ *                (src/kernels.cu:1846).  With out_mmq set, `out` may be NULL.
  * bias_k, bias_v and norm_k act on the appended row and need OATTN_FUSE_KV_APPEND. */
 typedef struct oattn_ext {
     const float* bias_q;
@@ -248,14 +255,16 @@ typedef struct oattn_ext {
     float norm_eps;
     int8_t* out_qs;
     float* out_scales;
+    void* out_mmq;
+    int out_mmq_ds4;
 } oattn_ext;
 
 /* oattn_decode with the extras above (ext == NULL: identical to oattn_decode). */
 int oattn_decode_ex(const float* q, const float* k_new, const float* v_new, uint16_t* kc, uint16_t* vc, float* out,
                     int n_head, int n_kv, int head_dim, int n_ctx, const int* d_pos, float scale, int fuse,
                     const oattn_rope_params* rope, const oattn_ext* ext, void* workspace, size_t workspace_bytes, void* stream);
-/* oattn_prefill with bias / norm (out_qs is refused: the reference's prefill feeds a different, 128-value block
- * format to its batched GEMM, src/kernels.cu:147-155, which is not produced here). */
+/* oattn_prefill with bias / norm and, optionally, the output as block_q8_1_mmq blocks (out_mmq; out_qs is the decode
+ * form and is refused here). */
 int oattn_prefill_ex(const float* q, const float* k_new, const float* v_new, uint16_t* kc, uint16_t* vc, float* out,
                      int n_head, int n_kv, int head_dim, int n_ctx, int n_past, int batch, float scale, int fuse,
                      const oattn_rope_params* rope, const oattn_ext* ext, void* workspace, size_t workspace_bytes,

@@ -222,3 +222,44 @@ void oracle_quantize_q8_1(const float *x, int n, signed char *qs, float *scales)
         scales[g] = d;
     }
 }
+
+/* src/kernels.cu:147-205  quantize_mmq_q8_1_k, the form in which the reference's GPU prefill path hands an activation
+ * matrix X [batch][ne00] (ne00 a multiple of 128 here) to its batched int8 GEMM.  Output: 144-byte blocks of 128
+ * values, block (chunk c, token t) at index c * batch + t (:172); inside a block four scale slots, then 128 int8.  Per
+ * group of 32 values: d_inv = 127 / max|x|, q = roundf(x * d_inv) (:184-189); slot = fp32 d = 1 / d_inv (:203), or for
+ * ds4 the fp16 pair (d, sum of the 32 values) (:194-201), the sum taken as the kernel takes it: four values per
+ * thread, then a butterfly over eight threads.  An all-zero group gives q = 0, d = 0.  IEEE division here, fast-math
+ * in the reference's build. */
+static unsigned short half_bits(float f) {
+    _Float16 h = (_Float16)f;
+    unsigned short b;
+    memcpy(&b, &h, 2);
+    return b;
+}
+
+void oracle_quantize_mmq_q8_1(const float *x, int ne00, int batch, int ds4, unsigned char *y) {
+    for (int t = 0; t < batch; ++t) {
+        for (int c = 0; c * 128 < ne00; ++c) {
+            unsigned char *blk = y + ((size_t)c * batch + t) * 144;
+            for (int g = 0; g < 4; ++g) {
+                const float *v = x + (size_t)t * ne00 + c * 128 + g * 32;
+                float amax = 0.0f, part[8];
+                for (int i = 0; i < 32; ++i) {
+                    float a = fabsf(v[i]);
+                    if (a > amax) amax = a;
+                }
+                for (int l = 0; l < 8; ++l) part[l] = ((v[4 * l] + v[4 * l + 1]) + v[4 * l + 2]) + v[4 * l + 3];
+                const float sum = ((part[0] + part[4]) + (part[2] + part[6])) + ((part[1] + part[5]) + (part[3] + part[7]));
+                const float d_inv = amax > 0.0f ? 127.0f / amax : 0.0f;
+                const float d = amax > 0.0f ? 1.0f / d_inv : 0.0f;
+                for (int i = 0; i < 32; ++i) blk[16 + g * 32 + i] = (unsigned char)(signed char)roundf(v[i] * d_inv);
+                if (ds4) {
+                    unsigned short pair[2] = {half_bits(d), half_bits(sum)};
+                    memcpy(blk + 4 * g, pair, 4);
+                } else {
+                    memcpy(blk + 4 * g, &d, 4);
+                }
+            }
+        }
+    }
+}

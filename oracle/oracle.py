@@ -72,6 +72,7 @@ class Oracle:
         L.oracle_rms_norm.argtypes = [_f32p, _f32p, _i, _f, _f32p]
         L.oracle_pre_attention.argtypes = [_f32p, _f32p, _f32p, _i, _i, _i] + [_f32p] * 5 + [_f]
         L.oracle_quantize_q8_1.argtypes = [_f32p, _i, ctypes.c_void_p, _f32p]
+        L.oracle_quantize_mmq_q8_1.argtypes = [_f32p, _i, _i, _i, ctypes.c_void_p]
         self.L = L
 
     def rope(self, x, rope_type, n_rot, theta, pos, freq_factors=None):
@@ -131,6 +132,16 @@ class Oracle:
         scales = np.empty((x.size + 31) // 32, np.float32)
         self.L.oracle_quantize_q8_1(_fp(x), x.size, qs.ctypes.data, _fp(scales))
         return qs, scales
+
+    def quantize_mmq_q8_1(self, x, ds4):
+        """x [batch][ne00] fp32 -> uint8 [ne00/128][batch][144]: the reference's block_q8_1_mmq activation form
+        (kernels.cu:147-205)."""
+        x = np.ascontiguousarray(x, np.float32)
+        batch, ne00 = x.shape
+        assert ne00 % 128 == 0
+        y = np.zeros((ne00 // 128, batch, 144), np.uint8)
+        self.L.oracle_quantize_mmq_q8_1(_fp(x), ne00, batch, 1 if ds4 else 0, y.ctypes.data)
+        return y
 
     def kv_shift(self, kcache, vcache, n_layer, n_kv, d, n_ctx, n_keep, shift):
         """In place on arrays of any element width (fp32 oracle cache or the uint16 device image)."""
@@ -262,6 +273,8 @@ class RefCuda:
         L.refcuda_scratch_size.argtypes = [_i, _i]
         L.refcuda_scratch_assign.argtypes = [vp, _i, _i]
         L.refcuda_quantize_activation.argtypes = [vp, _i]
+        if hasattr(L, "refcuda_gemv_batch"):
+            L.refcuda_gemv_batch.argtypes = [_i, vp, vp, vp, _i, _i, _i]
         L.refcuda_rms_norm_rows.argtypes = [vp, vp, _i, _i, _f, vp]
         L.refcuda_add_inplace_broadcast.argtypes = [vp, vp, _i, _i]
         L.refcuda_rope_batch.argtypes = [vp, _i, _i, _i, _i, _f, _i, _i, vp]
@@ -318,6 +331,25 @@ class RefCuda:
     def kv_shift(self, kc, vc, n_layer, n_kv, head_dim, n_ctx, n_keep, shift):
         self._sync_stream()
         self.L.refcuda_kv_shift(self._p(kc), self._p(vc), n_layer, n_kv, head_dim, n_ctx, n_keep, shift)
+
+    def quantize_mmq(self, x, ggml_type, w_blocks, n_out):
+        """The reference's quantize_mmq_q8_1_k pass (src/kernels.cu:160-205) as its batched GEMM runs it
+        (mmq_batch_launch, :1842-1850): x [batch][n_in] fp32 and a [n_out][n_in] weight of K-quant blocks (uint8
+        tensor) go through gemv_batch; returns the activation blocks it left in the scratch block,
+        uint8 [n_in/128][batch][144], and the GEMM result [batch][n_out]."""
+        torch = self.torch
+        self._sync_stream()
+        batch, n_in = x.shape
+        nbytes = int(self.L.refcuda_scratch_size(n_in, batch))
+        arena = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+        self.L.refcuda_scratch_assign(self._p(arena), n_in, batch)
+        y = torch.empty(batch, n_out, device="cuda")
+        self.L.refcuda_gemv_batch(int(ggml_type), self._p(w_blocks), self._p(x), self._p(y), n_in, n_out, batch)
+        torch.cuda.current_stream().synchronize()
+        n_al = (n_in + 255) // 256 * 256
+        off = n_al + (n_al // 32 * 4 + 255) // 256 * 256
+        nblk = (n_in + 127) // 128 * batch
+        return arena[off:off + nblk * 144].view(-1, batch, 144).clone(), y
 
     def rms_norm_rows(self, x, w, rows, cols, eps, y):
         self._sync_stream()

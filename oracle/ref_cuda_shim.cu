@@ -27,6 +27,12 @@ void refcuda_scratch_assign(void* base, int max_in, int max_batch) { llm::cuda::
 // (layout fixed by scratch_assign, src/kernels.cu:1763-1776).
 void refcuda_quantize_activation(const float* x, int n_in) { llm::cuda::quantize_activation(x, n_in); }
 
+// src/kernels.h: gemv_batch.  For Q4_K / Q6_K weights (ggml types 12 / 14) it first writes X as block_q8_1_mmq blocks
+// into the scratch block, behind the q8_1 values and scales (layout fixed by scratch_assign, src/kernels.cu:1763-1776).
+void refcuda_gemv_batch(int type, const void* W, const float* X, float* Y, int n_in, int n_out, int batch) {
+    llm::cuda::gemv_batch((llm::DType)type, W, X, Y, n_in, n_out, batch);
+}
+
 void refcuda_rms_norm_rows(const float* x, const float* w, int rows, int cols, float eps, float* y) {
     llm::cuda::rms_norm_rows(x, w, rows, cols, eps, y);
 }

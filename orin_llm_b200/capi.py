@@ -38,7 +38,8 @@ class RopeParams(ctypes.Structure):
 class Ext(ctypes.Structure):
     _fields_ = [("bias_q", ctypes.c_void_p), ("bias_k", ctypes.c_void_p), ("bias_v", ctypes.c_void_p),
                 ("norm_q", ctypes.c_void_p), ("norm_k", ctypes.c_void_p), ("norm_eps", ctypes.c_float),
-                ("out_qs", ctypes.c_void_p), ("out_scales", ctypes.c_void_p)]
+                ("out_qs", ctypes.c_void_p), ("out_scales", ctypes.c_void_p), ("out_mmq", ctypes.c_void_p),
+                ("out_mmq_ds4", ctypes.c_int)]
 
 
 class AttnError(RuntimeError):

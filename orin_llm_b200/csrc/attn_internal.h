@@ -136,6 +136,8 @@ struct PrefillArgs {
     int fuse;
     RopeArgs rope;
     PreArgs pre;           // optional bias / per-head RMSNorm in front of RoPE (k and v parts only with the append)
+    uint8_t* out_mmq = nullptr;   // optional: the output as block_q8_1_mmq blocks [head][batch], 144 bytes each
+    int mmq_ds4 = 0;              // scales as fp16 (d, sum) pairs instead of fp32 d
 };
 
 // Prologue shared by both prefill kernels: RoPE(q) -> q16, RoPE(k_new) + fp16 append of k_new, v_new.

@@ -239,6 +239,7 @@ static int apply_ext(const oattn_ext* ext, int fuse, bool allow_q8, int n_head, 
     if ((ext->norm_q || ext->norm_k) && !(ext->norm_eps >= 0.0f)) return OATTN_ERR_ARG;
     if ((ext->out_qs != nullptr) != (ext->out_scales != nullptr)) return OATTN_ERR_ARG;
     if (ext->out_qs && !allow_q8) return OATTN_ERR_UNSUPPORTED;
+    if (ext->out_mmq && out_qs) return OATTN_ERR_UNSUPPORTED;           // the decode calls have the q8_1 form instead
     if ((ext->norm_q || ext->norm_k) && n_head + n_kv > 160) return OATTN_ERR_UNSUPPORTED;
     pre.bias_q = ext->bias_q; pre.bias_k = ext->bias_k; pre.bias_v = ext->bias_v;
     pre.norm_q = ext->norm_q; pre.norm_k = ext->norm_k; pre.eps = ext->norm_eps;
@@ -448,7 +449,9 @@ int oattn_prefill_ex(const float* q, const float* k_new, const float* v_new, uin
     if (!dev) return OATTN_ERR_DEVICE;
     int rc = check_shape(n_head, n_kv, head_dim);
     if (rc != OATTN_OK) return rc;
-    if (!q || !kc || !vc || !out || n_ctx <= 0 || !(scale > 0.0f)) return OATTN_ERR_ARG;
+    const bool mmq_only = ext && ext->out_mmq;                         // the fp32 output is optional next to the block form
+    if (!q || !kc || !vc || (!out && !mmq_only) || n_ctx <= 0 || !(scale > 0.0f)) return OATTN_ERR_ARG;
+    if (mmq_only && (head_dim != 128 || g_prefill_impl != 0 || ((uintptr_t)ext->out_mmq & 15))) return OATTN_ERR_UNSUPPORTED;
     if (batch <= 0 || n_past < 0 || n_past + batch > n_ctx) return OATTN_ERR_ARG;
     if (fuse & ~OATTN_FUSE_ALL) return OATTN_ERR_ARG;
     if ((fuse & OATTN_FUSE_ROPE_K) && !(fuse & OATTN_FUSE_KV_APPEND)) return OATTN_ERR_ARG;
@@ -463,6 +466,7 @@ int oattn_prefill_ex(const float* q, const float* k_new, const float* v_new, uin
     a.status = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(workspace) + need - 256);
     a.n_head = n_head; a.n_kv = n_kv; a.head_dim = head_dim; a.n_ctx = n_ctx; a.n_past = n_past; a.batch = batch;
     a.scale = scale; a.fuse = fuse;
+    if (mmq_only) { a.out_mmq = reinterpret_cast<uint8_t*>(ext->out_mmq); a.mmq_ds4 = ext->out_mmq_ds4; }
     cudaStream_t s = (cudaStream_t)stream;
     cudaError_t e = launch_prefill_prologue(a, s, &g_launches);
     if (e != cudaSuccess) return cuda_fail(e, "prefill prologue launch");
@@ -471,6 +475,7 @@ int oattn_prefill_ex(const float* q, const float* k_new, const float* v_new, uin
         if (e == cudaSuccess) return OATTN_OK;
         if (e != cudaErrorNotSupported) return cuda_fail(e, "prefill (tcgen05) launch");
     }
+    if (mmq_only) return OATTN_ERR_UNSUPPORTED;       // the block form is written by the tcgen05 kernel only
     e = launch_prefill_mma(a, s, &g_launches);
     return e == cudaSuccess ? OATTN_OK : cuda_fail(e, "prefill (mma) launch");
 }

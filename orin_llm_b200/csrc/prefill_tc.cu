@@ -82,6 +82,8 @@ __device__ long long g_trace[3][8][128];
 
 struct TcArgs {
     float* out;
+    uint8_t* out_mmq;      // optional block_q8_1_mmq form of the output (src/kernels.cu:147-155), [head][batch] blocks
+    int mmq_ds4;
     int* status;
     int n_head, n_kv, n_past, batch, G, TQ;   // TQ = floor(128 / G) tokens per tile
 };
@@ -482,11 +484,36 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             for (int c = 0; c < 2; ++c) {
                 float a[32];
                 tmem_ld32(to + 64 * team + 32 * c, a);
-                if (valid) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) a[i] *= inv;
+                if (valid && p.out) {
 #pragma unroll
                     for (int i = 0; i < 8; ++i)
-                        *reinterpret_cast<float4*>(dst + 32 * c + 4 * i) =
-                            make_float4(a[4 * i] * inv, a[4 * i + 1] * inv, a[4 * i + 2] * inv, a[4 * i + 3] * inv);
+                        *reinterpret_cast<float4*>(dst + 32 * c + 4 * i) = make_float4(a[4 * i], a[4 * i + 1], a[4 * i + 2], a[4 * i + 3]);
+                }
+                if (valid && p.out_mmq) {
+                    // The 32 values are one quantisation group of the 128-value block of (head, token): what
+                    // quantize_mmq_q8_1_k (src/kernels.cu:160-205) computes with a shuffle over eight lanes is a
+                    // reduction over this thread's registers here.
+                    float amax = 0.f, sum = 0.f;
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) { amax = fmaxf(amax, fabsf(a[i])); sum += a[i]; }
+                    const float d_inv = amax > 0.f ? __fdiv_rn(127.0f, amax) : 0.f;
+                    uint32_t w[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int q0 = (int)roundf(a[4 * i] * d_inv), q1 = (int)roundf(a[4 * i + 1] * d_inv);
+                        const int q2 = (int)roundf(a[4 * i + 2] * d_inv), q3 = (int)roundf(a[4 * i + 3] * d_inv);
+                        w[i] = (uint32_t)(q0 & 0xFF) | ((uint32_t)(q1 & 0xFF) << 8) | ((uint32_t)(q2 & 0xFF) << 16) | ((uint32_t)(q3 & 0xFF) << 24);
+                    }
+                    uint8_t* blk = p.out_mmq + ((size_t)(kvh * p.G + hg) * p.batch + tglob) * 144;
+                    const int g = 2 * team + c;
+                    const float d = amax > 0.f ? __fdiv_rn(1.0f, d_inv) : 0.f;
+                    if (p.mmq_ds4) reinterpret_cast<__half2*>(blk)[g] = __halves2half2(__float2half(d), __float2half(sum));
+                    else           reinterpret_cast<float*>(blk)[g] = d;
+                    uint4* qs = reinterpret_cast<uint4*>(blk + 16 + 32 * g);
+                    qs[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                    qs[1] = make_uint4(w[4], w[5], w[6], w[7]);
                 }
             }
         }
@@ -550,6 +577,8 @@ cudaError_t launch_prefill_tc(const PrefillArgs& a, int sm_count, cudaStream_t s
     if (!make_map(&tmV, a.vc, rows, a.n_kv, rowb, rowb * a.n_ctx, BN, 1)) return cudaErrorInvalidValue;
     TcArgs t;
     t.out = a.out;
+    t.out_mmq = a.out_mmq;
+    t.mmq_ds4 = a.mmq_ds4;
     t.status = a.status;
     t.n_head = a.n_head; t.n_kv = a.n_kv; t.n_past = a.n_past; t.batch = a.batch; t.G = G; t.TQ = TQ;
     dim3 grid((a.batch + TQ - 1) / TQ, a.n_kv);

@@ -52,42 +52,40 @@ __global__ void __launch_bounds__(128) kv_store_kernel(uint16_t* kc, uint16_t* v
 }
 
 // ---- KV shift: kv_shift_k (src/kernels.cu:1682-1700) --------------------------------------------
-// The reference moves one element per thread per position in a serial loop.  A row only ever
-// moves to the same columns of a lower row, so 32-byte column slices of one (layer, head) are
-// independent: grid = (row_bytes/32, n_kv, n_layer), each CTA slides its slice 256 rows at a time
-// (read, barrier, write), then zeroes the tail.  K and V are handled by the same CTA.
-constexpr int kShiftThreads = 256;
+// The reference moves one element per thread per position in a serial loop.  Here one CTA slides the rows of one
+// (layer, kv head) of K or of V: grid = (2, n_kv, n_layer), 512 threads.  The rows of a head are contiguous, so a step
+// reads a contiguous block of 128 rows (every load issued, 64 bytes in flight per thread), passes a barrier and
+// writes the block `shift` rows lower; a step's sources overlap only its own destinations, never those of another
+// step.  Then the tail is zeroed.  All accesses are 16-byte pieces of consecutive addresses.
+constexpr int kShiftThreads = 512;
+constexpr int kShiftPieces = 4;        // 16-byte pieces per thread and step
 
 __global__ void __launch_bounds__(kShiftThreads) kv_shift_kernel(uint16_t* kc, uint16_t* vc, int n_kv, int head_dim,
                                                                  int n_ctx, int n_keep, int shift) {
-    const int col = blockIdx.x, head = blockIdx.y, layer = blockIdx.z;
+    const int head = blockIdx.y, layer = blockIdx.z;
     const size_t row_bytes = (size_t)head_dim * 2;
-    const size_t base = ((size_t)layer * n_kv + head) * n_ctx * row_bytes + (size_t)col * 32;
-    uint8_t* kb = reinterpret_cast<uint8_t*>(kc) + base;
-    uint8_t* vb = reinterpret_cast<uint8_t*>(vc) + base;
-    const int last = n_ctx - shift;   // first row of the zeroed tail
-    for (int row0 = n_keep; row0 < last; row0 += kShiftThreads) {
-        const int row = row0 + threadIdx.x;
-        uint4 k0, k1, v0, v1;
-        const bool ok = row < last;
-        if (ok) {
-            const uint4* ks = reinterpret_cast<const uint4*>(kb + (size_t)(row + shift) * row_bytes);
-            const uint4* vs = reinterpret_cast<const uint4*>(vb + (size_t)(row + shift) * row_bytes);
-            k0 = ks[0]; k1 = ks[1]; v0 = vs[0]; v1 = vs[1];
+    uint8_t* base = reinterpret_cast<uint8_t*>(blockIdx.x ? vc : kc) + ((size_t)layer * n_kv + head) * n_ctx * row_bytes;
+    const int last = n_ctx - shift;                        // first row of the zeroed tail
+    const size_t p16 = row_bytes / 16;                     // pieces per row
+    const size_t first = (size_t)n_keep * p16, end = (size_t)max(last, n_keep) * p16, off = (size_t)shift * p16;
+    uint4* c = reinterpret_cast<uint4*>(base);
+    constexpr size_t STEP = (size_t)kShiftThreads * kShiftPieces;
+    for (size_t i0 = first; i0 < end; i0 += STEP) {
+        uint4 t[kShiftPieces];
+#pragma unroll
+        for (int u = 0; u < kShiftPieces; ++u) {
+            const size_t i = i0 + (size_t)u * kShiftThreads + threadIdx.x;
+            if (i < end) t[u] = c[i + off];
         }
         __syncthreads();
-        if (ok) {
-            uint4* kd = reinterpret_cast<uint4*>(kb + (size_t)row * row_bytes);
-            uint4* vd = reinterpret_cast<uint4*>(vb + (size_t)row * row_bytes);
-            kd[0] = k0; kd[1] = k1; vd[0] = v0; vd[1] = v1;
+#pragma unroll
+        for (int u = 0; u < kShiftPieces; ++u) {
+            const size_t i = i0 + (size_t)u * kShiftThreads + threadIdx.x;
+            if (i < end) c[i] = t[u];
         }
     }
     const uint4 z = make_uint4(0, 0, 0, 0);
-    for (int row = max(last, 0) + threadIdx.x; row < n_ctx; row += kShiftThreads) {
-        uint4* kd = reinterpret_cast<uint4*>(kb + (size_t)row * row_bytes);
-        uint4* vd = reinterpret_cast<uint4*>(vb + (size_t)row * row_bytes);
-        kd[0] = z; kd[1] = z; vd[0] = z; vd[1] = z;
-    }
+    for (size_t i = (size_t)max(last, 0) * p16 + threadIdx.x; i < (size_t)n_ctx * p16; i += kShiftThreads) c[i] = z;
 }
 
 // ---- prefill prologue ---------------------------------------------------------------------------
@@ -240,7 +238,7 @@ cudaError_t launch_kv_store(uint16_t* kc, uint16_t* vc, const float* k, const fl
 
 cudaError_t launch_kv_shift(uint16_t* kc, uint16_t* vc, int n_layer, int n_kv, int head_dim, int n_ctx, int n_keep,
                             int shift, cudaStream_t stream, unsigned long long* launches) {
-    dim3 grid(head_dim * 2 / 32, n_kv, n_layer);
+    dim3 grid(2, n_kv, n_layer);
     kv_shift_kernel<<<grid, kShiftThreads, 0, stream>>>(kc, vc, n_kv, head_dim, n_ctx, n_keep, shift);
     if (launches) *launches += 1;
     return cudaGetLastError();

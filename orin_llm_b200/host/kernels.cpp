@@ -291,6 +291,7 @@ static oattn_ext to_ext(const AttnExtras& x) {
     e.bias_q = x.bq; e.bias_k = x.bk; e.bias_v = x.bv;
     e.norm_q = x.q_norm; e.norm_k = x.k_norm; e.norm_eps = x.rms_eps;
     e.out_qs = x.q8; e.out_scales = x.q8_scale;
+    e.out_mmq = x.q8_mmq; e.out_mmq_ds4 = x.q8_mmq_ds4 ? 1 : 0;
     return e;
 }
 void attention_decode_fused(const float* q, const float* k, const float* v, uint16_t* kc, uint16_t* vc, float* out,

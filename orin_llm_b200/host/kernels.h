@@ -90,6 +90,8 @@ struct AttnExtras {
     float rms_eps = 0.0f;             // HParams::rms_eps
     int8_t* q8 = nullptr;             // decode only: int8 [n_head*head_dim], as g_q8 (src/kernels.cu:1748)
     float* q8_scale = nullptr;        //              fp32 [n_head*head_dim/32], as g_q8_scale (src/kernels.cu:1749)
+    void* q8_mmq = nullptr;           // prefill only: block_q8_1_mmq blocks [n_head][batch], as g_q8_mmq (src/kernels.cu:1750)
+    bool q8_mmq_ds4 = false;          //               true when Wo is Q4_K (scales as fp16 (d, sum)), false for Q6_K
 };
 void attention_decode_fused(const float* q, const float* k, const float* v, uint16_t* kc, uint16_t* vc, float* out,
                             int n_head, int n_kv, int head_dim, int n_ctx, const int* d_pos, float scale,

@@ -140,17 +140,20 @@ def flash_attention_decode_ind(q, kc, vc, out, n_head, n_kv, head_dim, n_ctx, d_
 
 def _ext_params(ext):
     """ext: dict with any of bias_q, bias_k, bias_v, norm_q, norm_k (fp32 CUDA tensors), norm_eps (float), out_qs (int8
-    tensor), out_scales (fp32 tensor) -> (pointer to capi.Ext or None, object to keep alive)."""
+    tensor), out_scales (fp32 tensor), out_mmq (uint8 tensor of 144-byte blocks, prefill only), out_mmq_ds4 (bool)
+    -> (pointer to capi.Ext or None, object to keep alive)."""
     if not ext:
         return None, None
-    unknown = set(ext) - {"bias_q", "bias_k", "bias_v", "norm_q", "norm_k", "norm_eps", "out_qs", "out_scales"}
+    unknown = set(ext) - {"bias_q", "bias_k", "bias_v", "norm_q", "norm_k", "norm_eps", "out_qs", "out_scales", "out_mmq",
+                           "out_mmq_ds4"}
     if unknown:
         raise ValueError("unknown extension keys: %s" % sorted(unknown))
     e = capi.Ext()
-    for name in ("bias_q", "bias_k", "bias_v", "norm_q", "norm_k", "out_qs", "out_scales"):
+    for name in ("bias_q", "bias_k", "bias_v", "norm_q", "norm_k", "out_qs", "out_scales", "out_mmq"):
         t = ext.get(name)
         setattr(e, name, t.data_ptr() if t is not None else None)
     e.norm_eps = float(ext.get("norm_eps", 0.0))
+    e.out_mmq_ds4 = 1 if ext.get("out_mmq_ds4") else 0
     return ctypes.byref(e), e
 
 

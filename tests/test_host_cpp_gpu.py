@@ -177,3 +177,61 @@ def test_call_sequence_fusion(shim, ops, oracle):
         assert torch.equal(kc2[:, 7].cpu(), torch.from_numpy(k[1]).half())      # the unrotated other k, as asked
     finally:
         shim.shim_fuse_call_sequence(0)
+
+
+def test_fused_decode_captured_without_assigned_scratch(shim, tmp_path):
+    """attention_decode_fused as the FIRST call a host makes, under stream capture, with no attn_scratch_assign() before
+    it (what the reference's forward_capture would do, src/model_gpu.cu:295-316): the wrapper must not allocate during
+    the capture -- it runs on the library's built-in scratch block -- and the replayed graph must give the oracle's
+    result at several positions.  A fresh process, because the wrappers keep process-global state."""
+    from orin_llm_b200 import build
+    code = r'''
+import ctypes, os, sys
+import numpy as np, torch
+sys.path.insert(0, sys.argv[2]); sys.path.insert(0, os.path.join(sys.argv[2], "tests"))
+from oracle.oracle import Oracle
+from helpers import assert_close, f16_round, make_qkv
+L = ctypes.CDLL(sys.argv[1])
+vp, i, f = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+L.shim_set_stream.argtypes = [vp]
+L.shim_decode_layer_fused.argtypes = [vp] * 6 + [i] * 4 + [vp, f, i, i, f]
+torch.cuda.set_device(0); torch.zeros(1, device="cuda")
+n_head, n_kv, hd, n_ctx, n0 = 12, 2, 128, 1024, 300
+scale = np.float32(1.0 / np.sqrt(hd))
+rng = np.random.default_rng(5)
+_, K, V = make_qkv(6, n_head, n_kv, hd, n0, n_ctx)
+kc32, vc32 = K.astype(np.float32), V.astype(np.float32)
+dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+dK, dV = dev(K), dev(V)
+dq = torch.empty(n_head, hd, device="cuda"); dk = torch.empty(n_kv, hd, device="cuda"); dv = torch.empty(n_kv, hd, device="cuda")
+out = torch.empty(n_head, hd, device="cuda")
+d_pos = torch.tensor([n0], dtype=torch.int32, device="cuda")
+stream = torch.cuda.Stream(); graph = torch.cuda.CUDAGraph()
+stream.wait_stream(torch.cuda.current_stream())
+before = torch.cuda.memory_allocated()
+free0 = torch.cuda.mem_get_info()[0]
+with torch.cuda.stream(stream):
+    L.shim_set_stream(stream.cuda_stream)
+    graph.capture_begin(capture_error_mode="relaxed")       # the reference captures in relaxed mode too
+    L.shim_decode_layer_fused(dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dK.data_ptr(), dV.data_ptr(), out.data_ptr(), n_head,
+                              n_kv, hd, n_ctx, d_pos.data_ptr(), float(scale), 1, hd, 1e6)
+    graph.capture_end()
+    L.shim_set_stream(None)
+assert torch.cuda.mem_get_info()[0] >= free0 - (8 << 20), "the captured call allocated device memory"
+orc = Oracle()
+for step in range(3):
+    pos = n0 + step
+    q = rng.standard_normal((n_head, hd)).astype(np.float32); k = rng.standard_normal((n_kv, hd)).astype(np.float32)
+    v = f16_round(rng.standard_normal((n_kv, hd)).astype(np.float32))
+    dq.copy_(dev(q)); dk.copy_(dev(k)); dv.copy_(dev(v)); d_pos.fill_(pos)
+    torch.cuda.synchronize(); graph.replay(); torch.cuda.synchronize()
+    qo, ko = q.copy()[None], k.copy()[None]
+    want = orc.attn_batch(qo, ko, v[None].copy(), kc32, vc32, pos, scale, True, 1, hd, 1e6, None)[0]
+    kc32[:, pos] = f16_round(ko[0])
+    assert_close(out.cpu().numpy(), want, "captured fused decode, step %d" % step)
+print("ok")
+'''
+    root = os.path.dirname(HERE)
+    r = subprocess.run(["python", "-c", code, os.path.join(build.LIBDIR, "libhost_shim_test.so"), root], capture_output=True,
+                       text=True, timeout=300)
+    assert r.returncode == 0 and r.stdout.strip().endswith("ok"), r.stderr[-1500:]

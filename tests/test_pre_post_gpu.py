@@ -234,3 +234,86 @@ def test_extension_argument_errors(ops):
         ops.attn_prefill(qb, None, None, kc, kc, ob, n_head, n_kv, hd, n_ctx, 0, 4, 0.1, ops.FUSE_NONE,
                          ext=dict(out_qs=qs, out_scales=sc))
     assert e.value.code == capi.ERR_UNSUPPORTED
+
+
+def _mmq_fields(blocks, ds4):
+    """uint8 [..., 144] -> (scales fp32 [..., 4], sums fp32 [..., 4] or None, int8 values [..., 128])."""
+    b = np.ascontiguousarray(blocks)
+    head = b[..., :16]
+    qs = b[..., 16:].copy().view(np.int8)
+    if ds4:
+        h = head.copy().view(np.float16).astype(np.float32).reshape(b.shape[:-1] + (4, 2))
+        return h[..., 0], h[..., 1], qs
+    return head.copy().view(np.float32).reshape(b.shape[:-1] + (4,)), None, qs
+
+
+@pytest.mark.parametrize("ds4", [False, True])
+@pytest.mark.parametrize("n_head,n_kv,n_past,batch", [(32, 8, 4096, 512), (12, 2, 0, 45), (28, 4, 100, 37)])
+def test_prefill_mmq_output_is_the_quantised_fp32_output(ops, oracle, ds4, n_head, n_kv, n_past, batch):
+    """The block_q8_1_mmq blocks written by the prefill call equal the restated quantiser (src/kernels.cu:160-205)
+    applied to the fp32 output of the same call: values and fp32 scales bit for bit, the fp16 group sums to fp16
+    rounding (the kernel adds a group's 32 values in another order); with `out` omitted the blocks are unchanged."""
+    hd = 128
+    n_ctx = n_past + batch
+    scale = float(1.0 / np.sqrt(hd))
+    gen = torch.Generator("cuda").manual_seed(5 + n_past)
+    K = torch.randn(n_kv, n_ctx, hd, device="cuda", dtype=torch.float16, generator=gen)
+    V = torch.randn(n_kv, n_ctx, hd, device="cuda", dtype=torch.float16, generator=gen)
+    q = torch.randn(batch, n_head, hd, device="cuda", generator=gen).half().float()
+    out = torch.empty(batch, n_head, hd, device="cuda")
+    blk = torch.full((n_head, batch, 144), 0x5A, dtype=torch.uint8, device="cuda")
+    ops.attn_prefill(q, None, None, K, V, out, n_head, n_kv, hd, n_ctx, n_past, batch, scale, ops.FUSE_NONE,
+                     ext=dict(out_mmq=blk, out_mmq_ds4=ds4))
+    torch.cuda.synchronize()
+    assert ops.prefill_status(n_head, n_kv, hd, batch) == 0
+    want = oracle.quantize_mmq_q8_1(out.cpu().numpy().reshape(batch, n_head * hd), ds4)
+    gd, gs, gq = _mmq_fields(blk.cpu().numpy(), ds4)
+    wd, ws, wq = _mmq_fields(want, ds4)
+    assert np.array_equal(gq, wq)
+    assert np.array_equal(gd, wd)
+    if ds4:
+        assert np.allclose(gs, ws, rtol=2e-3, atol=2e-3)
+    plain = torch.empty_like(out)
+    ops.attn_prefill(q, None, None, K, V, plain, n_head, n_kv, hd, n_ctx, n_past, batch, scale, ops.FUSE_NONE)
+    blk2 = torch.zeros_like(blk)
+    ops.attn_prefill(q, None, None, K, V, None, n_head, n_kv, hd, n_ctx, n_past, batch, scale, ops.FUSE_NONE,
+                     ext=dict(out_mmq=blk2, out_mmq_ds4=ds4))
+    torch.cuda.synchronize()
+    assert torch.equal(plain, out) and torch.equal(blk2, blk)
+
+
+@pytest.mark.parametrize("ggml_type,ds4", [(12, True), (14, False)])
+def test_prefill_mmq_output_against_the_reference_quantise_pass(ops, oracle, refcuda, ggml_type, ds4):
+    """The reference's own quantize_mmq_q8_1_k, run the way its batched GEMM runs it (gemv_batch on a Q4_K / Q6_K weight,
+    src/kernels.cu:1842-1850), on the fp32 output of the prefill call: same block layout and scales (to an ulp of its
+    fast-math division), values equal except for a rare one-step difference on a rounding boundary."""
+    import sys
+    import os
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle", "e2e"))
+    import make_gguf
+    if not hasattr(refcuda.L, "refcuda_gemv_batch"):
+        pytest.skip("oracle/_ref/libref_cuda.so predates refcuda_gemv_batch")
+    n_head, n_kv, hd, n_past, batch = 32, 8, 128, 512, 64
+    n_ctx = n_past + batch
+    scale = float(1.0 / np.sqrt(hd))
+    gen = torch.Generator("cuda").manual_seed(17)
+    K = torch.randn(n_kv, n_ctx, hd, device="cuda", dtype=torch.float16, generator=gen)
+    V = torch.randn(n_kv, n_ctx, hd, device="cuda", dtype=torch.float16, generator=gen)
+    q = torch.randn(batch, n_head, hd, device="cuda", generator=gen).half().float()
+    out = torch.empty(batch, n_head, hd, device="cuda")
+    blk = torch.zeros(n_head, batch, 144, dtype=torch.uint8, device="cuda")
+    ops.attn_prefill(q, None, None, K, V, out, n_head, n_kv, hd, n_ctx, n_past, batch, scale, ops.FUSE_NONE,
+                     ext=dict(out_mmq=blk, out_mmq_ds4=ds4))
+    torch.cuda.synchronize()
+    n_in, n_out = n_head * hd, 128
+    rng = np.random.default_rng(3)
+    w = make_gguf.q4_k_bytes(rng, n_out, n_in) if ggml_type == 12 else make_gguf.q6_k_bytes(rng, n_out, n_in)
+    r_blk, _ = refcuda.quantize_mmq(out.view(batch, n_in), ggml_type, dev(w.reshape(-1)), n_out)
+    assert r_blk.shape == blk.shape
+    gd, gs, gq = _mmq_fields(blk.cpu().numpy(), ds4)
+    rd, rs, rq = _mmq_fields(r_blk.cpu().numpy(), ds4)
+    assert np.allclose(gd, rd, rtol=2e-3 if ds4 else 1e-6, atol=0)
+    diff = np.abs(gq.astype(np.int32) - rq.astype(np.int32))
+    assert diff.max() <= 1 and (diff != 0).mean() < 5e-3
+    if ds4:
+        assert np.allclose(gs, rs, rtol=2e-3, atol=2e-3)

@@ -24,7 +24,7 @@ def dev(a):
     return torch.from_numpy(np.ascontiguousarray(a)).cuda()
 
 
-def test_noalloc_matches_regular_entry_point_twice(ops):
+def test_noalloc_matches_regular_entry_point_twice(ops, oracle):
     from orin_llm_b200 import capi
     L = capi.lib()
     assert L.oattn_decode_noalloc_max_bytes() == 2 << 20
@@ -48,13 +48,17 @@ def test_noalloc_matches_regular_entry_point_twice(ops):
             assert torch.cuda.memory_allocated() == before
             outs.append(out)
         torch.cuda.synchronize()
-        # same kernels, same split plan, only the scratch address differs: within the tolerance the parity tests
+        # same kernel, same split plan, only the scratch address differs: within the tolerance the parity tests
         # use (in fact bit-identical)
         for out in outs:
             err = (out - ref).abs()
             assert torch.isfinite(out).all()
             assert err.max().item() <= 1e-2 and err.mean().item() <= 1e-3
             assert torch.equal(out, ref)
+        # and against the CPU oracle itself, not only against the other entry point
+        want = oracle.attend(q[0], K.astype(np.float32), V.astype(np.float32), npos, np.float32(scale))
+        oerr = np.abs(outs[1].cpu().numpy() - want)
+        assert oerr.max() <= 1e-2 and oerr.mean() <= 1e-3
 
 
 def test_noalloc_refuses_shapes_beyond_the_block(ops):
@@ -62,7 +66,8 @@ def test_noalloc_refuses_shapes_beyond_the_block(ops):
     L = capi.lib()
     t = torch.zeros(64, device="cuda")
     p = t.data_ptr()
-    # 64 query heads on one kv head: 64 * 296 splits * 130 floats = 9.8 MB of partials, more than the 2 MiB block
+    # 64 query heads over 4 kv heads: 64 heads * 74 splits * 130 floats * 4 bytes = 2.5 MB of partials (plus the group
+    # partials), more than the 2 MiB block
     n_head, n_kv, hd = 16 * 4, 4, 128
     need = L.oattn_decode_workspace_bytes(n_head, n_kv, hd)
     if need <= L.oattn_decode_noalloc_max_bytes():
