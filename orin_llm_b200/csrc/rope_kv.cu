@@ -133,6 +133,98 @@ __global__ void __launch_bounds__(kPrologueThreads) prefill_prologue_kernel(cons
         }
         __syncthreads();
     }
+    // Fast path (no per-head norm, whole-row rotation or none, head_dim a multiple of 16 and at most 128): a thread
+    // takes 8 consecutive dims of one head row -- two float4 loads, one 16-byte store; for the (i, i + n_rot/2)
+    // pairing it takes the partner 8 dims as well.  All loads of a thread are issued before its stores.
+    const uintptr_t ptr_bits = (uintptr_t)p.q | (uintptr_t)p.k_new | (uintptr_t)p.v_new | (uintptr_t)p.pre.bias_q |
+                               (uintptr_t)p.pre.bias_k | (uintptr_t)p.pre.bias_v;
+    if (!p.pre.norm_q && !p.pre.norm_k && (hd & 15) == 0 && hd <= 128 && (ptr_bits & 15) == 0 &&
+        ((!rope_q && !rope_k) || p.rope.n_rot == hd)) {
+        const float qscale = p.scale * LOG2E;
+        const bool neox = p.rope.rope_type == 1;
+        const int cpr = hd / 8;                                  // 8-dim chunks per row
+        const int upr = neox ? cpr / 2 : cpr;                    // work units per row (a neox unit is two chunks)
+        const int n_rows = p.n_head + (append ? 2 * p.n_kv : 0);
+        const int units = n_rows * upr;
+        constexpr int MAXU = 3;                                  // (32 + 8 + 8 rows) * 16 chunks / 256 threads
+        if (units <= MAXU * kPrologueThreads) {
+            float4 x[MAXU][4];
+#pragma unroll
+            for (int u = 0; u < MAXU; ++u) {
+                const int unit = tid + u * kPrologueThreads;
+                if (unit >= units) continue;
+                const int row = unit / upr, c = unit % upr;
+                const int kind = row < p.n_head ? 0 : (row < p.n_head + p.n_kv ? 1 : 2);
+                const int head = kind == 0 ? row : (kind == 1 ? row - p.n_head : row - p.n_head - p.n_kv);
+                const float* src = (kind == 0 ? p.q + ((size_t)b * p.n_head + head) * hd
+                                              : (kind == 1 ? p.k_new : p.v_new) + ((size_t)b * p.n_kv + head) * hd);
+                const float* bias0 = kind == 0 ? p.pre.bias_q : (kind == 1 ? p.pre.bias_k : p.pre.bias_v);
+                const int d0 = 8 * c, d1 = neox ? d0 + hd / 2 : d0;
+                x[u][0] = *reinterpret_cast<const float4*>(src + d0);
+                x[u][1] = *reinterpret_cast<const float4*>(src + d0 + 4);
+                if (neox) {
+                    x[u][2] = *reinterpret_cast<const float4*>(src + d1);
+                    x[u][3] = *reinterpret_cast<const float4*>(src + d1 + 4);
+                }
+                if (bias0) {
+                    const float* bs = bias0 + (size_t)head * hd;
+#pragma unroll
+                    for (int v4 = 0; v4 < 4; ++v4) {
+                        if (v4 >= 2 && !neox) continue;
+                        const float4 bv = *reinterpret_cast<const float4*>(bs + (v4 < 2 ? d0 : d1) + 4 * (v4 & 1));
+                        x[u][v4].x += bv.x; x[u][v4].y += bv.y; x[u][v4].z += bv.z; x[u][v4].w += bv.w;
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < MAXU; ++u) {
+                const int unit = tid + u * kPrologueThreads;
+                if (unit >= units) continue;
+                const int row = unit / upr, c = unit % upr;
+                const int kind = row < p.n_head ? 0 : (row < p.n_head + p.n_kv ? 1 : 2);
+                const int head = kind == 0 ? row : (kind == 1 ? row - p.n_head : row - p.n_head - p.n_kv);
+                const bool rot = kind == 0 ? rope_q : (kind == 1 ? rope_k : false);
+                const int d0 = 8 * c;
+                float a[8], bb[8];
+                a[0] = x[u][0].x; a[1] = x[u][0].y; a[2] = x[u][0].z; a[3] = x[u][0].w;
+                a[4] = x[u][1].x; a[5] = x[u][1].y; a[6] = x[u][1].z; a[7] = x[u][1].w;
+                if (neox) {
+                    bb[0] = x[u][2].x; bb[1] = x[u][2].y; bb[2] = x[u][2].z; bb[3] = x[u][2].w;
+                    bb[4] = x[u][3].x; bb[5] = x[u][3].y; bb[6] = x[u][3].z; bb[7] = x[u][3].w;
+                }
+                if (rot) {
+                    if (neox) {            // pair (d0 + i, d0 + i + hd/2), angle index d0 + i
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const float cs = s_cos[d0 + i], sn = s_sin[d0 + i];
+                            const float x0 = a[i] * cs - bb[i] * sn, x1 = a[i] * sn + bb[i] * cs;
+                            a[i] = x0; bb[i] = x1;
+                        }
+                    } else {               // pair (d0 + 2i, d0 + 2i + 1), angle index d0/2 + i
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const float cs = s_cos[d0 / 2 + i], sn = s_sin[d0 / 2 + i];
+                            const float x0 = a[2 * i] * cs - a[2 * i + 1] * sn, x1 = a[2 * i] * sn + a[2 * i + 1] * cs;
+                            a[2 * i] = x0; a[2 * i + 1] = x1;
+                        }
+                    }
+                }
+                const float mul = kind == 0 ? qscale : 1.f;
+                __half* dst = kind == 0 ? p.q16 + ((size_t)b * p.n_head + head) * hd
+                                        : reinterpret_cast<__half*>(kind == 1 ? p.kc : p.vc) + ((size_t)head * p.n_ctx + pos) * hd;
+                uint4 o;
+                o.x = pack_half2(a[0] * mul, a[1] * mul); o.y = pack_half2(a[2] * mul, a[3] * mul);
+                o.z = pack_half2(a[4] * mul, a[5] * mul); o.w = pack_half2(a[6] * mul, a[7] * mul);
+                *reinterpret_cast<uint4*>(dst + d0) = o;
+                if (neox) {
+                    o.x = pack_half2(bb[0] * mul, bb[1] * mul); o.y = pack_half2(bb[2] * mul, bb[3] * mul);
+                    o.z = pack_half2(bb[4] * mul, bb[5] * mul); o.w = pack_half2(bb[6] * mul, bb[7] * mul);
+                    *reinterpret_cast<uint4*>(dst + d0 + hd / 2) = o;
+                }
+            }
+            return;
+        }
+    }
     // One warp per head row: the q rows, then (with the append) the k rows and the v rows.  The lanes walk the row's
     // pairs, so consecutive lanes touch consecutive addresses.  A warp first loads the values of all its rows of a batch
     // and only then rotates and stores them: sources and destinations may alias as far as the compiler can tell, so
