@@ -213,8 +213,8 @@ def run_reference_arm(args, w):
 LAUNCH_ORDER = {0: "ordinary launches", 1: "programmatic dependent launches",
                 2: "programmatic dependent launches, K/V tiles fetched ahead of the dependency wait"}
 EXCHANGE = {"none": "single GPU",
-            "peer": "the CTA that finishes a kv head's merge stores the record into every peer's buffer (NVLink peer stores), "
-                    "waits for the peers' records (generation-tagged words) and merges, all in the decode launch",
+            "peer": "a launch of one CTA per head behind the decode launch stores the record into every peer's buffer (NVLink "
+                    "peer stores), waits for the peers' records (generation-tagged words) and merges",
             "peer-split": "as peer, with the wait and final merge in a launch of their own",
             "nccl": "NCCL all-gather of the records"}
 

@@ -183,9 +183,9 @@ int oattn_decode_partial(const float* q, const uint16_t* kc, const uint16_t* vc,
 int oattn_combine(const float* parts, int n_parts, float* out, int n_head, int head_dim, void* stream);
 
 /* ---- multi-GPU exchange without a collective call (no reference counterpart) ----------------------------------
- * The record exchange of split-KV decode is 8 KB per rank: latency-bound.  Instead of all-gather + combine, the
- * CTA that finishes a kv head's merge stores the record straight into every rank's exchange buffer over NVLink
- * (plain peer stores).  Every fp32 value travels in one aligned 8-byte word together with the generation number of
+ * The record exchange of split-KV decode is 8 KB per rank: latency-bound.  Instead of all-gather + combine, a small
+ * launch behind the decode launch (one CTA per head, so that the peer stores of a call leave from n_head SMs) stores
+ * this rank's record straight into every rank's exchange buffer over NVLink (plain peer stores).  Every fp32 value travels in one aligned 8-byte word together with the generation number of
  * the call, so the receiver needs neither a fence nor a flag: it polls the words of its own buffer until they carry
  * the current generation (bounded, ~2 s by default, see oattn_set_wait_limit_cycles; then a status word is set and the
  * output is left untouched) and merges the `world` records.
@@ -201,8 +201,8 @@ int oattn_decode_partial_push(const float* q, const uint16_t* kc, const uint16_t
                               int n_ctx, const int* d_len, float scale, void* workspace, size_t workspace_bytes,
                               const void* peer_bufs_dev, int rank, int world, void* state, void* stream);
 int oattn_peer_wait_combine(const void* my_buf, int world, float* out, int n_head, int head_dim, void* state, void* stream);
-/* Both steps in ONE launch instead of two: the CTA that stores this rank's record into every exchange buffer also
- * waits for the other ranks' records and writes the merged out [n_head][head_dim].  Every rank must be running on a
+/* Both steps in two launches instead of three: the exchange launch that stores this rank's record into every exchange
+ * buffer also waits for the other ranks' records and writes the merged out [n_head][head_dim].  Every rank must be running on a
  * GPU of its own (the launch waits for kernels of the other ranks); do not mix with the two calls above on the same
  * state block.  No counterpart in the reference. */
 int oattn_decode_peer(const float* q, const uint16_t* kc, const uint16_t* vc, float* out, int n_head, int n_kv, int head_dim,

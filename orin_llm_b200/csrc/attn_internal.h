@@ -33,7 +33,7 @@ inline int decode_group_size(int n_splits) {
 // Decode scratch (caller-owned): the un-normalised partial of every split, [n_kv][n_splits][G][hd] fp32 and
 // [n_kv][n_splits][G][2] (m in raw-score units, l), and the same for every group of `group` neighbouring splits.
 struct DecodeWsLayout {
-    size_t part_o, part_ml, grp_o, grp_ml, total;   // byte offsets, 256-byte aligned
+    size_t part_o, part_ml, grp_o, grp_ml, rec, total;   // byte offsets, 256-byte aligned; rec: this rank's record
     int n_splits, group, n_groups;
 };
 inline DecodeWsLayout decode_ws_layout(int n_head, int n_kv, int head_dim, int n_splits) {
@@ -46,7 +46,8 @@ inline DecodeWsLayout decode_ws_layout(int n_head, int n_kv, int head_dim, int n
     w.part_ml = w.part_o + al((size_t)n_head * n_splits * head_dim * sizeof(float));
     w.grp_o = w.part_ml + al((size_t)n_head * n_splits * 2 * sizeof(float));
     w.grp_ml = w.grp_o + al((size_t)n_head * w.n_groups * head_dim * sizeof(float));
-    w.total = w.grp_ml + al((size_t)n_head * w.n_groups * 2 * sizeof(float));
+    w.rec = w.grp_ml + al((size_t)n_head * w.n_groups * 2 * sizeof(float));
+    w.total = w.rec + al((size_t)n_head * (head_dim + PART_PAD) * sizeof(float));
     return w;
 }
 
@@ -73,13 +74,7 @@ struct DecodeArgs {
     const int* d_rope_pos = nullptr;   // position used for RoPE when it is not the local row index (sharded cache)
     int8_t* out_qs = nullptr;      // optional q8_1 form of the output: int8 [n_head*hd] ...
     float* out_scales = nullptr;   // ... and one fp32 scale per 32 values; `out` may then be nullptr
-    const unsigned long long* peer_bufs = nullptr;   // multi-GPU peer exchange: device array of `world` buffer pointers
-    int* gen_push = nullptr;                          // [n_head] generation counters (private to this rank)
-    int rank = 0, world = 1;
     int overlap = 0;                                  // 0 plain launch, 1 dependent launch, 2 + K/V prefetch before the wait
-    int fused_wait = 0;                               // also wait for every rank's record and write the merged `out`
-    int* peer_status = nullptr;                       // raised when that wait ran out
-    long long wait_cycles = 4000000000LL;             // bound of that wait, in SM clock cycles
 };
 
 // Size of the scratch block built into the library for oattn_decode_noalloc, and its device address on the
@@ -102,6 +97,11 @@ cudaError_t launch_decode(const DecodeArgs& a, cudaStream_t stream, unsigned lon
 cudaError_t launch_combine_records(const float* parts, int n_parts, float* out, int n_head, int head_dim,
                                    cudaStream_t stream, unsigned long long* launches);
 
+// Stores this rank's record (left by a decode launch with emit_partial) into every rank's exchange buffer and, with
+// fused_wait, waits for all records of the generation and writes the merged out.
+cudaError_t launch_peer_exchange(const float* rec, const unsigned long long* peer_bufs, int* gen_push, int rank, int world,
+                                 int n_head, int head_dim, int fused_wait, float* out, int* status, long long wait_cycles,
+                                 int overlap, cudaStream_t stream, unsigned long long* launches);
 cudaError_t launch_peer_wait_combine(const void* my_buf, int world, float* out, int n_head, int head_dim, int* gen_wait,
                                      int* status, long long wait_cycles, int overlap, cudaStream_t stream,
                                      unsigned long long* launches);

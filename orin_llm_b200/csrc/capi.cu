@@ -280,10 +280,12 @@ static int decode_common(const float* q, const float* k_new, const float* v_new,
     a.d_pos = d_pos; a.pos_bias = pos_bias;
     a.n_head = n_head; a.n_kv = n_kv; a.head_dim = head_dim; a.n_ctx = n_ctx;
     a.n_splits = w.n_splits; a.group = w.group; a.n_groups = w.n_groups; a.min_tiles = g_decode_min_tiles; a.overlap = g_decode_overlap;
-    a.wait_cycles = g_wait_cycles;
     a.scale = scale; a.fuse = fuse; a.emit_partial = emit_partial;
-    if (peer) { a.peer_bufs = peer->bufs; a.gen_push = peer->gen_push; a.rank = peer->rank; a.world = peer->world;
-                a.fused_wait = peer->fused_wait; a.peer_status = peer->status; a.d_rope_pos = peer->rope_pos; }
+    if (peer) {
+        // the launch leaves this rank's record in the workspace; the exchange launch below sends it round
+        a.d_rope_pos = peer->rope_pos;
+        a.out = reinterpret_cast<float*>(wsb + w.rec);
+    }
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     if (g_prof_ev && g_prof_n < g_prof_cap) {
         ev0 = g_prof_ev[2 * g_prof_n];
@@ -291,7 +293,13 @@ static int decode_common(const float* q, const float* k_new, const float* v_new,
         ++g_prof_n;
     }
     cudaError_t e = launch_decode(a, (cudaStream_t)stream, &g_launches, ev0, ev1);
-    return e == cudaSuccess ? OATTN_OK : cuda_fail(e, "decode launch");
+    if (e != cudaSuccess) return cuda_fail(e, "decode launch");
+    if (peer) {
+        e = launch_peer_exchange(a.out, peer->bufs, peer->gen_push, peer->rank, peer->world, n_head, head_dim, peer->fused_wait,
+                                 out, peer->status, g_wait_cycles, g_decode_overlap, (cudaStream_t)stream, &g_launches);
+        if (e != cudaSuccess) return cuda_fail(e, "peer exchange launch");
+    }
+    return OATTN_OK;
 }
 
 int oattn_decode(const float* q, const float* k_new, const float* v_new, uint16_t* kc, uint16_t* vc, float* out,

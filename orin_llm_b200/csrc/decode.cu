@@ -314,63 +314,15 @@ __device__ __forceinline__ void emit_final(const Args& p, int kvh, int G, const 
         }
         return;
     }
-    if (!p.peer_bufs) {
-        // per-rank record {O, m, l, 0, 0}, m in natural-log units of the scaled score
-#pragma unroll
-        for (int k = 0; k < S::N; ++k) {
-            const int row = S::row(tid, k), c4 = S::col4(tid, k);
-            if (row < G) {
-                float* rec = p.out + (size_t)(kvh * G + row) * (HD + PART_PAD);
-                *reinterpret_cast<float4*>(rec + c4 * 4) = st[k].acc;
-                if (c4 == 0) *reinterpret_cast<float4*>(rec + HD) = make_float4(st[k].M * p.scale, st[k].L, 0.f, 0.f);
-            }
-        }
-        return;
-    }
-    // Peer exchange: the record goes straight into every rank's exchange buffer (plain stores over NVLink), every
-    // value tagged with the generation of the call.  Only this CTA touches the generation counters of its heads.
-    unsigned g[S::N];
-#pragma unroll
-    for (int k = 0; k < S::N; ++k) {
-        const int row = S::row(tid, k);
-        g[k] = row < G ? (unsigned)(__ldcg(p.gen_push + kvh * G + row) + 1) : 0u;
-    }
-    __syncthreads();      // every thread has read its generations before anyone advances them below
-    constexpr size_t rec_sz = HD + PART_PAD;
+    // per-rank record {O, m, l, 0, 0}, m in natural-log units of the scaled score
 #pragma unroll
     for (int k = 0; k < S::N; ++k) {
         const int row = S::row(tid, k), c4 = S::col4(tid, k);
         if (row < G) {
-            const int head = kvh * G + row;
-            for (int r = 0; r < p.world; ++r) {
-                unsigned long long* rec = reinterpret_cast<unsigned long long*>(p.peer_bufs[r]) +
-                                          ((size_t)((g[k] & 1) * p.world + p.rank) * p.n_head + head) * rec_sz;
-                peer_store_pair(rec + c4 * 4, st[k].acc.x, st[k].acc.y, g[k]);
-                peer_store_pair(rec + c4 * 4 + 2, st[k].acc.z, st[k].acc.w, g[k]);
-                if (c4 == 0) peer_store_pair(rec + HD, st[k].M * p.scale, st[k].L, g[k]);
-            }
+            float* rec = p.out + (size_t)(kvh * G + row) * (HD + PART_PAD);
+            *reinterpret_cast<float4*>(rec + c4 * 4) = st[k].acc;
+            if (c4 == 0) *reinterpret_cast<float4*>(rec + HD) = make_float4(st[k].M * p.scale, st[k].L, 0.f, 0.f);
         }
-    }
-    if (p.fused_wait) {
-        const unsigned long long* mine = reinterpret_cast<const unsigned long long*>(p.peer_bufs[p.rank]);
-#pragma unroll
-        for (int k = 0; k < S::N; ++k) {
-            const int row = S::row(tid, k), c4 = S::col4(tid, k);
-            if (row < G) {
-                const int head = kvh * G + row;
-                RunState fin;
-                const unsigned long long* recs = mine + ((size_t)(g[k] & 1) * p.world * p.n_head + head) * rec_sz;
-                if (wait_records(recs, (size_t)p.n_head * rec_sz, p.world, HD, c4, g[k], p.wait_cycles, fin))
-                    *reinterpret_cast<float4*>(p.out + (size_t)head * HD + c4 * 4) = normalised(fin);
-                else if (p.peer_status)
-                    atomicExch(p.peer_status, 1);
-            }
-        }
-    }
-#pragma unroll
-    for (int k = 0; k < S::N; ++k) {
-        const int row = S::row(tid, k);
-        if (row < G && S::col4(tid, k) == 0) p.gen_push[kvh * G + row] = (int)g[k];
     }
 }
 
@@ -457,8 +409,18 @@ __global__ void __launch_bounds__(kThreads, 2) decode_split_kernel(const DecodeA
         }
     }
 
-    // q, the new K/V row and the scratch block belong to preceding kernels
-    if (p.overlap == 2) pdl_wait();
+    // q, the new K/V row and the scratch block belong to preceding kernels.  Their values may not be read yet, but L2 can be
+    // asked to fetch the lines (a hint without a destination: whatever the preceding kernel still writes lands in the same
+    // L2 lines), which takes the HBM latency of the first read after the wait off the critical path.
+    if (p.overlap == 2) {
+        const int q_lines = (G * HD * 4 + 127) / 128;
+        if (tid < q_lines) l2_prefetch_line(reinterpret_cast<const char*>(p.q + (size_t)kvh * G * HD) + 128 * tid);
+        if (owner && append && tid >= 64 && tid < 64 + 2 * (HD * 4 / 128)) {
+            const int t2 = tid - 64, which = t2 / (HD * 4 / 128), ln = t2 % (HD * 4 / 128);
+            l2_prefetch_line(reinterpret_cast<const char*>((which ? p.v_new : p.k_new) + (size_t)kvh * HD) + 128 * ln);
+        }
+        pdl_wait();
+    }
 
     // ---- prologue: Q -> fp16 fragments, new K/V row ------------------------------------------
     // All global reads of the inputs are issued together (one round trip): q rows, then k_new and v_new, with their
@@ -750,6 +712,51 @@ __global__ void combine_records_kernel(const float* parts, int n_parts, float* o
     *reinterpret_cast<float4*>(out + (size_t)h * hd + c4 * 4) = normalised(fin);
 }
 
+// ---- record exchange between ranks, one CTA per head ----------------------------------------------------------
+// The decode launch leaves this rank's record [n_head][hd + PART_PAD] in local memory.  CTA h stores head h's record
+// straight into every rank's exchange buffer (plain stores over NVLink, one tagged word per thread and rank), then --
+// with fused_wait -- waits for every rank's record of the same generation in its own buffer and writes the merged
+// output.  One CTA per head keeps the stores of a call spread over n_head SMs: from one or two SMs the same stores take
+// several times as long (measured on 8 GPUs).  Only CTA h touches gen_push[h].
+struct PeerExchangeArgs {
+    const float* rec;
+    const unsigned long long* peer_bufs;    // device array of `world` buffer pointers (this rank's own included)
+    int* gen_push;                          // [n_head]
+    float* out;
+    int* status;
+    int rank, world, n_head, head_dim, fused_wait;
+    long long wait_cycles;
+};
+
+__global__ void __launch_bounds__(160) peer_exchange_kernel(const PeerExchangeArgs p) {
+    const int h = blockIdx.x, tid = threadIdx.x, hd = p.head_dim;
+    pdl_trigger();
+    pdl_wait();                    // the decode launch's record must be complete
+    const unsigned g = (unsigned)(__ldcg(p.gen_push + h) + 1);
+    const size_t rec_sz = hd + PART_PAD;
+    const float* mine = p.rec + (size_t)h * rec_sz;
+    if (tid < hd + 2) {
+        // thread d < hd carries O[d], threads hd and hd + 1 carry m and l (two neighbouring words of the record)
+        const float v = __ldcg(mine + tid);
+        for (int r = 0; r < p.world; ++r) {
+            unsigned long long* dst = reinterpret_cast<unsigned long long*>(p.peer_bufs[r]) +
+                                      ((size_t)((g & 1) * p.world + p.rank) * p.n_head + h) * rec_sz + tid;
+            asm volatile("st.relaxed.sys.global.u64 [%0], %1;\n" ::"l"(dst), "l"(tag_word(v, g)) : "memory");
+        }
+    }
+    if (p.fused_wait && tid * 4 < hd) {
+        const unsigned long long* recs = reinterpret_cast<const unsigned long long*>(p.peer_bufs[p.rank]) +
+                                         ((size_t)(g & 1) * p.world * p.n_head + h) * rec_sz;
+        RunState fin;
+        if (wait_records(recs, (size_t)p.n_head * rec_sz, p.world, hd, tid, g, p.wait_cycles, fin))
+            *reinterpret_cast<float4*>(p.out + (size_t)h * hd + tid * 4) = normalised(fin);
+        else if (p.status)
+            atomicExch(p.status, 1);
+    }
+    __syncthreads();
+    if (tid == 0) p.gen_push[h] = (int)g;
+}
+
 // ---- wait for every rank's record of this generation and merge them -------------------------------------------
 // One CTA per head, one thread per four dims, in a launch of its own: the form that can run after all pushes on a
 // single GPU.
@@ -901,6 +908,18 @@ cudaError_t launch_combine_records(const float* parts, int n_parts, float* out, 
     combine_records_kernel<<<n_head, 32, 0, stream>>>(parts, n_parts, out, n_head, head_dim);
     if (launches) *launches += 1;
     return cudaGetLastError();
+}
+
+cudaError_t launch_peer_exchange(const float* rec, const unsigned long long* peer_bufs, int* gen_push, int rank, int world,
+                                 int n_head, int head_dim, int fused_wait, float* out, int* status, long long wait_cycles,
+                                 int overlap, cudaStream_t stream, unsigned long long* launches) {
+    PeerExchangeArgs x;
+    x.rec = rec; x.peer_bufs = peer_bufs; x.gen_push = gen_push; x.out = out; x.status = status;
+    x.rank = rank; x.world = world; x.n_head = n_head; x.head_dim = head_dim; x.fused_wait = fused_wait;
+    x.wait_cycles = wait_cycles;
+    cudaError_t e = launch_dependent(peer_exchange_kernel, dim3(n_head), 128 + 32, 0, stream, overlap, x);
+    if (launches) *launches += 1;
+    return e;
 }
 
 cudaError_t launch_peer_wait_combine(const void* my_buf, int world, float* out, int n_head, int head_dim, int* gen_wait,

@@ -7,9 +7,9 @@ every kv head is cut into `world` contiguous slices, rank r keeping rows
     exchange of the world records                 [n_head][head_dim + 4] fp32 = {O, m, l, 0, 0} per rank
     log-sum-exp merge on every rank
 The exchange is latency-bound (8448 bytes per rank for 16 heads of 128).  Two forms:
-    PeerSplitKVDecoder   the CTA of the decode launch that finishes a kv head's merge stores the record into every rank's
+    PeerSplitKVDecoder   a small launch behind the decode launch (one CTA per head) stores the record into every rank's
                          exchange buffer over NVLink (peer stores, every value tagged with the call's generation) and
-                         waits for the others' records in its own buffer: no collective call, ONE launch per layer
+                         waits for the others' records in its own buffer: no collective call, two launches per layer
                          call, graph-capturable
     SplitKVDecoder       oattn_decode_partial -> NCCL all-gather (torch.distributed) -> oattn_combine
 
@@ -50,11 +50,11 @@ def gather_records(local, world_buf, group=None):
 
 
 class PeerSplitKVDecoder:
-    """Split-KV decode whose record exchange is done by the decode kernel itself: the CTA that finishes a kv head's
-    merge stores the record into every rank's exchange buffer with plain peer stores over NVLink (every value tagged
-    with the call's generation number), then waits (bounded) until the other ranks' values of this generation have
-    arrived in its own buffer and writes the merged output.  One launch per layer call, no collective call,
-    graph-capturable; fused=False keeps the wait in a launch of its own.
+    """Split-KV decode whose record exchange is done by a kernel of this library: a launch of one CTA per head behind the
+    decode launch stores the rank's record into every rank's exchange buffer with plain peer stores over NVLink (every
+    value tagged with the call's generation number), then waits (bounded) until the other ranks' values of this
+    generation have arrived in its own buffer and writes the merged output.  Two launches per layer call, no collective
+    call, graph-capturable; fused=False keeps the wait in a launch of its own.
     The exchange buffers come from torch's symmetric memory (CUDA VMM mappings of every rank's block).  torch would also
     bind such a block to an NVLink multicast object where the hardware has one; TORCH_SYMM_MEM_DISABLE_MULTICAST=1 is set
     here (unless the caller set it) so that none is created: the kernels use plain peer stores only, and a rank must
