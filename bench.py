@@ -43,8 +43,8 @@ PREFILL_WORKLOADS = {
 }
 # DRAM traffic of one launch of the decode kernel, from an ncu capture (dram__bytes_read.sum, dram__bytes_write.sum) of
 # a 16/2-head, 131072-row launch: reads per algorithmic K+V byte, and the writes (partials, independent of the length).
-NCU_READ_PER_KV_BYTE = 134.272 / 134.218
-NCU_WRITE_BYTES_PER_LAUNCH = 4.46e6
+NCU_READ_PER_KV_BYTE = 134.316 / 134.218
+NCU_WRITE_BYTES_PER_LAUNCH = 4.23e6
 NCU_CAPTURE = "ncu capture of decode_split_kernel<128,false>, 16/2 heads, 131072 rows"
 MIN_DISTINCT_KV_BYTES = 512 << 20      # a step of a secondary workload touches at least this much KV (4x L2)
 
