@@ -35,6 +35,7 @@ WORKLOADS = {
     "decode_7b_L4096": dict(n_head=28, n_kv=4, head_dim=128, layers=28, L=4096),
     "decode_7b_L1024": dict(n_head=28, n_kv=4, head_dim=128, layers=28, L=1024),
 }
+KV_SHIFT_WORKLOAD = "kv_shift_8b_ctx8192"
 PREFILL_WORKLOADS = {
     # Llama-3-8B attention shape: one 512-token chunk at KV offset n_past, RoPE theta 5e5 (normal pairing)
     "prefill_8b_off0": dict(n_head=32, n_kv=8, head_dim=128, batch=512, n_past=0, theta=5e5, layers=32),
@@ -783,13 +784,22 @@ def run_b200_prefill(args, w):
     print(json.dumps(bench_prefill(args, w, args.workload, args.steps, args.warmup, with_ref_cuda=not args.no_ref_cuda)))
 
 
+def run_b200_kv_shift(args):
+    import torch
+    from orin_llm_b200 import build, ops
+    build.build()
+    torch.cuda.set_device(0)
+    ops.init(0)
+    print(json.dumps(bench_kv_shift(args, reps=args.steps)))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="decode_3b_L1048576", choices=sorted(WORKLOADS) + sorted(PREFILL_WORKLOADS))
+    ap.add_argument("--workload", default="decode_3b_L1048576", choices=sorted(WORKLOADS) + sorted(PREFILL_WORKLOADS) + [KV_SHIFT_WORKLOAD])
     ap.add_argument("--layers", type=int, default=None, help="override the layer calls per step")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-ref-cuda", action="store_true", help="skip the reference-CUDA-kernel comparison leg")
@@ -800,6 +810,10 @@ def main():
     ap.add_argument("--secondary-steps", type=int, default=5)
     ap.add_argument("--no-graph", action="store_true", help="launch the step eagerly instead of replaying a CUDA graph")
     args = ap.parse_args()
+    if args.workload == KV_SHIFT_WORKLOAD:
+        if args.impl == "reference" or args.gpus != 1:
+            raise SystemExit("context rolling is timed on one GPU, on this repository's arm")
+        return run_b200_kv_shift(args)
     if args.workload in PREFILL_WORKLOADS:
         w = dict(PREFILL_WORKLOADS[args.workload])
         if args.layers:
