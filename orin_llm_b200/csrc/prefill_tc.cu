@@ -60,9 +60,11 @@ constexpr long long kWaitCycles = 2000000000LL;    // ~1 s
 constexpr long long kDrainCycles = 200000000LL;    // ~0.1 s
 constexpr float kRescaleThreshold = 4.0f;          // log2 units: P stays below 2^4 relative to the reference max
 
-enum Bar { Q_FULL = 0, K_FULL = 1, K_EMPTY = K_FULL + NKS, V_FULL = K_EMPTY + NKS, V_EMPTY = V_FULL + NVS, S_FULL = V_EMPTY + NVS,
-           P_FULL = S_FULL + NSB, PV_DONE = P_FULL + NSB, MREF = PV_DONE + 2, DRAIN = MREF + 2, XCH = DRAIN + 1, ALL_DONE = XCH + 1,
-           NBAR = ALL_DONE + 1 };
+enum Bar { Q_FULL = 0, K_FULL = 1, V_FULL = K_FULL + NKS, S_FULL = V_FULL + NVS, P_FULL = S_FULL + NSB, PV_DONE = P_FULL + NSB,
+           MREF = PV_DONE + 2, DRAIN = MREF + 2, XCH = DRAIN + 1, ALL_DONE = XCH + 1, NBAR = ALL_DONE + 1 };
+// K block j lives in ring stage j % NKS and its scores in buffer j % NSB: with NKS == NSB the commit that publishes the
+// scores (S_FULL) is also the moment the K stage is free again.  The same holds for V stage j % NVS and PV_DONE[j & 1].
+static_assert(NKS == NSB && NVS == 2, "the producer waits on S_FULL / PV_DONE for free ring stages");
 static_assert(NBAR * 8 + 16 <= 256, "barrier block");
 
 #ifndef OATTN_TC_POLY
@@ -132,19 +134,25 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+// The MMA warp runs its loop with all 32 lanes (warp-uniform control flow lets the compiler keep the descriptor arithmetic
+// on the uniform datapath: issued from a single lane inside a divergent branch, every MMA costs the lane roughly twice the
+// 64 cycles the tensor pipe needs for it, and the pipe starves).  The tcgen05 instructions themselves are executed by
+// one elected lane; with a full mask the election is the same lane every time, which tcgen05.commit relies on (it
+// tracks the MMAs of the thread that executes it).
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+    asm volatile("{\n.reg .pred e;\nelect.sync _|e, 0xffffffff;\n"
+                 "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n}\n" ::"r"(bar) : "memory");
 }
 // D[tmem] (+)= A[smem desc] * B[smem desc], fp16 inputs, fp32 accumulate, M128 N128 K16.
 __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}\n"
+    asm volatile("{\n.reg .pred p, e;\nsetp.ne.b32 p, %4, 0;\nelect.sync _|e, 0xffffffff;\n"
+                 "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}\n"
                  ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
 }
 // Same with the A operand taken from TMEM (128 lanes x 8 columns of packed fp16 pairs per K16 step).
 __device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n}\n"
+    asm volatile("{\n.reg .pred p, e;\nsetp.ne.b32 p, %4, 0;\nelect.sync _|e, 0xffffffff;\n"
+                 "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n}\n"
                  ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
 }
 // TMEM -> registers.  The load and its wait sit in ONE asm statement: the destination registers are
@@ -226,8 +234,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 
     if (tid == 0) {
         mbar_init(bar(Q_FULL), 1);
-        for (int s = 0; s < NKS; ++s) { mbar_init(bar(K_FULL + s), 1); mbar_init(bar(K_EMPTY + s), 1); }
-        for (int s = 0; s < NVS; ++s) { mbar_init(bar(V_FULL + s), 1); mbar_init(bar(V_EMPTY + s), 1); }
+        for (int s = 0; s < NKS; ++s) mbar_init(bar(K_FULL + s), 1);
+        for (int s = 0; s < NVS; ++s) mbar_init(bar(V_FULL + s), 1);
         for (int s = 0; s < NSB; ++s) { mbar_init(bar(S_FULL + s), 1); mbar_init(bar(P_FULL + s), 4); }
         for (int s = 0; s < 2; ++s) { mbar_init(bar(PV_DONE + s), 1); mbar_init(bar(MREF + s), 4); }
         mbar_init(bar(XCH), 256);
@@ -269,7 +277,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             tma_load_3d(sbase + OFF_Q + SLAB, &tmQ, 64, kvh * p.G, t0, bar(Q_FULL));
             auto load_k = [&](int j) {
                 const int s = j % NKS;
-                if (j >= NKS) ok = mbar_wait(bar(K_EMPTY + s), ((j / NKS) - 1) & 1, s_abort);
+                if (j >= NKS) ok = mbar_wait(bar(S_FULL + s), ((j / NKS) - 1) & 1, s_abort);     // S_(j-NKS) done: stage free
                 if (!ok) return;
                 mbar_expect_tx(bar(K_FULL + s), TILE);
                 tma_load_3d(sbase + OFF_K + s * TILE, &tmK, 0, j * BN, kvh, bar(K_FULL + s));
@@ -278,7 +286,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             };
             auto load_v = [&](int j) {
                 const int s = j % NVS;
-                if (j >= NVS) ok = mbar_wait(bar(V_EMPTY + s), ((j / NVS) - 1) & 1, s_abort);
+                if (j >= NVS) ok = mbar_wait(bar(PV_DONE + s), ((j / NVS) - 1) & 1, s_abort);    // P V of block j-2 done: stage free
                 if (!ok) return;
                 mbar_expect_tx(bar(V_FULL + s), TILE);
                 tma_load_3d(sbase + OFF_V + s * TILE, &tmV, 0, j * BN, kvh, bar(V_FULL + s));
@@ -302,56 +310,57 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         }
         __syncwarp();
     } else if (warp == 1) {
-        // ---------------------------------------------------------------- MMA issuer
-        if (lane == 0) {
-            bool ok = mbar_wait(bar(Q_FULL), 0, s_abort);
-            // Descriptors are built once; inside the loops only the (compile-time) k-step offset and the stage
-            // offset are added to the 14-bit address field (in 16-byte units; it cannot carry out of the field).
-            // The issuing lane shares its scheduler with two softmax warps, so every instruction between two MMAs
-            // delays the tensor pipe.
-            const uint64_t dQ = desc_kmajor(sbase + OFF_Q), dK = desc_kmajor(sbase + OFF_K), dV = desc_mnmajor(sbase + OFF_V);
-            auto issue_s = [&](int j) {
-                const int s = j % NKS, b = j % NSB;
-                ok = mbar_wait(bar(K_FULL + s), (j / NKS) & 1, s_abort);
-                if (!ok) return;
-                TRACE(0, 0, j);
-                tc_fence_after();
-                const uint64_t dKs = dK + (uint64_t)((s * TILE) >> 4);
-                const uint32_t d = TM_S + b * BN;
+        // ---------------------------------------------------------------- MMA issuer (all lanes walk the loop)
+        bool ok = __all_sync(0xffffffffu, mbar_wait(bar(Q_FULL), 0, s_abort));
+        // Descriptors are built once; inside the loops only the (compile-time) k-step offset and the stage offset are
+        // added to the 14-bit address field (in 16-byte units; it cannot carry out of the field).
+        const uint64_t dQ = desc_kmajor(sbase + OFF_Q), dK = desc_kmajor(sbase + OFF_K), dV = desc_mnmajor(sbase + OFF_V);
+        // S_j = Q K_j^T into score buffer j % NSB.  `first`: the buffer has not been used yet, so no softmax thread's
+        // TMEM reads have to be ordered in front of the MMAs (afterwards the fence in front of P_(j-NSB) V_(j-NSB), issued
+        // just before, covers the buffer's last readers).
+        auto issue_s = [&](int j, int s, uint32_t parity) {
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(K_FULL + s), parity, s_abort));
+            if (!ok) return;
+            if (lane == 0) TRACE(0, 0, j);
+            const uint64_t dKs = dK + (uint64_t)((s * TILE) >> 4);
+            const uint32_t d = TM_S + s * BN;
 #pragma unroll
-                for (int kk = 0; kk < HD / 16; ++kk) {
-                    const uint64_t off = (uint64_t)((((kk >> 2) * SLAB) + (kk & 3) * 32) >> 4);
-                    tc_mma(d, dQ + off, dKs + off, IDESC_S, kk > 0);
-                }
-                tc_commit(bar(S_FULL + b));
-                tc_commit(bar(K_EMPTY + s));
-            };
-            for (int j = 0; j < NSB && j < nb && ok; ++j) issue_s(j);
-            for (int j = 0; j < nb && ok; ++j) {
-                const int b = j % NSB, sv = j % NVS;
-                ok = mbar_wait(bar(P_FULL + b), (j / NSB) & 1, s_abort);
-                TRACE(0, 1, j);
-                if (ok) ok = mbar_wait(bar(V_FULL + sv), (j / NVS) & 1, s_abort);
-                if (!ok) break;
-                TRACE(0, 2, j);
-                tc_fence_after();
-                const uint64_t dVs = dV + (uint64_t)((sv * TILE) >> 4);
-                const uint32_t a_t = TM_S + b * BN;
-                const uint32_t acc0 = j > 0 ? 1u : 0u;
+            for (int kk = 0; kk < HD / 16; ++kk) {
+                const uint64_t off = (uint64_t)((((kk >> 2) * SLAB) + (kk & 3) * 32) >> 4);
+                tc_mma(d, dQ + off, dKs + off, IDESC_S, kk > 0);
+            }
+            tc_commit(bar(S_FULL + s));        // scores ready; K stage s free
+        };
+        tc_fence_after();
+        for (int j = 0; j < NSB && j < nb && ok; ++j) issue_s(j, j, 0);
+        int b = 0;                      // j % NSB
+        uint32_t ph3 = 0, ph2 = 0;      // (j / NSB) & 1, (j / 2) & 1
+        for (int j = 0; j < nb && ok; ++j) {
+            const int sv = j & 1;
+            ok = __all_sync(0xffffffffu, mbar_wait(bar(P_FULL + b), ph3, s_abort));
+            if (lane == 0) TRACE(0, 1, j);
+            if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(V_FULL + sv), ph2, s_abort));
+            if (!ok) break;
+            if (lane == 0) TRACE(0, 2, j);
+            tc_fence_after();
+            const uint64_t dVs = dV + (uint64_t)((sv * TILE) >> 4);
+            const uint32_t a_t = TM_S + b * BN;
+            const uint32_t acc0 = j > 0 ? 1u : 0u;
 #pragma unroll
-                for (int kk = 0; kk < BN / 16; ++kk)                              // V: 16 rows of 128 B per k-step
-                    tc_mma_ts(TM_O, a_t + kk * 8, dVs + (uint64_t)((kk * 2048) >> 4), IDESC_PV, kk > 0 ? 1u : acc0);
-                tc_commit(bar(PV_DONE + (j & 1)));
-                tc_commit(bar(V_EMPTY + sv));
-                TRACE(0, 3, j);
-                // score buffer b is free again once P_j V_j has been issued (the tensor pipe runs in order)
-                if (j + NSB < nb) issue_s(j + NSB);
-            }
-            if (ok) tc_commit(bar(ALL_DONE));
-            if (*s_abort) {
-                tc_commit(bar(DRAIN));
-                mbar_drain(bar(DRAIN), 0);
-            }
+            for (int kk = 0; kk < BN / 16; ++kk)                              // V: 16 rows of 128 B per k-step
+                tc_mma_ts(TM_O, a_t + kk * 8, dVs + (uint64_t)((kk * 2048) >> 4), IDESC_PV, kk > 0 ? 1u : acc0);
+            tc_commit(bar(PV_DONE + sv));      // accumulator complete up to block j; V stage sv free
+            if (lane == 0) TRACE(0, 3, j);
+            // score buffer b is free again once P_j V_j has been issued (the tensor pipe runs in order); K block j + NSB
+            // arrives in the stage of the same index, in that stage's next phase
+            if (j + NSB < nb) issue_s(j + NSB, b, ph3 ^ 1u);
+            if (++b == NSB) { b = 0; ph3 ^= 1u; }
+            ph2 ^= (uint32_t)sv;
+        }
+        if (ok) tc_commit(bar(ALL_DONE));
+        if (*s_abort) {
+            tc_commit(bar(DRAIN));
+            mbar_drain(bar(DRAIN), 0);
         }
         __syncwarp();
     } else {
