@@ -108,6 +108,13 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
                  : "=r"(ok) : "r"(bar), "r"(parity), "r"(1000000u) : "memory");
     return ok != 0;
 }
+// Non-blocking look at a phase (no suspend): used to take a barrier's latency off the MMA warp's critical path.
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
 // Bounded wait.  Returns false when the abort flag is up or the time limit passed (and raises the flag).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* s_abort) {
     if (mbar_try(bar, parity)) return true;
@@ -134,26 +141,76 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
-// The MMA warp runs its loop with all 32 lanes (warp-uniform control flow lets the compiler keep the descriptor arithmetic
-// on the uniform datapath: issued from a single lane inside a divergent branch, every MMA costs the lane roughly twice the
-// 64 cycles the tensor pipe needs for it, and the pipe starves).  The tcgen05 instructions themselves are executed by
-// one elected lane; with a full mask the election is the same lane every time, which tcgen05.commit relies on (it
-// tracks the MMAs of the thread that executes it).
+// The MMA warp runs its loop with all 32 lanes: warp-uniform control flow lets the compiler keep the descriptor arithmetic
+// on the uniform datapath.  (Issued from one lane inside a divergent branch, every MMA cost the lane about twice the 64
+// cycles the tensor pipe needs for it.)  The pipe's queue is shallow: it hides only about a hundred cycles between two
+// groups of MMAs, so the instruction count of this warp is what decides whether the pipe starves.  Hence one election
+// per group of eight MMAs, with the group's commits in the same predicated block.  With a full mask the election is the
+// same lane every time, which tcgen05.commit relies on (it tracks the MMAs of the thread that executes it).
+// S = Q K^T: eight K16 steps, D[tmem] = A[smem desc] * B[smem desc], fp16 in, fp32 out, M128 N128; the first step
+// overwrites.  Then commit to bar_a.
+__device__ __forceinline__ void tc_group_ss(uint32_t d_tmem, const uint64_t (&a)[8], const uint64_t (&b)[8], uint32_t idesc,
+                                            uint32_t bar_a) {
+    asm volatile("{\n.reg .pred e, pt, pf;\n"
+                 "elect.sync _|e, 0xffffffff;\n"
+                 "setp.eq.u32 pt, %2, 0;\n"
+                 "setp.ne.u32 pf, %2, 0;\n"
+                 "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %5, %13, %1, {%2, %2, %2, %2}, pf;\n"
+                 "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %6, %14, %1, {%2, %2, %2, %2}, pt;\n"
+                 "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %7, %15, %1, {%2, %2, %2, %2}, pt;\n"
+                 "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %8, %16, %1, {%2, %2, %2, %2}, pt;\n"
+                 "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %9, %17, %1, {%2, %2, %2, %2}, pt;\n"
+                 "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %10, %18, %1, {%2, %2, %2, %2}, pt;\n"
+                 "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %11, %19, %1, {%2, %2, %2, %2}, pt;\n"
+                 "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %12, %20, %1, {%2, %2, %2, %2}, pt;\n"
+                 "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%3];\n}\n"
+                 ::"r"(d_tmem), "r"(idesc), "r"(0u), "r"(bar_a), "r"(0u),
+                   "l"(a[0]), "l"(a[1]), "l"(a[2]), "l"(a[3]), "l"(a[4]), "l"(a[5]), "l"(a[6]), "l"(a[7]),
+                   "l"(b[0]), "l"(b[1]), "l"(b[2]), "l"(b[3]), "l"(b[4]), "l"(b[5]), "l"(b[6]), "l"(b[7]) : "memory");
+}
+// O (+)= P V: eight K16 steps with A from TMEM (128 lanes x 8 columns of packed fp16 pairs per step) and B[smem desc];
+// the first step accumulates only if `acc0`.  Then commit to bar_a.
+__device__ __forceinline__ void tc_group_ts(uint32_t d_tmem, uint32_t a_tmem, const uint64_t (&b)[8], uint32_t idesc, uint32_t acc0,
+                                            uint32_t bar_a) {
+    asm volatile("{\n.reg .pred e, pt, p0;\n.reg .b32 t;\n"
+                 "elect.sync _|e, 0xffffffff;\n"
+                 "setp.eq.u32 pt, %2, 0;\n"
+                 "setp.ne.u32 p0, %4, 0;\n"
+                 "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%5], %6, %1, {%2, %2, %2, %2}, p0;\n"
+                 "add.u32 t, %5, 8;\n"
+                 "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [t], %7, %1, {%2, %2, %2, %2}, pt;\n"
+                 "add.u32 t, %5, 16;\n"
+                 "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [t], %8, %1, {%2, %2, %2, %2}, pt;\n"
+                 "add.u32 t, %5, 24;\n"
+                 "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [t], %9, %1, {%2, %2, %2, %2}, pt;\n"
+                 "add.u32 t, %5, 32;\n"
+                 "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [t], %10, %1, {%2, %2, %2, %2}, pt;\n"
+                 "add.u32 t, %5, 40;\n"
+                 "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [t], %11, %1, {%2, %2, %2, %2}, pt;\n"
+                 "add.u32 t, %5, 48;\n"
+                 "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [t], %12, %1, {%2, %2, %2, %2}, pt;\n"
+                 "add.u32 t, %5, 56;\n"
+                 "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [t], %13, %1, {%2, %2, %2, %2}, pt;\n"
+                 "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%3];\n}\n"
+                 ::"r"(d_tmem), "r"(idesc), "r"(0u), "r"(bar_a), "r"(acc0), "r"(a_tmem),
+                   "l"(b[0]), "l"(b[1]), "l"(b[2]), "l"(b[3]), "l"(b[4]), "l"(b[5]), "l"(b[6]), "l"(b[7]) : "memory");
+}
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
     asm volatile("{\n.reg .pred e;\nelect.sync _|e, 0xffffffff;\n"
                  "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n}\n" ::"r"(bar) : "memory");
 }
-// D[tmem] (+)= A[smem desc] * B[smem desc], fp16 inputs, fp32 accumulate, M128 N128 K16.
-__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n.reg .pred p, e;\nsetp.ne.b32 p, %4, 0;\nelect.sync _|e, 0xffffffff;\n"
-                 "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n}\n"
-                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
-}
-// Same with the A operand taken from TMEM (128 lanes x 8 columns of packed fp16 pairs per K16 step).
-__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n.reg .pred p, e;\nsetp.ne.b32 p, %4, 0;\nelect.sync _|e, 0xffffffff;\n"
-                 "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n}\n"
-                 ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+// Wait of the MMA warp: every lane polls (one warp instruction), no vote.  A time-out raises the abort flag and returns;
+// the warp's loop looks at the flag once per block, with a vote, so all lanes leave together.
+__device__ __forceinline__ void mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* s_abort) {
+    if (mbar_try(bar, parity)) return;
+    const long long t0 = clock64();
+    int spins = 0;
+    while (!mbar_try(bar, parity)) {
+        if ((++spins & 31) == 0) {
+            if (*s_abort) return;
+            if (clock64() - t0 > kWaitCycles) { *s_abort = 1; return; }
+        }
+    }
 }
 // TMEM -> registers.  The load and its wait sit in ONE asm statement: the destination registers are
 // written asynchronously, and nothing (not even a compiler-generated register move) may touch them before
@@ -311,54 +368,73 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         __syncwarp();
     } else if (warp == 1) {
         // ---------------------------------------------------------------- MMA issuer (all lanes walk the loop)
-        bool ok = __all_sync(0xffffffffu, mbar_wait(bar(Q_FULL), 0, s_abort));
-        // Descriptors are built once; inside the loops only the (compile-time) k-step offset and the stage offset are
-        // added to the 14-bit address field (in 16-byte units; it cannot carry out of the field).
-        const uint64_t dQ = desc_kmajor(sbase + OFF_Q), dK = desc_kmajor(sbase + OFF_K), dV = desc_mnmajor(sbase + OFF_V);
-        // S_j = Q K_j^T into score buffer j % NSB.  `first`: the buffer has not been used yet, so no softmax thread's
-        // TMEM reads have to be ordered in front of the MMAs (afterwards the fence in front of P_(j-NSB) V_(j-NSB), issued
-        // just before, covers the buffer's last readers).
-        auto issue_s = [&](int j, int s, uint32_t parity) {
-            ok = __all_sync(0xffffffffu, mbar_wait(bar(K_FULL + s), parity, s_abort));
-            if (!ok) return;
-            if (lane == 0) TRACE(0, 0, j);
-            const uint64_t dKs = dK + (uint64_t)((s * TILE) >> 4);
-            const uint32_t d = TM_S + s * BN;
+        mbar_wait_warp(bar(Q_FULL), 0, s_abort);
+        // Descriptors are built once: per k-step for Q, per ring stage and k-step for K and V (the offsets are added to the
+        // 14-bit address field, in 16-byte units; it cannot carry out of the field).
+        uint64_t dQ[8], dK0[8], dV0[8];
 #pragma unroll
-            for (int kk = 0; kk < HD / 16; ++kk) {
-                const uint64_t off = (uint64_t)((((kk >> 2) * SLAB) + (kk & 3) * 32) >> 4);
-                tc_mma(d, dQ + off, dKs + off, IDESC_S, kk > 0);
-            }
-            tc_commit(bar(S_FULL + s));        // scores ready; K stage s free
+        for (int kk = 0; kk < 8; ++kk) {
+            const uint32_t off = (uint32_t)((kk >> 2) * SLAB + (kk & 3) * 32);
+            dQ[kk] = desc_kmajor(sbase + OFF_Q + off);
+            dK0[kk] = desc_kmajor(sbase + OFF_K + off);
+            dV0[kk] = desc_mnmajor(sbase + OFF_V + kk * 2048);       // V: 16 rows of 128 B per k-step
+        }
+        // S_j = Q K_j^T into score buffer s = j % NSB, K from ring stage s.  The commit publishes the scores and frees the
+        // K stage.
+        auto issue_s = [&](int j, int s) {
+            if (lane == 0) TRACE(0, 0, j);
+            uint64_t dKs[8];
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk) dKs[kk] = dK0[kk] + (uint64_t)((s * TILE) >> 4);
+            tc_group_ss(TM_S + s * BN, dQ, dKs, IDESC_S, bar(S_FULL + s));
         };
         tc_fence_after();
-        for (int j = 0; j < NSB && j < nb && ok; ++j) issue_s(j, j, 0);
+        for (int j = 0; j < NSB && j < nb; ++j) {
+            mbar_wait_warp(bar(K_FULL + j), 0, s_abort);
+            issue_s(j, j);
+        }
+        // An MMA group keeps this warp inside its issue for about as long as the group runs (the pipe's queue is shallow),
+        // and whatever the warp does between two groups is time the tensor pipe idles.  So the barriers a group needs are
+        // looked at (non-blocking) before the group in front of it is issued: their latency passes while that group
+        // runs, and only a barrier that really is late costs a wait.
         int b = 0;                      // j % NSB
         uint32_t ph3 = 0, ph2 = 0;      // (j / NSB) & 1, (j / 2) & 1
-        for (int j = 0; j < nb && ok; ++j) {
+        bool rdy_p = false, rdy_v = false;
+        for (int j = 0; j < nb; ++j) {
+            if ((j & 3) == 0 && __any_sync(0xffffffffu, *s_abort != 0)) break;      // all lanes leave together
             const int sv = j & 1;
-            ok = __all_sync(0xffffffffu, mbar_wait(bar(P_FULL + b), ph3, s_abort));
+            if (!rdy_p) mbar_wait_warp(bar(P_FULL + b), ph3, s_abort);
             if (lane == 0) TRACE(0, 1, j);
-            if (ok) ok = __all_sync(0xffffffffu, mbar_wait(bar(V_FULL + sv), ph2, s_abort));
-            if (!ok) break;
+            if (!rdy_v) mbar_wait_warp(bar(V_FULL + sv), ph2, s_abort);
             if (lane == 0) TRACE(0, 2, j);
             tc_fence_after();
-            const uint64_t dVs = dV + (uint64_t)((sv * TILE) >> 4);
-            const uint32_t a_t = TM_S + b * BN;
-            const uint32_t acc0 = j > 0 ? 1u : 0u;
+            // K block j + NSB arrives in the ring stage b, in that stage's next phase
+            const bool do_s = j + NSB < nb;
+            const bool rdy_k = do_s && mbar_test(bar(K_FULL + b), ph3 ^ 1u);
+            uint64_t dVs[8];
 #pragma unroll
-            for (int kk = 0; kk < BN / 16; ++kk)                              // V: 16 rows of 128 B per k-step
-                tc_mma_ts(TM_O, a_t + kk * 8, dVs + (uint64_t)((kk * 2048) >> 4), IDESC_PV, kk > 0 ? 1u : acc0);
-            tc_commit(bar(PV_DONE + sv));      // accumulator complete up to block j; V stage sv free
+            for (int kk = 0; kk < 8; ++kk) dVs[kk] = dV0[kk] + (uint64_t)((sv * TILE) >> 4);
+            // commit: accumulator complete up to block j; V stage sv free
+            tc_group_ts(TM_O, TM_S + b * BN, dVs, IDESC_PV, j > 0 ? 1u : 0u, bar(PV_DONE + sv));
             if (lane == 0) TRACE(0, 3, j);
-            // score buffer b is free again once P_j V_j has been issued (the tensor pipe runs in order); K block j + NSB
-            // arrives in the stage of the same index, in that stage's next phase
-            if (j + NSB < nb) issue_s(j + NSB, b, ph3 ^ 1u);
-            if (++b == NSB) { b = 0; ph3 ^= 1u; }
-            ph2 ^= (uint32_t)sv;
+            // what the next block's P V needs, looked at before the S group below is issued
+            const int bn = (b + 1 == NSB) ? 0 : b + 1;
+            const uint32_t ph3n = (b + 1 == NSB) ? ph3 ^ 1u : ph3, ph2n = ph2 ^ (uint32_t)sv;
+            rdy_p = rdy_v = false;
+            if (j + 1 < nb) {
+                rdy_p = mbar_test(bar(P_FULL + bn), ph3n);
+                rdy_v = mbar_test(bar(V_FULL + (sv ^ 1)), ph2n);
+            }
+            // score buffer b is free again once P_j V_j has been issued (the tensor pipe runs in order)
+            if (do_s) {
+                if (!rdy_k) mbar_wait_warp(bar(K_FULL + b), ph3 ^ 1u, s_abort);
+                issue_s(j + NSB, b);
+            }
+            b = bn; ph3 = ph3n; ph2 = ph2n;
         }
+        const bool ok = !__any_sync(0xffffffffu, *s_abort != 0);
         if (ok) tc_commit(bar(ALL_DONE));
-        if (*s_abort) {
+        if (!ok) {
             tc_commit(bar(DRAIN));
             mbar_drain(bar(DRAIN), 0);
         }
