@@ -13,13 +13,15 @@
 //   warp 0   (one lane)  TMA producer: Q tile once, then 128-row K blocks (three-stage ring) and V blocks
 //                        (two-stage ring) with cp.async.bulk.tensor, 128-byte swizzle, no multicast; rows
 //                        past the chunk are outside the tensor map and arrive as zeros
-//   warp 1   (one lane)  tcgen05.mma issuer: S_j = Q K_j^T (M128 N128 K16 x8, both operands from shared
+//   warp 1   (all lanes) tcgen05.mma issuer: S_j = Q K_j^T (M128 N128 K16 x8, both operands from shared
 //                        memory) into one of THREE TMEM score buffers, so that the scores of blocks j+1 and
 //                        j+2 are already there while block j is in the softmax; O += P_j V_j with P read
 //                        straight from TMEM (it overwrites the first 64 columns of its own score buffer as
 //                        packed fp16 pairs) and V as MN-major B operand from shared memory, into the one
-//                        TMEM accumulator; tcgen05.commit signals the mbarriers.  Descriptors are built
-//                        once; only offsets are added per MMA.
+//                        TMEM accumulator.  The warp walks its loop with all 32 lanes and one elected lane
+//                        executes the tcgen05 instructions: eight MMAs and the commit of a group in one
+//                        predicated block, descriptors built once.  The commit behind S_j also frees K ring
+//                        stage j % 3, the commit behind P_j V_j also frees V ring stage j & 1.
 //   warps 2-5, 6-9       two softmax teams, one thread per row each, taking alternate KV blocks.  Per block:
 //                        tcgen05.ld of the 128-column score row, causal mask, row max; the reference max is a
 //                        single chain over all blocks, handed from team to team through shared memory (block
@@ -27,9 +29,18 @@
 //                        (only when the max grows by more than 2^4, after the previous P V has completed);
 //                        exp2; fp16 P stored back to TMEM (tcgen05.st).  Each thread keeps its own partial
 //                        row sum; the two are added at the end and O/l goes to global memory.
-// TMEM: 3 x 128 score columns + 128 accumulator columns = 512.  With three score buffers the tensor pipe is
-// never waiting for a softmax: the loop is bound by the MMAs (about 1770 cycles per block, of which the
-// S = Q K^T MMAs, which read both operands from shared memory, take about 1070).
+// TMEM: 3 x 128 score columns + 128 accumulator columns = 512.
+//
+// What bounds the loop (measured with clock stamps and with a stand-alone issue-rate kernel): an M128 N128 K16 MMA
+// takes the tensor pipe 64 cycles, 1024 per KV block, whether its A operand comes from shared memory or from TMEM and
+// whatever TMA copies, TMEM loads/stores and exp2 work run beside it.  But the pipe's queue is shallow: the issuing warp
+// sits inside an MMA group for about as long as the group runs, and every cycle it spends between two groups (barrier
+// waits, fences, address arithmetic) is a cycle the pipe idles -- hence the warp-uniform issue, the single election per
+// group and the non-blocking look at the next barriers before a group is issued.  With that the loop is bound by the
+// softmax side: one KV block takes a team about 2500-3000 cycles from scores ready to P stored, two teams alternate,
+// and the score buffer of block j is tied up from S_j until P_j V_j has run; about 1650 cycles per block result.
+// (Scores two blocks ahead in buffers of their own, P in separate buffers: measured, slower -- the extra hand-over
+// and the wait for the P buffer lengthen the softmax, which is the bound.)
 //
 // Every mbarrier wait is bounded: after about a second without progress the kernel raises an abort
 // flag, every role leaves its loop, outstanding copies and MMAs are drained (bounded again), TMEM is
