@@ -70,6 +70,8 @@ struct DecodeArgs {
     int fuse;
     RopeArgs rope;
     int emit_partial;      // write the un-normalised record instead of the normalised output
+    int defer_final = 0;   // with emit_partial: stop after the first merge level and leave the kv head's group results
+                           // (grp_o / grp_ml, group 0 when there is only one) to the exchange launch, which merges them
     PreArgs pre;                   // optional bias / per-head RMSNorm in front of RoPE
     const int* d_rope_pos = nullptr;   // position used for RoPE when it is not the local row index (sharded cache)
     int8_t* out_qs = nullptr;      // optional q8_1 form of the output: int8 [n_head*hd] ...
@@ -97,11 +99,11 @@ cudaError_t launch_decode(const DecodeArgs& a, cudaStream_t stream, unsigned lon
 cudaError_t launch_combine_records(const float* parts, int n_parts, float* out, int n_head, int head_dim,
                                    cudaStream_t stream, unsigned long long* launches);
 
-// Stores this rank's record (left by a decode launch with emit_partial) into every rank's exchange buffer and, with
-// fused_wait, waits for all records of the generation and writes the merged out.
-cudaError_t launch_peer_exchange(const float* rec, const unsigned long long* peer_bufs, int* gen_push, int rank, int world,
-                                 int n_head, int head_dim, int fused_wait, float* out, int* status, long long wait_cycles,
-                                 int overlap, cudaStream_t stream, unsigned long long* launches);
+// Merges the group results a decode launch with defer_final left for each kv head into this rank's record, stores it into
+// every rank's exchange buffer and, with fused_wait, waits for all records of the generation and writes the merged out.
+cudaError_t launch_peer_exchange(const DecodeArgs& d, const unsigned long long* peer_bufs, int* gen_push, int rank, int world,
+                                 int fused_wait, float* out, int* status, long long wait_cycles, int overlap,
+                                 cudaStream_t stream, unsigned long long* launches);
 cudaError_t launch_peer_wait_combine(const void* my_buf, int world, float* out, int n_head, int head_dim, int* gen_wait,
                                      int* status, long long wait_cycles, int overlap, cudaStream_t stream,
                                      unsigned long long* launches);

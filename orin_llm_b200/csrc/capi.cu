@@ -285,6 +285,7 @@ static int decode_common(const float* q, const float* k_new, const float* v_new,
         // the launch leaves this rank's record in the workspace; the exchange launch below sends it round
         a.d_rope_pos = peer->rope_pos;
         a.out = reinterpret_cast<float*>(wsb + w.rec);
+        a.defer_final = 1;            // the kv heads' group results are merged by the exchange launch
     }
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     if (g_prof_ev && g_prof_n < g_prof_cap) {
@@ -295,8 +296,8 @@ static int decode_common(const float* q, const float* k_new, const float* v_new,
     cudaError_t e = launch_decode(a, (cudaStream_t)stream, &g_launches, ev0, ev1);
     if (e != cudaSuccess) return cuda_fail(e, "decode launch");
     if (peer) {
-        e = launch_peer_exchange(a.out, peer->bufs, peer->gen_push, peer->rank, peer->world, n_head, head_dim, peer->fused_wait,
-                                 out, peer->status, g_wait_cycles, g_decode_overlap, (cudaStream_t)stream, &g_launches);
+        e = launch_peer_exchange(a, peer->bufs, peer->gen_push, peer->rank, peer->world, peer->fused_wait, out, peer->status,
+                                 g_wait_cycles, g_decode_overlap, (cudaStream_t)stream, &g_launches);
         if (e != cudaSuccess) return cuda_fail(e, "peer exchange launch");
     }
     return OATTN_OK;

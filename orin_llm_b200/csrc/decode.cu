@@ -352,7 +352,8 @@ __global__ void __launch_bounds__(kThreads, 2) decode_split_kernel(const DecodeA
         RunState st[S::N];
 #pragma unroll
         for (int k = 0; k < S::N; ++k) st[k] = run_empty();
-        emit_final<HD, WIDE>(p, kvh, G, st);
+        if (p.defer_final) store_part<HD, WIDE>(p.grp_o + (size_t)kvh * p.n_groups * G * HD, p.grp_ml + (size_t)kvh * p.n_groups * G * 2, G, st);
+        else emit_final<HD, WIDE>(p, kvh, G, st);
         return;
     }
     const int tile0 = split * plan.tiles_per_split;
@@ -658,11 +659,12 @@ __global__ void __launch_bounds__(kThreads, 2) decode_split_kernel(const DecodeA
     }
 
     // ---- merge across the CTAs of this kv head -------------------------------------------------------------------
+    const size_t blk = (size_t)G * HD;       // floats of one partial
     if (plan.active == 1) {
-        emit_final<HD, WIDE>(p, kvh, G, st);
+        if (p.defer_final) store_part<HD, WIDE>(p.grp_o + (size_t)kvh * p.n_groups * blk, p.grp_ml + (size_t)kvh * p.n_groups * G * 2, G, st);
+        else emit_final<HD, WIDE>(p, kvh, G, st);
         return;
     }
-    const size_t blk = (size_t)G * HD;       // floats of one partial
     {
         const size_t part = (size_t)kvh * p.n_splits + split;
         store_part<HD, WIDE>(p.ws_o + part * blk, p.ws_ml + part * G * 2, G, st);
@@ -677,6 +679,12 @@ __global__ void __launch_bounds__(kThreads, 2) decode_split_kernel(const DecodeA
         merge_parts<HD, WIDE>(p.ws_o + part0 * blk, p.ws_ml + part0 * G * 2, grp_n, G, c, st);
     }
     const int n_grp = (plan.active + group - 1) / group;
+    if (p.defer_final) {
+        // the exchange launch behind this one merges the kv head's group results (same plan, same order)
+        const size_t gpart = (size_t)kvh * p.n_groups + grp;
+        store_part<HD, WIDE>(p.grp_o + gpart * blk, p.grp_ml + gpart * G * 2, G, st);
+        return;
+    }
     if (n_grp > 1) {
         const size_t gpart = (size_t)kvh * p.n_groups + grp;
         store_part<HD, WIDE>(p.grp_o + gpart * blk, p.grp_ml + gpart * G * 2, G, st);
@@ -719,7 +727,11 @@ __global__ void combine_records_kernel(const float* parts, int n_parts, float* o
 // output.  One CTA per head keeps the stores of a call spread over n_head SMs: from one or two SMs the same stores take
 // several times as long (measured on 8 GPUs).  Only CTA h touches gen_push[h].
 struct PeerExchangeArgs {
-    const float* rec;
+    const float* grp_o;                     // group results of the decode launch: [n_kv][n_groups][G][hd]
+    const float* grp_ml;                    //                                     [n_kv][n_groups][G][2]  (M, L)
+    const int* d_pos;
+    int pos_bias, n_ctx, n_splits, min_tiles, group, n_groups, n_kv;
+    float scale;
     const unsigned long long* peer_bufs;    // device array of `world` buffer pointers (this rank's own included)
     int* gen_push;                          // [n_head]
     float* out;
@@ -731,13 +743,49 @@ struct PeerExchangeArgs {
 __global__ void __launch_bounds__(160) peer_exchange_kernel(const PeerExchangeArgs p) {
     const int h = blockIdx.x, tid = threadIdx.x, hd = p.head_dim;
     pdl_trigger();
-    pdl_wait();                    // the decode launch's record must be complete
+    // how many group results the decode launch left for this kv head: its own plan, from the same position word
+    const int G = p.n_head / p.n_kv, kvh = h / G, row = h - kvh * G;
+    pdl_wait();                    // the decode launch's group results must be complete
     const unsigned g = (unsigned)(__ldcg(p.gen_push + h) + 1);
     const size_t rec_sz = hd + PART_PAD;
-    const float* mine = p.rec + (size_t)h * rec_sz;
     if (tid < hd + 2) {
-        // thread d < hd carries O[d], threads hd and hd + 1 carry m and l (two neighbouring words of the record)
-        const float v = __ldcg(mine + tid);
+        const int npos = clamp_len(__ldcg(p.d_pos) + p.pos_bias, p.n_ctx);
+        const SplitPlan plan = plan_splits(npos, p.n_splits, p.min_tiles);
+        const int group = plan.active <= 16 ? max(plan.active, 1) : p.group;
+        const int n_grp = plan.active <= 1 ? 1 : (plan.active + group - 1) / group;
+        // thread d < hd carries O[d], threads hd and hd + 1 carry m and l (two neighbouring words of the record).  Every
+        // thread reads all (M, L) pairs (a broadcast from L2) and its own column of every group: one round of loads.
+        const float c = p.scale * LOG2E;
+        const float* go = p.grp_o + ((size_t)kvh * p.n_groups * G + row) * hd;
+        const float* gml = p.grp_ml + ((size_t)kvh * p.n_groups * G + row) * 2;
+        float M = -CUDART_INF_F, L = 0.f, acc = 0.f;
+        for (int i0 = 0; i0 < n_grp; i0 += 16) {
+            float2 ml[16];
+            float o[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                ml[i] = make_float2(-CUDART_INF_F, 0.f);
+                o[i] = 0.f;
+                if (i0 + i < n_grp) {
+                    ml[i] = __ldcg(reinterpret_cast<const float2*>(gml + (size_t)(i0 + i) * G * 2));
+                    if (tid < hd) o[i] = __ldcg(go + (size_t)(i0 + i) * G * hd + tid);
+                }
+            }
+            float m_new = M;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) m_new = fmaxf(m_new, ml[i].x);
+            const float a = (m_new == -CUDART_INF_F || M == -CUDART_INF_F) ? 0.f : fast_exp2((M - m_new) * c);
+            L *= a; acc *= a;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {          // groups are added in index order
+                const float w = (m_new == -CUDART_INF_F || ml[i].x == -CUDART_INF_F) ? 0.f : fast_exp2((ml[i].x - m_new) * c);
+                L = fmaf(w, ml[i].y, L);
+                acc = fmaf(w, o[i], acc);
+            }
+            M = m_new;
+        }
+        // the record carries m in natural-log units of the scaled score
+        const float v = tid < hd ? acc : (tid == hd ? M * p.scale : L);
         for (int r = 0; r < p.world; ++r) {
             unsigned long long* dst = reinterpret_cast<unsigned long long*>(p.peer_bufs[r]) +
                                       ((size_t)((g & 1) * p.world + p.rank) * p.n_head + h) * rec_sz + tid;
@@ -910,14 +958,17 @@ cudaError_t launch_combine_records(const float* parts, int n_parts, float* out, 
     return cudaGetLastError();
 }
 
-cudaError_t launch_peer_exchange(const float* rec, const unsigned long long* peer_bufs, int* gen_push, int rank, int world,
-                                 int n_head, int head_dim, int fused_wait, float* out, int* status, long long wait_cycles,
-                                 int overlap, cudaStream_t stream, unsigned long long* launches) {
+cudaError_t launch_peer_exchange(const DecodeArgs& d, const unsigned long long* peer_bufs, int* gen_push, int rank, int world,
+                                 int fused_wait, float* out, int* status, long long wait_cycles, int overlap,
+                                 cudaStream_t stream, unsigned long long* launches) {
     PeerExchangeArgs x;
-    x.rec = rec; x.peer_bufs = peer_bufs; x.gen_push = gen_push; x.out = out; x.status = status;
-    x.rank = rank; x.world = world; x.n_head = n_head; x.head_dim = head_dim; x.fused_wait = fused_wait;
+    x.grp_o = d.grp_o; x.grp_ml = d.grp_ml; x.d_pos = d.d_pos; x.pos_bias = d.pos_bias; x.n_ctx = d.n_ctx;
+    x.n_splits = d.n_splits; x.min_tiles = d.min_tiles; x.group = d.group; x.n_groups = d.n_groups; x.n_kv = d.n_kv;
+    x.scale = d.scale;
+    x.peer_bufs = peer_bufs; x.gen_push = gen_push; x.out = out; x.status = status;
+    x.rank = rank; x.world = world; x.n_head = d.n_head; x.head_dim = d.head_dim; x.fused_wait = fused_wait;
     x.wait_cycles = wait_cycles;
-    cudaError_t e = launch_dependent(peer_exchange_kernel, dim3(n_head), 128 + 32, 0, stream, overlap, x);
+    cudaError_t e = launch_dependent(peer_exchange_kernel, dim3(d.n_head), 128 + 32, 0, stream, overlap, x);
     if (launches) *launches += 1;
     return e;
 }

@@ -18,10 +18,11 @@ def dev(a):
     return torch.from_numpy(np.ascontiguousarray(a)).cuda()
 
 
+@pytest.mark.parametrize("L", [5000, 40000])      # per rank: one merge level in the decode launch / several group results
 @pytest.mark.parametrize("world", [2, 4])
-def test_push_then_wait_on_one_device(ops, oracle, world):
+def test_push_then_wait_on_one_device(ops, oracle, world, L):
     from orin_llm_b200.dist import slice_bounds
-    n_head, n_kv, hd, L = 16, 2, 128, 5000
+    n_head, n_kv, hd = 16, 2, 128
     scale = np.float32(1.0 / np.sqrt(hd))
     nbytes = ops.peer_buffer_bytes(world, n_head, hd)
     bufs = [torch.zeros(nbytes, dtype=torch.uint8, device="cuda") for _ in range(world)]
@@ -50,11 +51,12 @@ def test_push_then_wait_on_one_device(ops, oracle, world):
             assert torch.equal(outs[r], outs[0])
 
 
-def test_fused_exchange_world_one(ops, oracle):
+@pytest.mark.parametrize("L", [3000, 150, 30000])      # 47 tiles; one CTA per kv head; ten group results per kv head
+def test_fused_exchange_world_one(ops, oracle, L):
     """oattn_decode_peer (push, wait and merge in one launch) with a single rank: the launch waits only for its own
     flag, so it can run alone on one GPU.  Covers the fused code path, its generation counter over repeated calls
     (both record slots) and the status word; equal to the plain decode call."""
-    n_head, n_kv, hd, L = 16, 2, 128, 3000
+    n_head, n_kv, hd = 16, 2, 128
     scale = np.float32(1.0 / np.sqrt(hd))
     buf = torch.zeros(ops.peer_buffer_bytes(1, n_head, hd), dtype=torch.uint8, device="cuda")
     state = torch.zeros(ops.peer_state_bytes(n_head), dtype=torch.uint8, device="cuda")
