@@ -184,9 +184,10 @@ int oattn_combine(const float* parts, int n_parts, float* out, int n_head, int h
 
 /* ---- multi-GPU exchange without a collective call (no reference counterpart) ----------------------------------
  * The record exchange of split-KV decode is 8 KB per rank: latency-bound.  Instead of all-gather + combine, a small
- * launch behind the decode launch (one CTA per head, so that the peer stores of a call leave from n_head SMs) stores
- * this rank's record straight into every rank's exchange buffer over NVLink (plain peer stores).  Every fp32 value travels in one aligned 8-byte word together with the generation number of
- * the call, so the receiver needs neither a fence nor a flag: it polls the words of its own buffer until they carry
+ * launch behind the decode launch (one CTA per head, so that the peer stores of a call leave from n_head SMs) finishes
+ * this rank's record -- the decode launch stops after its first merge level and leaves a handful of group results per
+ * kv head -- and stores it straight into every rank's exchange buffer over NVLink (plain peer stores).  Every fp32
+ * value travels in one aligned 8-byte word together with the generation number of the call, so the receiver needs neither a fence nor a flag: it polls the words of its own buffer until they carry
  * the current generation (bounded, ~2 s by default, see oattn_set_wait_limit_cycles; then a status word is set and the
  * output is left untouched) and merges the `world` records.
  *   exchange buffer   oattn_peer_buffer_bytes(world, n_head, head_dim) bytes on every rank, peer-mapped (e.g. CUDA

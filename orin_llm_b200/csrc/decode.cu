@@ -721,11 +721,14 @@ __global__ void combine_records_kernel(const float* parts, int n_parts, float* o
 }
 
 // ---- record exchange between ranks, one CTA per head ----------------------------------------------------------
-// The decode launch leaves this rank's record [n_head][hd + PART_PAD] in local memory.  CTA h stores head h's record
-// straight into every rank's exchange buffer (plain stores over NVLink, one tagged word per thread and rank), then --
-// with fused_wait -- waits for every rank's record of the same generation in its own buffer and writes the merged
-// output.  One CTA per head keeps the stores of a call spread over n_head SMs: from one or two SMs the same stores take
-// several times as long (measured on 8 GPUs).  Only CTA h touches gen_push[h].
+// The decode launch (defer_final) stops after its first merge level and leaves, per kv head, up to 16-odd group results
+// (M, L, O) in the workspace.  CTA h of this launch merges head h's column of them into this rank's record -- one round
+// of loads, every thread one dim -- and stores the record straight into every rank's exchange buffer (plain stores over
+// NVLink, one tagged word per thread and rank); then, with fused_wait, it waits for every rank's record of the same
+// generation in its own buffer and writes the merged output.  That takes the second ticket and the second merge pass of
+// the decode launch off the path between the last K/V byte and the first peer store, and one CTA per head keeps the
+// stores of a call spread over n_head SMs: from one or two SMs the same stores take several times as long (measured on
+// 8 GPUs).  Only CTA h touches gen_push[h].
 struct PeerExchangeArgs {
     const float* grp_o;                     // group results of the decode launch: [n_kv][n_groups][G][hd]
     const float* grp_ml;                    //                                     [n_kv][n_groups][G][2]  (M, L)
@@ -736,7 +739,7 @@ struct PeerExchangeArgs {
     int* gen_push;                          // [n_head]
     float* out;
     int* status;
-    int rank, world, n_head, head_dim, fused_wait;
+    int rank, world, n_head, head_dim, fused_wait, overlap;
     long long wait_cycles;
 };
 
@@ -745,11 +748,19 @@ __global__ void __launch_bounds__(160) peer_exchange_kernel(const PeerExchangeAr
     pdl_trigger();
     // how many group results the decode launch left for this kv head: its own plan, from the same position word
     const int G = p.n_head / p.n_kv, kvh = h / G, row = h - kvh * G;
+    // What does not depend on the decode launch is fetched while that launch still runs: the ranks' buffer addresses, and
+    // the position word where the caller vouched for it (overlap 2) -- the plan decides which loads follow the wait.
+    unsigned long long* peer[8];
+#pragma unroll
+    for (int r = 0; r < 8; ++r) peer[r] = r < p.world ? reinterpret_cast<unsigned long long*>(p.peer_bufs[r]) : nullptr;
+    int pos_word = 0;
+    if (p.overlap == 2) pos_word = __ldcg(p.d_pos);
     pdl_wait();                    // the decode launch's group results must be complete
+    if (p.overlap != 2) pos_word = __ldcg(p.d_pos);
     const unsigned g = (unsigned)(__ldcg(p.gen_push + h) + 1);
     const size_t rec_sz = hd + PART_PAD;
     if (tid < hd + 2) {
-        const int npos = clamp_len(__ldcg(p.d_pos) + p.pos_bias, p.n_ctx);
+        const int npos = clamp_len(pos_word + p.pos_bias, p.n_ctx);
         const SplitPlan plan = plan_splits(npos, p.n_splits, p.min_tiles);
         const int group = plan.active <= 16 ? max(plan.active, 1) : p.group;
         const int n_grp = plan.active <= 1 ? 1 : (plan.active + group - 1) / group;
@@ -786,9 +797,13 @@ __global__ void __launch_bounds__(160) peer_exchange_kernel(const PeerExchangeAr
         }
         // the record carries m in natural-log units of the scaled score
         const float v = tid < hd ? acc : (tid == hd ? M * p.scale : L);
-        for (int r = 0; r < p.world; ++r) {
-            unsigned long long* dst = reinterpret_cast<unsigned long long*>(p.peer_bufs[r]) +
-                                      ((size_t)((g & 1) * p.world + p.rank) * p.n_head + h) * rec_sz + tid;
+        const size_t off = ((size_t)((g & 1) * p.world + p.rank) * p.n_head + h) * rec_sz + tid;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            if (r < p.world) asm volatile("st.relaxed.sys.global.u64 [%0], %1;\n" ::"l"(peer[r] + off), "l"(tag_word(v, g)) : "memory");
+        }
+        for (int r = 8; r < p.world; ++r) {
+            unsigned long long* dst = reinterpret_cast<unsigned long long*>(p.peer_bufs[r]) + off;
             asm volatile("st.relaxed.sys.global.u64 [%0], %1;\n" ::"l"(dst), "l"(tag_word(v, g)) : "memory");
         }
     }
@@ -968,6 +983,7 @@ cudaError_t launch_peer_exchange(const DecodeArgs& d, const unsigned long long* 
     x.peer_bufs = peer_bufs; x.gen_push = gen_push; x.out = out; x.status = status;
     x.rank = rank; x.world = world; x.n_head = d.n_head; x.head_dim = d.head_dim; x.fused_wait = fused_wait;
     x.wait_cycles = wait_cycles;
+    x.overlap = overlap;
     cudaError_t e = launch_dependent(peer_exchange_kernel, dim3(d.n_head), 128 + 32, 0, stream, overlap, x);
     if (launches) *launches += 1;
     return e;

@@ -51,7 +51,8 @@ def gather_records(local, world_buf, group=None):
 
 class PeerSplitKVDecoder:
     """Split-KV decode whose record exchange is done by a kernel of this library: a launch of one CTA per head behind the
-    decode launch stores the rank's record into every rank's exchange buffer with plain peer stores over NVLink (every
+    decode launch merges the group results that launch left for its kv head into the rank's record and stores it into every
+    rank's exchange buffer with plain peer stores over NVLink (every
     value tagged with the call's generation number), then waits (bounded) until the other ranks' values of this
     generation have arrived in its own buffer and writes the merged output.  Two launches per layer call, no collective
     call, graph-capturable; fused=False keeps the wait in a launch of its own.

@@ -78,6 +78,24 @@ def test_fused_exchange_world_one(ops, oracle, L):
         assert torch.allclose(out, ref, rtol=1e-5, atol=1e-6)
 
 
+def test_fused_exchange_more_group_results_than_one_round(ops, oracle):
+    """One kv head gets all 2 x SM-count splits: at 100,000 rows the decode launch leaves 17 group results, which the
+    exchange launch merges in two rounds of loads."""
+    n_head, n_kv, hd, L = 8, 1, 128, 100000
+    scale = np.float32(1.0 / np.sqrt(hd))
+    buf = torch.zeros(ops.peer_buffer_bytes(1, n_head, hd), dtype=torch.uint8, device="cuda")
+    state = torch.zeros(ops.peer_state_bytes(n_head), dtype=torch.uint8, device="cuda")
+    ptrs = torch.tensor([buf.data_ptr()], dtype=torch.int64, device="cuda")
+    q, K, V = make_qkv(77, n_head, n_kv, hd, L)
+    want = oracle.attend(q[0], K.astype(np.float32), V.astype(np.float32), L, scale)
+    d_len = torch.tensor([L], dtype=torch.int32, device="cuda")
+    out = torch.empty(n_head, hd, device="cuda")
+    ops.attn_decode_peer(dev(q[0]), dev(K), dev(V), out, n_head, n_kv, hd, L, d_len, float(scale), ptrs.data_ptr(), 0, 1, state)
+    torch.cuda.synchronize()
+    assert ops.peer_status(state, n_head) == 0
+    assert_close(out.cpu().numpy(), want, "17 group results")
+
+
 def test_fused_prologue_on_a_sharded_cache(ops, oracle):
     """oattn_decode_peer_fused on the rank that owns the newest rows of a longer sequence: its local cache holds rows
     [lo, pos) of the sequence as local rows 0..pos-lo-1, the new token is rotated at its GLOBAL position `pos` and
