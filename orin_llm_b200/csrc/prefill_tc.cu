@@ -99,6 +99,7 @@ struct TcArgs {
     int mmq_ds4;
     int* status;
     int n_head, n_kv, n_past, batch, G, TQ;   // TQ = floor(128 / G) tokens per tile
+    int out_tma;           // the fp32 output leaves through shared memory and bulk tensor stores (tmO is valid)
 };
 
 // ---- PTX wrappers ---------------------------------------------------------------------------------
@@ -149,6 +150,10 @@ __device__ __forceinline__ void mbar_drain(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
     asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];\n"
                  ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, int c0, int c1, int c2, uint32_t src) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];\n"
+                 ::"l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(c0), "r"(c1), "r"(c2) : "memory");
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
@@ -282,7 +287,7 @@ constexpr uint32_t IDESC_PV = IDESC_S | (1u << 16);
 
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                  const __grid_constant__ CUtensorMap tmV, const TcArgs p) {
+                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO, const TcArgs p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t sbase = (raw + 1023u) & ~1023u;
@@ -582,7 +587,15 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 tmem_ld32(to + 64 * team + 32 * c, a);
 #pragma unroll
                 for (int i = 0; i < 32; ++i) a[i] *= inv;
-                if (valid && p.out) {
+                if (p.out_tma) {
+                    // Straight from here a warp's store would touch 32 rows, 512 bytes apart, with 16 bytes each.  The
+                    // tile goes through shared memory instead (the K ring is idle now): four slabs of 32 columns, a row's
+                    // 128 bytes of a slab swizzled like a tensor-map tile, and leaves as four bulk tensor stores.
+                    uint8_t* rowp = smem + OFF_K + (2 * team + c) * (BM * 128) + row * 128;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        *reinterpret_cast<float4*>(rowp + ((i ^ (row & 7)) << 4)) = make_float4(a[4 * i], a[4 * i + 1], a[4 * i + 2], a[4 * i + 3]);
+                } else if (valid && p.out) {
 #pragma unroll
                     for (int i = 0; i < 8; ++i)
                         *reinterpret_cast<float4*>(dst + 32 * c + 4 * i) = make_float4(a[4 * i], a[4 * i + 1], a[4 * i + 2], a[4 * i + 3]);
@@ -613,6 +626,18 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 }
             }
         }
+        if (p.out_tma) {
+            // every softmax thread comes here, whatever its waits returned
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");       // generic-proxy stores -> the bulk copies' reads
+            asm volatile("bar.sync 1, 256;\n" ::: "memory");
+            if (tid == 64 && !*s_abort) {
+                // rows past the batch (a ragged last tile) lie outside the tensor map and are not written
+#pragma unroll
+                for (int c = 0; c < 4; ++c) tma_store_3d(&tmO, 32 * c, kvh * p.G, t0, sbase + OFF_K + c * (BM * 128));
+                asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
+                asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");  // shared memory stays valid until it has been read
+            }
+        }
     }
 
     tc_fence_before();
@@ -629,6 +654,18 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 EncodeTiledFn g_encode = nullptr;
 
 // fp16 tensor [d2][d1][128] with the given strides (bytes); box = 64 x b1 x b2, 128-byte swizzle, zero fill.
+// fp32 tensor [d2][d1][128] (the output): box = 32 x b1 x b2 (one 128-byte swizzle span of columns), for stores.
+bool make_out_map(CUtensorMap* m, const void* base, uint64_t d1, uint64_t d2, uint64_t stride1, uint64_t stride2, uint32_t b1,
+                  uint32_t b2) {
+    cuuint64_t dims[3] = {(cuuint64_t)HD, d1, d2};
+    cuuint64_t strides[2] = {stride1, stride2};
+    cuuint32_t box[3] = {32, b1, b2};
+    cuuint32_t estr[3] = {1, 1, 1};
+    return g_encode(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 bool make_map(CUtensorMap* m, const void* base, uint64_t d1, uint64_t d2, uint64_t stride1, uint64_t stride2, uint32_t b1,
               uint32_t b2) {
     cuuint64_t dims[3] = {(cuuint64_t)HD, d1, d2};
@@ -671,14 +708,19 @@ cudaError_t launch_prefill_tc(const PrefillArgs& a, int sm_count, cudaStream_t s
     if (!make_map(&tmQ, a.q16, a.n_head, a.batch, rowb, rowb * a.n_head, G, TQ)) return cudaErrorInvalidValue;
     if (!make_map(&tmK, a.kc, rows, a.n_kv, rowb, rowb * a.n_ctx, BN, 1)) return cudaErrorInvalidValue;
     if (!make_map(&tmV, a.vc, rows, a.n_kv, rowb, rowb * a.n_ctx, BN, 1)) return cudaErrorInvalidValue;
+    // the fp32 output as a tensor map for bulk stores (16-byte aligned base; else the kernel stores directly)
+    CUtensorMap tmO = tmQ;
+    const uint64_t orow = HD * sizeof(float);
+    const bool out_tma = a.out && !((uintptr_t)a.out & 15) && make_out_map(&tmO, a.out, a.n_head, a.batch, orow, orow * a.n_head, G, TQ);
     TcArgs t;
+    t.out_tma = out_tma ? 1 : 0;
     t.out = a.out;
     t.out_mmq = a.out_mmq;
     t.mmq_ds4 = a.mmq_ds4;
     t.status = a.status;
     t.n_head = a.n_head; t.n_kv = a.n_kv; t.n_past = a.n_past; t.batch = a.batch; t.G = G; t.TQ = TQ;
     dim3 grid((a.batch + TQ - 1) / TQ, a.n_kv);
-    const cudaError_t e = launch_dependent(prefill_tc_kernel, grid, kThreads, SMEM_BYTES, stream, 1, tmQ, tmK, tmV, t);
+    const cudaError_t e = launch_dependent(prefill_tc_kernel, grid, kThreads, SMEM_BYTES, stream, 1, tmQ, tmK, tmV, tmO, t);
     if (launches) *launches += 1;
     return e;
 }
