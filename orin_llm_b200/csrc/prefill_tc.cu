@@ -9,7 +9,8 @@
 // R -> token t0 + R/G, head kvh*G + R%G (G = n_head/n_kv), so a single pass over the kv head's K/V rows
 // serves all G query heads of floor(128/G) tokens (when G does not divide 128 the last few tile rows are
 // zero and unused).  The KV sequence is walked in blocks of
-// 128 rows.  320 threads in three roles:
+// 128 rows.  384 threads = three warpgroups (warps 2 and 3 only hold the place that makes the softmax teams whole warpgroups,
+// so that registers can be moved to them); three roles:
 //   warp 0   (one lane)  TMA producer: Q tile once, then 128-row K blocks (three-stage ring) and V blocks
 //                        (two-stage ring) with cp.async.bulk.tensor, 128-byte swizzle, no multicast; rows
 //                        past the chunk are outside the tensor map and arrive as zeros
@@ -22,7 +23,7 @@
 //                        executes the tcgen05 instructions: eight MMAs and the commit of a group in one
 //                        predicated block, descriptors built once.  The commit behind S_j also frees K ring
 //                        stage j % 3, the commit behind P_j V_j also frees V ring stage j & 1.
-//   warps 2-5, 6-9       two softmax teams, one thread per row each, taking alternate KV blocks.  Per block:
+//   warps 4-7, 8-11      two softmax teams, one thread per row each, taking alternate KV blocks.  Per block:
 //                        tcgen05.ld of the 128-column score row, causal mask, row max; the reference max is a
 //                        single chain over all blocks, handed from team to team through shared memory (block
 //                        j continues from what the other team published for block j-1); lazy rescale of O
@@ -53,7 +54,9 @@ namespace oattn {
 
 namespace {
 
-constexpr int kThreads = 320;
+constexpr int kThreads = 384;                   // three warpgroups: {TMA, MMA, two idle warps}, softmax team 0, softmax team 1
+constexpr int kFirstSoftmaxWarp = 4;
+constexpr int kRegsService = 104, kRegsSoftmax = 200;   // per-thread register budgets after the set-up (setmaxnreg)
 constexpr int BM = 128, BN = 128, HD = 128;
 constexpr int SLAB = 128 * 128;                 // bytes of one 128-row x 64-element fp16 slab
 constexpr int TILE = 2 * SLAB;                  // a 128 x 128 fp16 tile = two slabs
@@ -340,6 +343,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     pdl_wait();
     const uint32_t TM_S = tmem, TM_O = tmem + NSB * BN;   // score buffer b at TM_S + 128 b, the accumulator behind them
 
+    // The kernel is compiled for 384 threads x 168 registers.  The warpgroup of the TMA and MMA warps needs fewer and hands
+    // the difference to the two softmax warpgroups, whose threads keep a 128-value score row in registers.  Each
+    // setmaxnreg sits at the head of the code it governs.
+    if (warp < kFirstSoftmaxWarp) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;\n" ::"n"(kRegsService));
     if (warp == 0) {
         // ---------------------------------------------------------------- TMA producer
         if (lane == 0) {
@@ -455,10 +463,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             mbar_drain(bar(DRAIN), 0);
         }
         __syncwarp();
+    }
     } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;\n" ::"n"(kRegsSoftmax));
         // ---------------------------------------------------------------- softmax + epilogue
         const int quad = warp & 3;                          // TMEM lane quadrant this warp may access
-        const int team = (warp - 2) >> 2;                   // 0: even KV blocks, 1: odd KV blocks
+        const int team = (warp - kFirstSoftmaxWarp) >> 2;   // 0: even KV blocks, 1: odd KV blocks
         const int row = quad * 32 + lane;
         const int tok = row / p.G, hg = row - tok * p.G;
         const int tglob = t0 + tok;
@@ -473,18 +483,18 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         for (int j = team; j < nb && ok; j += 2) {
             const int b = j % NSB;
             const uint32_t ts = TM_S + lane_addr + b * BN;  // score buffer of this block, this thread's lane
-            if (tid == 64 || tid == 192) TRACE(1 + team, 0, j);
+            if (tid == 128 || tid == 256) TRACE(1 + team, 0, j);
             // every give-up decision is made warp-uniform: the TMEM loads and stores below are warp-collective
             ok = __all_sync(0xffffffffu, mbar_wait(bar(S_FULL + b), (j / NSB) & 1, s_abort));
             if (!ok) break;
-            if (tid == 64 || tid == 192) TRACE(1 + team, 1, j);
+            if (tid == 128 || tid == 256) TRACE(1 + team, 1, j);
             tc_fence_after();
             float v[128];
             tmem_ld32(ts, v);
             tmem_ld32(ts + 32, v + 32);
             tmem_ld32(ts + 64, v + 64);
             tmem_ld32(ts + 96, v + 96);
-            if (tid == 64 || tid == 192) TRACE(1 + team, 2, j);
+            if (tid == 128 || tid == 256) TRACE(1 + team, 2, j);
             if (j * BN + BN - 1 > p.n_past + t0) {          // block reaches past the tile's first query: mask
                 const int lim = vis - j * BN;               // columns <= lim are visible
 #pragma unroll
@@ -537,7 +547,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 l *= (m_l == -CUDART_INF_F) ? 0.f : fast_exp2(m_l - m_new);
                 m_l = m_new;
             }
-            if (tid == 64 || tid == 192) TRACE(1 + team, 3, j);
+            if (tid == 128 || tid == 256) TRACE(1 + team, 3, j);
             // P (fp16 pairs) goes over the first 64 columns of this thread's own score row.
             uint32_t pk[64];
             float l4[4] = {0.f, 0.f, 0.f, 0.f};
@@ -551,14 +561,14 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 pk[i] = pack_half2(p0, p1);
             }
             l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
-            if (tid == 64 || tid == 192) TRACE(1 + team, 4, j);
+            if (tid == 128 || tid == 256) TRACE(1 + team, 4, j);
             tmem_st32(ts, reinterpret_cast<const float*>(pk));
             tmem_st32(ts + 32, reinterpret_cast<const float*>(pk + 32));
             asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(P_FULL + b));         // one arrival per warp (the barrier counts 4)
-            if (tid == 64 || tid == 192) TRACE(1 + team, 5, j);
+            if (tid == 128 || tid == 256) TRACE(1 + team, 5, j);
         }
         // ---- add the two teams' row sums and write the output -----------------------------------------
         float2* s_x = reinterpret_cast<float2*>(smem + OFF_MX);
@@ -630,7 +640,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             // every softmax thread comes here, whatever its waits returned
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");       // generic-proxy stores -> the bulk copies' reads
             asm volatile("bar.sync 1, 256;\n" ::: "memory");
-            if (tid == 64 && !*s_abort) {
+            if (tid == 32 * kFirstSoftmaxWarp && !*s_abort) {
                 // rows past the batch (a ragged last tile) lie outside the tensor map and are not written
 #pragma unroll
                 for (int c = 0; c < 4; ++c) tma_store_3d(&tmO, 32 * c, kvh * p.G, t0, sbase + OFF_K + c * (BM * 128));
