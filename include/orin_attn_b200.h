@@ -279,7 +279,8 @@ size_t oattn_prefill_workspace_bytes(int n_head, int n_kv, int head_dim, int max
 /* Replaces the prefill sequence rope_*_batch(q), rope_*_batch(k), kv_store_batch,
  * flash_attention (src/model_gpu.cu:379-384; src/kernels.cu:1974-1981).  Query token t of
  * q [batch][n_head][head_dim] sits at position n_past + t and sees cache rows 0..n_past+t.
- * With fuse == OATTN_FUSE_NONE it is exactly cuda::flash_attention. */
+ * With fuse == OATTN_FUSE_NONE it is exactly cuda::flash_attention.  `out` must be 16-byte aligned
+ * (OATTN_ERR_ARG otherwise); q, k_new and v_new may have any float alignment. */
 int oattn_prefill(const float* q, const float* k_new, const float* v_new, uint16_t* kc, uint16_t* vc,
                   float* out, int n_head, int n_kv, int head_dim, int n_ctx, int n_past, int batch,
                   float scale, int fuse, const oattn_rope_params* rope, void* workspace, size_t workspace_bytes,

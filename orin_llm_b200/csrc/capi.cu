@@ -462,6 +462,7 @@ int oattn_prefill_ex(const float* q, const float* k_new, const float* v_new, uin
     if (!q || !kc || !vc || (!out && !mmq_only) || n_ctx <= 0 || !(scale > 0.0f)) return OATTN_ERR_ARG;
     if (mmq_only && (head_dim != 128 || g_prefill_impl != 0 || ((uintptr_t)ext->out_mmq & 15))) return OATTN_ERR_UNSUPPORTED;
     if (batch <= 0 || n_past < 0 || n_past + batch > n_ctx) return OATTN_ERR_ARG;
+    if ((uintptr_t)out & 15) return OATTN_ERR_ARG;                     // the output is written in 16-byte pieces
     if (fuse & ~OATTN_FUSE_ALL) return OATTN_ERR_ARG;
     if ((fuse & OATTN_FUSE_ROPE_K) && !(fuse & OATTN_FUSE_KV_APPEND)) return OATTN_ERR_ARG;
     if ((fuse & OATTN_FUSE_KV_APPEND) && (!k_new || !v_new)) return OATTN_ERR_ARG;
