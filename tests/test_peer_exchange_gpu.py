@@ -78,6 +78,32 @@ def test_fused_exchange_world_one(ops, oracle, L):
         assert torch.allclose(out, ref, rtol=1e-5, atol=1e-6)
 
 
+def test_rank_without_rows_contributes_the_neutral_record(ops, oracle):
+    """A context shorter than the number of tiles the ranks could share: rank 1 of 2 owns no row at all (length 0).  Its
+    decode launch leaves the empty state (m = -inf, l = 0), the exchange launch turns it into the neutral record, and
+    both ranks' outputs equal the oracle over rank 0's rows."""
+    n_head, n_kv, hd, L, world = 16, 2, 128, 50, 2
+    scale = np.float32(1.0 / np.sqrt(hd))
+    nbytes = ops.peer_buffer_bytes(world, n_head, hd)
+    bufs = [torch.zeros(nbytes, dtype=torch.uint8, device="cuda") for _ in range(world)]
+    states = [torch.zeros(ops.peer_state_bytes(n_head), dtype=torch.uint8, device="cuda") for _ in range(world)]
+    ptrs = torch.tensor([b.data_ptr() for b in bufs], dtype=torch.int64, device="cuda")
+    q, K, V = make_qkv(321, n_head, n_kv, hd, L, 64)
+    want = oracle.attend(q[0], K.astype(np.float32), V.astype(np.float32), L, scale)
+    dq, dK, dV = dev(q[0]), dev(K), dev(V)
+    lens = [torch.tensor([L], dtype=torch.int32, device="cuda"), torch.tensor([0], dtype=torch.int32, device="cuda")]
+    for r in range(world):
+        ops.attn_decode_partial_push(dq, dK, dV, n_head, n_kv, hd, 64, lens[r], float(scale), ptrs.data_ptr(), r, world, states[r])
+    outs = [torch.empty(n_head, hd, device="cuda") for _ in range(world)]
+    for r in range(world):
+        ops.attn_peer_wait_combine(bufs[r], world, outs[r], n_head, hd, states[r])
+    torch.cuda.synchronize()
+    for r in range(world):
+        assert ops.peer_status(states[r], n_head) == 0
+        assert_close(outs[r].cpu().numpy(), want, "rank %d" % r)
+    assert torch.equal(outs[0], outs[1])
+
+
 def test_fused_exchange_more_group_results_than_one_round(ops, oracle):
     """One kv head gets all 2 x SM-count splits: at 100,000 rows the decode launch leaves 17 group results, which the
     exchange launch merges in two rounds of loads."""
