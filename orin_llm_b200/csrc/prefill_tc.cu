@@ -257,6 +257,19 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
                  : "memory");
 }
 
+__device__ __forceinline__ unsigned long long f32x2_pack(float lo, float hi) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};\n" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void f32x2_unpack(unsigned long long v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;\n" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long f32x2_add(unsigned long long a, unsigned long long b) {
+    unsigned long long r;
+    asm("add.rn.f32x2 %0, %1, %2;\n" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
 __device__ __forceinline__ float max3(float a, float b, float c) {
     float d;
     asm("max.f32 %0, %1, %2, %3;\n" : "=f"(d) : "f"(a), "f"(b), "f"(c));
@@ -550,17 +563,26 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             if (tid == 128 || tid == 256) TRACE(1 + team, 3, j);
             // P (fp16 pairs) goes over the first 64 columns of this thread's own score row.
             uint32_t pk[64];
-            float l4[4] = {0.f, 0.f, 0.f, 0.f};
+            // two-wide fp32 adds (add.f32x2) for the subtraction of the reference max and for the row sum: the loop is
+            // short of issue slots, not of arithmetic
+            unsigned long long l2[4] = {0ull, 0ull, 0ull, 0ull};       // four accumulators of (even, odd) partial sums
+            const unsigned long long negm = f32x2_pack(-m_use, -m_use);
 #pragma unroll
             for (int i = 0; i < 64; ++i) {
-                const float x0 = v[2 * i] - m_use, x1 = v[2 * i + 1] - m_use;
+                float x0, x1;
+                f32x2_unpack(f32x2_add(f32x2_pack(v[2 * i], v[2 * i + 1]), negm), x0, x1);
                 float p0, p1;
                 if (OATTN_TC_POLY && (i % (OATTN_TC_POLY ? OATTN_TC_POLY : 1)) == OATTN_TC_POLY - 1) { p0 = exp2_poly(x0); p1 = exp2_poly(x1); }
                 else { p0 = fast_exp2(x0); p1 = fast_exp2(x1); }
-                l4[i & 3] += p0 + p1;
+                l2[i & 3] = f32x2_add(l2[i & 3], f32x2_pack(p0, p1));
                 pk[i] = pack_half2(p0, p1);
             }
-            l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
+            {
+                float a0, a1, b0, b1;
+                f32x2_unpack(f32x2_add(f32x2_add(l2[0], l2[1]), f32x2_add(l2[2], l2[3])), a0, a1);
+                (void)b0; (void)b1;
+                l += a0 + a1;
+            }
             if (tid == 128 || tid == 256) TRACE(1 + team, 4, j);
             tmem_st32(ts, reinterpret_cast<const float*>(pk));
             tmem_st32(ts + 32, reinterpret_cast<const float*>(pk + 32));
